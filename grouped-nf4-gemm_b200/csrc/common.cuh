@@ -1,0 +1,180 @@
+// Shared device helpers: codebooks, scale conversion, mbarrier / bulk-copy PTX wrappers
+// with bounded waits.  sm_100a only.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/gnf4b.h"
+
+namespace gnf4b {
+
+// ---- codebooks (values identical to NF4_LUT / FP4_VALUES of the reference,
+//      kernel/nf4_grouped.py:53-70 and kernel/mxfp4_grouped.py:34-35) ----
+__device__ __constant__ float kNf4Lut[16] = {
+    -1.0f, -0.6961928009986877f, -0.5250730514526367f, -0.39491748809814453f,
+    -0.28444138169288635f, -0.18477343022823334f, -0.09105003625154495f, 0.0f,
+    0.07958029955625534f, 0.16093020141124725f, 0.24611230194568634f,
+    0.33791524171829224f, 0.44070982933044434f, 0.5626170039176941f,
+    0.7229568362236023f, 1.0f};
+__device__ __constant__ float kFp4Lut[16] = {
+    0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f,
+    -0.0f, -0.5f, -1.0f, -1.5f, -2.0f, -3.0f, -4.0f, -6.0f};
+
+// Both codebook values of one packed byte, in ELEMENT order (even element first).
+// NF4 keeps the even element in the high nibble, MXFP4 in the low nibble.
+// MXFP4 values come back DOUBLED (0, 1, 2, 3, 4, 6, 8, 12) and load_scale returns
+// 2^(e-128): the product is the same number, every step is exact, and the largest block
+// exponent (e = 255, i.e. 2^128, not an fp32 value) needs no special case -- 0.5 * 2^128
+// is the finite 2^127, larger magnitudes overflow to inf and zeros stay zero, exactly as
+// ldexp(value, e - 127) does.
+template <int FMT>
+__device__ __forceinline__ float2 byte_pair(uint32_t b) {
+    if (FMT == GNF4B_FMT_NF4) return make_float2(kNf4Lut[b >> 4], kNf4Lut[b & 15]);
+    return make_float2(2.0f * kFp4Lut[b & 15], 2.0f * kFp4Lut[b >> 4]);
+}
+
+__device__ __forceinline__ float bf16_bits_to_float(uint32_t h) { return __uint_as_float(h << 16); }
+
+// One block scale as fp32.  NF4: the absmax itself (bf16 widened exactly).  MXFP4:
+// 2^(e-128) (see byte_pair): subnormal for e < 2, always finite.
+template <int SDT>
+__device__ __forceinline__ float load_scale(const void* base, int64_t idx) {
+    if (SDT == GNF4B_S_F32) return __ldg(reinterpret_cast<const float*>(base) + idx);
+    if (SDT == GNF4B_S_BF16)
+        return bf16_bits_to_float(__ldg(reinterpret_cast<const unsigned short*>(base) + idx));
+    const uint32_t e = __ldg(reinterpret_cast<const unsigned char*>(base) + idx);
+    return __uint_as_float(e >= 2 ? (e - 1) << 23 : 0x00200000u << e);
+}
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void fence_barrier_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Every wait in these kernels is bounded: after kWaitLimitNs without progress the
+// waiter raises *abort_flag (shared memory), and every other waiter of the CTA sees it
+// and leaves too; the kernel then records GNF4B_ST_TIMEOUT and returns.
+constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
+
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity,
+                                                  volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    uint32_t spins = 0;
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((++spins & 63u) == 0) {
+            if (*abort_flag) return false;
+            if (global_timer_ns() - t0 > kWaitLimitNs) {
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+}
+
+// 1-D bulk copy global -> shared, completion counted on an mbarrier (TMA engine).
+// Both addresses 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes,
+                                         uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_u32(dst_smem)), "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
+
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+
+__device__ __forceinline__ float ld_shared_f32(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float2 ld_shared_f32x2(uint32_t addr) {
+    float2 v;
+    asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float4 ld_shared_f32x4(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint4 ld_shared_u32x4(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "r"(addr));
+    return v;
+}
+
+__device__ __forceinline__ uint16_t f32_to_bf16_bits(float x) {
+    return __bfloat16_as_ushort(__float2bfloat16_rn(x));
+}
+
+// Problem description shared by all GEMM kernels.
+struct GemmArgs {
+    const void* x;          // activations / grad rows
+    const uint8_t* W;       // packed nibbles
+    const void* S;          // scales
+    const int32_t* off;     // [G+1]
+    const int32_t* eids;    // [G]
+    void* out;              // bf16
+    float* ws;              // split-K partials [split][T][N]
+    int32_t* counters;      // split-K arrival counters, one per (group, n-tile)
+    int32_t* status;        // optional
+    int64_t w_se, w_sn;     // bytes
+    int64_t s_se, s_sn;     // elements
+    int64_t T, N, K;
+    int32_t G, E;
+    int32_t x_dtype;
+    int32_t split_k;
+};
+
+}  // namespace gnf4b

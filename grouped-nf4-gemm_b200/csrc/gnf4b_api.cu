@@ -1,0 +1,343 @@
+// C ABI of libgnf4b.so (see include/gnf4b.h): argument checks, launch planning, launches.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "common.cuh"
+#include "stream_kernel.cuh"
+#include "tensor_kernel.cuh"
+
+namespace gnf4b {
+
+static thread_local char g_cuda_err[256] = "";
+
+static int cuda_fail(cudaError_t e, const char* what) {
+    snprintf(g_cuda_err, sizeof g_cuda_err, "%s: %s", what, cudaGetErrorString(e));
+    return GNF4B_ECUDA;
+}
+
+struct DevInfo {
+    int sm_count = 0;
+    int smem_optin = 0;
+    bool ok = false;
+};
+
+static int device_info(DevInfo* out) {
+    static std::mutex mu;
+    static DevInfo cache[64];
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    if (dev < 0 || dev >= 64) return GNF4B_EINVAL;
+    std::lock_guard<std::mutex> lk(mu);
+    if (!cache[dev].ok) {
+        e = cudaDeviceGetAttribute(&cache[dev].sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute(SM count)");
+        e = cudaDeviceGetAttribute(&cache[dev].smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute(shared memory)");
+        cache[dev].ok = true;
+    }
+    *out = cache[dev];
+    return GNF4B_OK;
+}
+
+static inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+static inline int64_t round_up(int64_t a, int64_t b) { return ceil_div(a, b) * b; }
+
+// ------------------------------------------------------------------ planning
+struct Plan {
+    int path = 0;            // GNF4B_PATH_STREAM / GNF4B_PATH_TENSOR
+    // stream path
+    int split_k = 1;
+    int chunk_bytes = 1024;
+    int n_chunks = 1;
+    int chunks_per_split = 1;
+    int rows_cap = 1;
+    int a_units_pad = 32;
+    int au = 0;
+    int64_t n_tiles = 0;
+    size_t counters_bytes = 0;
+    size_t ws_bytes = 0;
+};
+
+static int check_shape(int fmt, int op, int x_dtype, int s_dtype, int64_t T, int32_t G, int32_t E,
+                       int64_t N, int64_t K) {
+    if (fmt != GNF4B_FMT_NF4 && fmt != GNF4B_FMT_MXFP4) return GNF4B_EINVAL;
+    if (op != GNF4B_OP_FWD && op != GNF4B_OP_DGRAD) return GNF4B_EINVAL;
+    if (x_dtype != GNF4B_X_BF16 && x_dtype != GNF4B_X_FP16) return GNF4B_EINVAL;
+    if (fmt == GNF4B_FMT_NF4 && s_dtype != GNF4B_S_F32 && s_dtype != GNF4B_S_BF16) return GNF4B_EINVAL;
+    if (fmt == GNF4B_FMT_MXFP4 && s_dtype != GNF4B_S_E8M0) return GNF4B_EINVAL;
+    if (T < 0 || G < 0 || E <= 0 || N <= 0 || K <= 0) return GNF4B_ESHAPE;
+    if (K % (fmt == GNF4B_FMT_NF4 ? 64 : 32)) return GNF4B_ESHAPE;
+    if (T > INT32_MAX) return GNF4B_ETOOBIG;
+    return GNF4B_OK;
+}
+
+static int make_plan(int fmt, int op, int64_t T, int32_t G, int64_t N, int64_t K, int32_t max_rows,
+                     uint32_t flags, const DevInfo& di, Plan* p) {
+    const uint32_t want = flags & GNF4B_PATH_MASK;
+    const int forced_split = (int)((flags & GNF4B_SPLITK_MASK) >> GNF4B_SPLITK_SHIFT);
+    int path = (int)want;
+    if (path == GNF4B_PATH_AUTO) {
+        // Streaming kernel while groups are a couple of rows at most (its per-element cost
+        // grows with the rows of a group); tensor cores beyond that.  Without a host-known
+        // maximum the mean T/G decides.
+        const double mean_rows = G > 0 ? (double)T / G : 0.0;
+        const bool small = (max_rows > 0) ? (max_rows <= 4 && mean_rows <= 2.0) : (mean_rows <= 1.5);
+        path = (op == GNF4B_OP_DGRAD) ? GNF4B_PATH_TENSOR : (small ? GNF4B_PATH_STREAM : GNF4B_PATH_TENSOR);
+        if (forced_split > 1 && op == GNF4B_OP_FWD) path = GNF4B_PATH_STREAM;
+    }
+    if (path == GNF4B_PATH_STREAM && op == GNF4B_OP_DGRAD) return GNF4B_EUNSUPPORTED;
+    p->path = path;
+    if (path == GNF4B_PATH_TENSOR) return GNF4B_OK;
+
+    const int64_t row_bytes = K / 2;
+    const int unit = (fmt == GNF4B_FMT_NF4) ? 32 : 16;   // chunk granularity in bytes
+    p->n_tiles = ceil_div(N, kSTileN);
+    int S = 1;
+    int chunk = kSRowPitch;
+    if (forced_split > 1) {
+        S = forced_split;
+        const int64_t want_chunk = round_up(ceil_div(row_bytes, S), unit);
+        chunk = (int)std::min<int64_t>(kSRowPitch, std::max<int64_t>(unit, want_chunk));
+    } else if (forced_split == 0) {
+        // starved grid: fewer than two items per SM, and at least 2048 elements per split
+        const int64_t items = (int64_t)G * p->n_tiles;
+        const int64_t full_chunks = ceil_div(row_bytes, kSRowPitch);
+        if (items > 0 && items < 2 * (int64_t)di.sm_count && full_chunks > 1) {
+            const int64_t wantS = ceil_div(4 * (int64_t)di.sm_count, items);
+            while (S < wantS && S < 8 && S * 2 <= full_chunks) S *= 2;
+        }
+    }
+    p->chunk_bytes = chunk;
+    p->n_chunks = (int)ceil_div(row_bytes, chunk);
+    p->chunks_per_split = (int)ceil_div(p->n_chunks, S);
+    p->split_k = (int)ceil_div(p->n_chunks, p->chunks_per_split);   // no empty splits
+    p->a_units_pad = (int)round_up(K / 32, 32);
+    const int64_t fixed = (int64_t)kSTableBytes + (int64_t)kSStages * kSStageBytes + 256;
+    const int64_t per_row = (int64_t)p->a_units_pad * 128;
+    int64_t cap = (di.smem_optin - fixed) / per_row;
+    if (cap < 1) return GNF4B_EUNSUPPORTED;
+    cap = std::min<int64_t>(cap, kSRowsMax);
+    if (max_rows > 0) cap = std::min<int64_t>(cap, max_rows);
+    p->rows_cap = (int)cap;
+    p->au = (chunk == kSRowPitch) ? (K <= 2048 ? 2 : (K <= 3072 ? 3 : 0)) : 0;
+    if (p->split_k > 1) {
+        p->counters_bytes = (size_t)round_up((int64_t)G * p->n_tiles * 4, 256);
+        p->ws_bytes = (size_t)p->split_k * (size_t)T * (size_t)N * 4;
+    }
+    return GNF4B_OK;
+}
+
+// ------------------------------------------------------------------ launches
+template <int FMT, int SDT>
+static cudaError_t launch_stream_au(const StreamArgs& sa, int au, int grid, size_t smem, cudaStream_t st) {
+#define GNF4B_LAUNCH_AU(AUV)                                                                          \
+    do {                                                                                              \
+        auto kfn = stream_gemm_kernel<FMT, SDT, AUV>;                                                 \
+        cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        if (e != cudaSuccess) return e;                                                               \
+        kfn<<<grid, kSThreads, smem, st>>>(sa);                                                       \
+        return cudaGetLastError();                                                                    \
+    } while (0)
+    if (au == 2) GNF4B_LAUNCH_AU(2);
+    if (au == 3) GNF4B_LAUNCH_AU(3);
+    GNF4B_LAUNCH_AU(0);
+#undef GNF4B_LAUNCH_AU
+}
+
+static int align_class(const void* p, int64_t a, int64_t b) {
+    const uint64_t v = (uint64_t)(uintptr_t)p | (uint64_t)a | (uint64_t)b;
+    if ((v & 15) == 0) return 16;
+    if ((v & 7) == 0) return 8;
+    if ((v & 3) == 0) return 4;
+    return 1;
+}
+
+// ------------------------------------------------------------------ small kernels
+__global__ void offsets_kernel(const int32_t* sizes, int32_t G, int32_t* off) {
+    // one warp, ordered scan: G is at most a few thousand
+    __shared__ int32_t carry;
+    if (threadIdx.x == 0) { carry = 0; off[0] = 0; }
+    __syncwarp();
+    for (int base = 0; base < G; base += 32) {
+        const int g = base + threadIdx.x;
+        int v = (g < G) ? sizes[g] : 0;
+        if (v < 0) v = 0;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, v, o);
+            if ((int)threadIdx.x >= o) v += t;
+        }
+        const int c = carry;
+        if (g < G) off[g + 1] = c + v;
+        __syncwarp();
+        if (threadIdx.x == 31) carry = c + v;
+        __syncwarp();
+    }
+}
+
+template <int FMT, int SDT>
+__global__ void dequant_kernel(const uint8_t* W, int64_t w_se, int64_t w_sn, const void* S, int64_t s_se,
+                               int64_t s_sn, int32_t E, int64_t N, int64_t K, float* out) {
+    const int64_t half = K / 2;
+    const int64_t total = (int64_t)E * N * half;
+    const int64_t blk = (FMT == GNF4B_FMT_NF4) ? 64 : 32;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t j = i % half;
+        const int64_t r = i / half;
+        const int64_t n = r % N, e = r / N;
+        const uint32_t b = W[e * w_se + n * w_sn + j];
+        const float2 p = byte_pair<FMT>(b);
+        const float sc = load_scale<SDT>(S, e * s_se + n * s_sn + (2 * j) / blk);
+        reinterpret_cast<float2*>(out)[(e * N + n) * half + j] = make_float2(p.x * sc, p.y * sc);
+    }
+}
+
+}  // namespace gnf4b
+
+using namespace gnf4b;
+
+extern "C" {
+
+int gnf4b_abi_version(void) { return GNF4B_ABI_VERSION; }
+
+const char* gnf4b_strerror(int rc) {
+    switch (rc) {
+        case GNF4B_OK: return "ok";
+        case GNF4B_EINVAL: return "invalid argument (enum, null or misaligned pointer, negative size)";
+        case GNF4B_ESHAPE: return "shape violates the contract (K not a multiple of the quant block, N <= 0, ...)";
+        case GNF4B_EWORKSPACE: return "workspace missing or smaller than gnf4b_workspace_bytes()";
+        case GNF4B_ECUDA: return "a CUDA runtime call failed (gnf4b_last_cuda_error has the text)";
+        case GNF4B_EUNSUPPORTED: return "this combination is not supported by the requested path";
+        case GNF4B_ETOOBIG: return "a size exceeds a fixed maximum of this entry point";
+        default: return "unknown gnf4b error";
+    }
+}
+
+const char* gnf4b_last_cuda_error(void) { return g_cuda_err; }
+
+int gnf4b_device_info(int32_t* sm_count, int32_t* smem_optin_bytes) {
+    DevInfo di;
+    int rc = device_info(&di);
+    if (rc) return rc;
+    if (sm_count) *sm_count = di.sm_count;
+    if (smem_optin_bytes) *smem_optin_bytes = di.smem_optin;
+    return GNF4B_OK;
+}
+
+size_t gnf4b_workspace_bytes(int fmt, int op, int64_t T, int32_t G, int64_t N, int64_t K,
+                             int32_t max_rows, uint32_t flags) {
+    DevInfo di;
+    if (device_info(&di)) return 0;
+    Plan p;
+    if (make_plan(fmt, op, T, G, N, K, max_rows, flags, di, &p)) return 0;
+    return p.counters_bytes + p.ws_bytes;
+}
+
+int gnf4b_plan_split_k(int fmt, int op, int64_t T, int32_t G, int64_t N, int64_t K, int32_t max_rows,
+                       uint32_t flags) {
+    DevInfo di;
+    int rc = device_info(&di);
+    if (rc) return rc;
+    Plan p;
+    rc = make_plan(fmt, op, T, G, N, K, max_rows, flags, di, &p);
+    if (rc) return rc;
+    return p.path == GNF4B_PATH_STREAM ? p.split_k : 1;
+}
+
+int gnf4b_gemm_grouped(int fmt, int op, const void* x, int x_dtype, int64_t T, const uint8_t* W,
+                       int64_t w_stride_e, int64_t w_stride_n, const void* S, int s_dtype,
+                       int64_t s_stride_e, int64_t s_stride_n, const int32_t* group_offsets,
+                       const int32_t* expert_ids, int32_t G, int32_t E, int64_t N, int64_t K,
+                       int32_t max_rows, void* out, void* workspace, size_t workspace_bytes,
+                       int32_t* status_word, uint32_t flags, void* cuda_stream) {
+    int rc = check_shape(fmt, op, x_dtype, s_dtype, T, G, E, N, K);
+    if (rc) return rc;
+    if (T == 0 || G == 0) return GNF4B_OK;
+    if (!x || !W || !S || !group_offsets || !expert_ids || !out) return GNF4B_EINVAL;
+    if (((uintptr_t)x & 15) || ((uintptr_t)out & 15)) return GNF4B_EINVAL;
+    if (w_stride_n < K / 2 || w_stride_e < 0 || s_stride_n < 0 || s_stride_e < 0) return GNF4B_EINVAL;
+    DevInfo di;
+    rc = device_info(&di);
+    if (rc) return rc;
+    Plan p;
+    rc = make_plan(fmt, op, T, G, N, K, max_rows, flags, di, &p);
+    if (rc) return rc;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(cuda_stream);
+
+    GemmArgs g;
+    g.x = x; g.W = W; g.S = S; g.off = group_offsets; g.eids = expert_ids; g.out = out;
+    g.ws = nullptr; g.counters = nullptr; g.status = status_word;
+    g.w_se = w_stride_e; g.w_sn = w_stride_n; g.s_se = s_stride_e; g.s_sn = s_stride_n;
+    g.T = T; g.N = N; g.K = K; g.G = G; g.E = E; g.x_dtype = x_dtype; g.split_k = 1;
+
+    if (p.path == GNF4B_PATH_TENSOR) {
+        rc = launch_tensor(fmt, op, s_dtype, g, max_rows, di.sm_count, di.smem_optin, st);
+        if (rc == GNF4B_ECUDA) return cuda_fail(cudaGetLastError(), "tensor kernel launch");
+        return rc;
+    }
+
+    if (p.split_k > 1) {
+        if (!workspace || workspace_bytes < p.counters_bytes + p.ws_bytes) return GNF4B_EWORKSPACE;
+        g.counters = reinterpret_cast<int32_t*>(workspace);
+        g.ws = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + p.counters_bytes);
+    }
+    g.split_k = p.split_k;
+    StreamArgs sa;
+    sa.g = g;
+    sa.n_tiles = (int32_t)p.n_tiles;
+    sa.chunk_bytes = p.chunk_bytes;
+    sa.n_chunks = p.n_chunks;
+    sa.chunks_per_split = p.chunks_per_split;
+    sa.rows_cap = p.rows_cap;
+    sa.a_units_pad = p.a_units_pad;
+    sa.w_align = align_class(W, w_stride_e, w_stride_n);
+    sa.total_items = (int64_t)G * p.n_tiles * p.split_k;
+    const size_t smem = stream_smem_bytes(p.rows_cap, p.a_units_pad);
+    const int grid = (int)std::min<int64_t>(di.sm_count, sa.total_items);
+    cudaError_t e;
+    if (fmt == GNF4B_FMT_NF4 && s_dtype == GNF4B_S_F32)
+        e = launch_stream_au<GNF4B_FMT_NF4, GNF4B_S_F32>(sa, p.au, grid, smem, st);
+    else if (fmt == GNF4B_FMT_NF4)
+        e = launch_stream_au<GNF4B_FMT_NF4, GNF4B_S_BF16>(sa, p.au, grid, smem, st);
+    else
+        e = launch_stream_au<GNF4B_FMT_MXFP4, GNF4B_S_E8M0>(sa, p.au, grid, smem, st);
+    if (e != cudaSuccess) return cuda_fail(e, "stream kernel launch");
+    return GNF4B_OK;
+}
+
+int gnf4b_build_offsets(const int32_t* sizes, int32_t G, int32_t* group_offsets, void* cuda_stream) {
+    if (G < 0 || !group_offsets || (G > 0 && !sizes)) return GNF4B_EINVAL;
+    offsets_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(cuda_stream)>>>(sizes, G, group_offsets);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "offsets kernel launch");
+    return GNF4B_OK;
+}
+
+int gnf4b_dequant(int fmt, const uint8_t* W, int64_t w_stride_e, int64_t w_stride_n, const void* S,
+                  int s_dtype, int64_t s_stride_e, int64_t s_stride_n, int32_t E, int64_t N, int64_t K,
+                  float* out_f32, void* cuda_stream) {
+    int rc = check_shape(fmt, GNF4B_OP_FWD, GNF4B_X_BF16, s_dtype, 0, 0, E, N, K);
+    if (rc) return rc;
+    if (!W || !S || !out_f32) return GNF4B_EINVAL;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(cuda_stream);
+    const int64_t total = (int64_t)E * N * (K / 2);
+    const int grid = (int)std::min<int64_t>(ceil_div(total, 256), 148 * 16);
+    if (fmt == GNF4B_FMT_NF4 && s_dtype == GNF4B_S_F32)
+        dequant_kernel<GNF4B_FMT_NF4, GNF4B_S_F32><<<grid, 256, 0, st>>>(W, w_stride_e, w_stride_n, S, s_stride_e, s_stride_n, E, N, K, out_f32);
+    else if (fmt == GNF4B_FMT_NF4)
+        dequant_kernel<GNF4B_FMT_NF4, GNF4B_S_BF16><<<grid, 256, 0, st>>>(W, w_stride_e, w_stride_n, S, s_stride_e, s_stride_n, E, N, K, out_f32);
+    else
+        dequant_kernel<GNF4B_FMT_MXFP4, GNF4B_S_E8M0><<<grid, 256, 0, st>>>(W, w_stride_e, w_stride_n, S, s_stride_e, s_stride_n, E, N, K, out_f32);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "dequant kernel launch");
+    return GNF4B_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,87 @@
+"""Grouped W4A16 GEMM over native MXFP4 expert stacks on NVIDIA B200 -- the drop-in for
+the reference module of the same name (pjordanandrsn/grouped-nf4-gemm,
+kernel/mxfp4_grouped.py:134-172).
+
+``out[t] = a[t] @ dequant_mxfp4(blocks[e(t)]).T`` for rows grouped by expert, one launch of
+the sm_100a kernels in ``libgnf4b.so``.  Decode rules (ref :7-16): e2m1 codebook, element
+2j in the LOW nibble of byte j, one e8m0 scale byte per 32 elements with value 2^(e-127).
+The decode follows the ``ldexp`` semantics of ``mxfp4_pack_ref.dequant_mxfp4`` (a zero
+element times the 0xFF scale stays zero).  Offsets are 64-bit throughout, so stacks beyond
+2 GiB are fine (the reference's Triton kernel multiplies ``eid * stride`` in int32,
+ref :65, 73).
+"""
+from __future__ import annotations
+
+import torch
+
+import _gnf4b
+from nf4_grouped import (_launch, _prefill_block_m, _require_cuda,  # noqa: F401  (re-exported names)
+                         build_group_tiles)
+
+# e2m1 codebook, index = (sign << 3) | magnitude (ref :34-35)
+FP4_VALUES = [0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0,
+              -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0]
+MX_BLOCK = 32
+E8M0_BIAS = 127
+
+_LUT_CACHE: dict = {}
+
+
+def _lut(device):
+    key = str(device)
+    if key not in _LUT_CACHE:
+        _LUT_CACHE[key] = torch.tensor(FP4_VALUES, dtype=torch.float32, device=device)
+    return _LUT_CACHE[key]
+
+
+def gemm_mxfp4_grouped(a_cat, blocks, scales, sizes, expert_ids,
+                       block_m: int | None = None, prefill_variant: int | None = None):
+    """Single-launch grouped MXFP4 GEMM (ref :134-172).  ``a_cat [T,K]`` bf16/fp16 rows
+    sorted by group; ``blocks [E,N,K//2]`` uint8; ``scales [E,N,K//32]`` uint8 (e8m0);
+    ``sizes`` per-group row counts; ``expert_ids [G]`` list / CPU / CUDA int tensor.
+    Returns ``[T,N]`` bf16 in the same row order.  ``block_m`` and ``prefill_variant`` are
+    Triton knobs of the reference, accepted and ignored."""
+    E, N, _ = blocks.shape
+    T, K = a_cat.shape
+    assert scales.shape == (E, N, K // MX_BLOCK), (scales.shape, (E, N, K // MX_BLOCK))
+    assert blocks.dtype == torch.uint8 and scales.dtype == torch.uint8
+    _require_cuda(a_cat, "gemm_mxfp4_grouped",
+                  "For a CPU-checkable decode of the same MXFP4 bytes, use "
+                  "mxfp4_pack_ref.dequant_mxfp4(blocks, scales).")
+    if blocks.shape[2] * 2 != K:
+        raise ValueError(f"a_cat has K={K} but blocks pack K={blocks.shape[2] * 2}")
+    return _launch(_gnf4b.FMT_MXFP4, _gnf4b.OP_FWD, a_cat, blocks, scales, sizes, expert_ids, N)
+
+
+def dgrad_mxfp4_grouped(grad_out, blocks, scales, sizes, expert_ids):
+    """``grad_a[t,:] = grad_out[t,:] @ dequant_mxfp4(blocks[e(t)])`` in one launch, ``[T,K]``
+    bf16.  The reference has this only as a per-expert Python loop on the GPU
+    (kernel/mxfp4_qlora.py:105-122) and as a CPU kernel (gnf4_native/cpu_kernels.c:1386-1397)."""
+    E, N, half = blocks.shape
+    _require_cuda(grad_out, "dgrad_mxfp4_grouped",
+                  "The CPU-checkable equivalent is grad_out @ dequant_mxfp4(blocks, scales) per group.")
+    if grad_out.dtype != torch.bfloat16:
+        raise ValueError(f"dgrad_mxfp4_grouped cannot run this problem: grad_out dtype {grad_out.dtype} is not bfloat16")
+    if grad_out.shape[1] != N:
+        raise ValueError(f"grad_out has {grad_out.shape[1]} columns but the stack has N={N}")
+    return _launch(_gnf4b.FMT_MXFP4, _gnf4b.OP_DGRAD, grad_out, blocks, scales, sizes, expert_ids, half * 2)
+
+
+def dequant_stack_cuda(blocks, scales):
+    """Element decode of a whole MXFP4 stack by the CUDA library's decode routines ->
+    ``[E,N,K]`` fp32, for bit-for-bit comparison with ``mxfp4_pack_ref.dequant_mxfp4``."""
+    _require_cuda(blocks, "dequant_stack_cuda", "Use mxfp4_pack_ref.dequant_mxfp4 on CPU tensors.")
+    E, N, half = blocks.shape
+    if blocks.stride(2) != 1:
+        blocks = blocks.contiguous()
+    if scales.stride(2) != 1:
+        scales = scales.contiguous()
+    out = torch.empty(E, N, half * 2, dtype=torch.float32, device=blocks.device)
+    lib = _gnf4b.load()
+    with torch.cuda.device(blocks.device):
+        rc = lib.gnf4b_dequant(_gnf4b.FMT_MXFP4, blocks.data_ptr(), blocks.stride(0), blocks.stride(1),
+                               scales.data_ptr(), _gnf4b.S_E8M0, scales.stride(0), scales.stride(1),
+                               E, N, half * 2, out.data_ptr(),
+                               torch.cuda.current_stream(blocks.device).cuda_stream)
+    _gnf4b.check(rc, "gnf4b_dequant")
+    return out

@@ -1,0 +1,508 @@
+"""Grouped W4A16 GEMM over NF4 expert stacks on NVIDIA B200 -- the drop-in for the
+reference module of the same name (pjordanandrsn/grouped-nf4-gemm, kernel/nf4_grouped.py).
+
+Same entry points, argument meaning and error behaviour:
+
+    gemm_4bit_grouped(a_cat, B, absmax, sizes, expert_ids, ...)   -> [T, N] bf16   (ref :697-907)
+    dgrad_4bit_grouped(grad_out, B, absmax, sizes, expert_ids)    -> [T, K] bf16   (ref :1056-1121)
+
+What differs is everything below the call: no Triton, no backend detection.  Each call is
+one launch of a hand-written sm_100a kernel from ``libgnf4b.so`` (C ABI in
+``include/gnf4b.h``) that walks a device-side schedule built from ``group_offsets`` and
+``expert_ids``; the host never builds a tile table.  There is no CPU fallback: tensors that
+are not on a CUDA device raise the same taught ``RuntimeError`` as the reference
+(ref :732-738), and a missing library raises at the first launch.
+
+Helpers that other layers of the reference import from this module keep their names and
+values: ``dequant_ref``, ``repack_from_bnb``, ``build_group_tiles``, ``to_device_i32``,
+``decode_dispatch``, ``_decode_plan``, ``_prefill_block_m``, ``dgrad_eligible``,
+``_DGRAD_DEFAULT``, ``_sm_count``, ``_lut``, ``_arena``, ``_ARENAS``, ``_PinnedIndexArena``,
+``NF4_LUT``, ``BLOCKSIZE``.  The Triton-specific tuning keywords are accepted and do not
+change results.
+"""
+from __future__ import annotations
+
+import os
+
+import torch
+
+import _gnf4b
+
+# bitsandbytes / QLoRA NF4 codebook; code 7 is exactly 0.0 (ref :53-70).
+NF4_LUT = [
+    -1.0, -0.6961928009986877, -0.5250730514526367, -0.39491748809814453,
+    -0.28444138169288635, -0.18477343022823334, -0.09105003625154495, 0.0,
+    0.07958029955625534, 0.16093020141124725, 0.24611230194568634, 0.33791524171829224,
+    0.44070982933044434, 0.5626170039176941, 0.7229568362236023, 1.0,
+]
+BLOCKSIZE = 64
+
+# Product-layer hints of the reference (ref :605-606); kept so callers that consult
+# decode_dispatch() keep working.  They were measured on sm_86 and do not steer this op.
+DECODE_MIN_FUSED_BYTES = 3_000_000
+SPLITK_MIN_BLOCKS = 32
+_DGRAD_DEFAULT = (32, 64, 64, 2)
+
+_LUT_CACHE: dict = {}
+_SM_CACHE: dict = {}
+_STATUS: dict = {}
+
+
+# --------------------------------------------------------------------------- #
+# small-int transfers (capture-legal), ref :99-331
+# --------------------------------------------------------------------------- #
+class _PinnedIndexArena:
+    """Pinned host staging for the small int32 tensors a call needs (group offsets,
+    expert ids).
+
+    Two regions.  ``take`` hands out PERMANENT slices and is what a call uses while the
+    current stream is being captured into a CUDA graph: a captured host-to-device copy
+    re-reads its pinned source on every replay, so those bytes may never be reused, the
+    watermark never rewinds, and the arena refuses to grow inside a capture (allocating
+    pinned memory there breaks the capture) -- the semantics of the reference's arena
+    (ref :99-217).  Outside a capture ``stage`` cycles through a small ring of slots, each
+    guarded by an event recorded after its copy, so an eager call pays one asynchronous
+    pinned copy and no stream synchronisation.
+    """
+
+    DEFAULT_INTS = int(os.environ.get("GNF4_PIN_ARENA_INTS", 1 << 20))
+    RING_SLOTS = 64
+    RING_SLOT_INTS = 8192
+
+    def __init__(self, device, n: int | None = None):
+        self.device = device
+        self.host = torch.empty(n or self.DEFAULT_INTS, dtype=torch.int32, pin_memory=True)
+        self.off = 0
+        self._retired: list = []
+        self._ring = torch.empty(self.RING_SLOTS * self.RING_SLOT_INTS, dtype=torch.int32, pin_memory=True)
+        self._ring_evt = [None] * self.RING_SLOTS
+        self._ring_next = 0
+
+    @staticmethod
+    def _capturing() -> bool:
+        try:
+            return torch.cuda.is_current_stream_capturing()
+        except Exception:
+            return False
+
+    def take(self, n: int):
+        capturing = self._capturing()
+        if self.off + n > self.host.numel():
+            if capturing:
+                need = 2 * (self.off + n)
+                raise RuntimeError(
+                    f"grouped-nf4: the pinned index arena ({self.host.numel()} int32, {self.off} already "
+                    f"owned by this process's captures) cannot hold {n} more ints, and growing it would "
+                    "allocate pinned memory inside the capture region, which is not capturable. Slices "
+                    "taken under capture are permanent (replays re-read them): set GNF4_PIN_ARENA_INTS "
+                    f"to at least {need} ({need * 4 / 2**20:.1f} MiB pinned) or call reserve() before capturing.")
+            self._grow(self.off + n)
+        view = self.host[self.off:self.off + n]
+        self.off += n
+        return view, capturing
+
+    def _grow(self, need: int):
+        self._retired.append(self.host)          # live graphs may still read it
+        fresh = torch.empty(max(2 * self.host.numel(), need), dtype=torch.int32, pin_memory=True)
+        fresh[: self.off] = self.host[: self.off]
+        self.host = fresh
+
+    def reserve(self, n_more: int):
+        if self._capturing():
+            raise RuntimeError("reserve() inside a capture would allocate pinned memory in the region; "
+                               "call it before capturing.")
+        if self.off + n_more > self.host.numel():
+            self._grow(self.off + n_more)
+
+    def mark(self):
+        """Kept for call-site compatibility; permanence made it a no-op."""
+
+    def stage(self, n: int):
+        """A reusable pinned slot of n ints for an eager (uncaptured) call, or None when n
+        does not fit a slot."""
+        if n > self.RING_SLOT_INTS:
+            return None, -1
+        i = self._ring_next
+        self._ring_next = (i + 1) % self.RING_SLOTS
+        evt = self._ring_evt[i]
+        if evt is not None:
+            evt.synchronize()
+        return self._ring[i * self.RING_SLOT_INTS: i * self.RING_SLOT_INTS + n], i
+
+    def staged(self, slot: int):
+        if self._ring_evt[slot] is None:
+            self._ring_evt[slot] = torch.cuda.Event()
+        self._ring_evt[slot].record()
+
+
+_ARENAS: dict = {}
+
+
+def _arena(device) -> _PinnedIndexArena:
+    key = str(device)
+    if key not in _ARENAS:
+        _ARENAS[key] = _PinnedIndexArena(device)
+    return _ARENAS[key]
+
+
+def _flat_ints(seqs):
+    flat = []
+    for s in seqs:
+        if torch.is_tensor(s):
+            flat.extend(int(v) for v in s.reshape(-1).tolist())
+        else:
+            flat.extend(int(v) for v in s)
+    return flat
+
+
+def to_device_i32(seqs, device):
+    """Small host integer sequences -> one int32 device view per input, identical values
+    on every path, in ONE transfer (ref :229-331).  Under CUDA-graph capture the source is
+    a permanent slice of the pinned arena and the copy is asynchronous (a pageable build
+    synchronises, which is illegal in a capture); otherwise a recycled pinned slot."""
+    lens = [len(s) for s in seqs]
+    total = sum(lens)
+    dev = torch.device(device)
+    if total == 0:
+        return [torch.empty(0, dtype=torch.int32, device=dev) for _ in seqs]
+    if dev.type != "cuda" or not torch.cuda.is_available():
+        packed = torch.tensor(_flat_ints(seqs), dtype=torch.int32, device=dev)
+    else:
+        ar = _arena(dev)
+        vals = torch.tensor(_flat_ints(seqs), dtype=torch.int32)
+        if ar._capturing():
+            host, _ = ar.take(total)
+            host.copy_(vals)
+            packed = host.to(dev, non_blocking=True)
+        else:
+            host, slot = ar.stage(total)
+            if host is None:
+                packed = vals.to(dev)
+            else:
+                host.copy_(vals)
+                packed = host.to(dev, non_blocking=True)
+                ar.staged(slot)
+    out, o = [], 0
+    for n in lens:
+        out.append(packed[o:o + n])
+        o += n
+    return out
+
+
+def build_group_tiles(sizes, block_m: int, device):
+    """Jagged group sizes -> fixed-height M-tiles ``(row0, valid_rows, group)`` as three
+    int32 tensors on ``device`` (ref :334-362).  The CUDA kernels here do not consume this
+    table (they schedule from group offsets on the device); it stays for callers and tests
+    that import it.  ``sizes`` is never modified, including when it is a tensor."""
+    t_row0, t_rows, t_group = [], [], []
+    row = 0
+    for g, m in enumerate(sizes):
+        m = int(m)
+        for done in range(0, m, block_m):
+            t_row0.append(row + done)
+            t_rows.append(min(block_m, m - done))
+            t_group.append(g)
+        row += m
+    a, b, c = to_device_i32((t_row0, t_rows, t_group), device)
+    return a, b, c
+
+
+# --------------------------------------------------------------------------- #
+# planning helpers kept for API parity
+# --------------------------------------------------------------------------- #
+def _sm_count(device) -> int:
+    key = str(device)
+    if key not in _SM_CACHE:
+        if torch.cuda.is_available() and "cuda" in key:
+            _SM_CACHE[key] = torch.cuda.get_device_properties(device).multi_processor_count
+        else:
+            _SM_CACHE[key] = 64
+    return _SM_CACHE[key]
+
+
+def _decode_plan(N: int, K: int, T: int, sm_count: int):
+    """The reference's decode launch plan ``(BLOCK_N, num_warps, split_k)`` (ref :609-632):
+    constant (64, 2); split-K only for starved grids (programs < 2*SM), power of two up to
+    8, each split owning at least SPLITK_MIN_BLOCKS absmax blocks.  Pure function, kept so
+    integrations that consult it see the same answers; the sm_100a kernel plans for itself
+    (``gnf4b_plan_split_k``)."""
+    bn, warps = 64, 2
+    programs = T * -(-N // bn)
+    split_k = 1
+    if programs < 2 * sm_count:
+        want = -(-(4 * sm_count) // programs)
+        while split_k < want and split_k < 8:
+            split_k *= 2
+        kblocks = max(K // BLOCKSIZE, 1)
+        while split_k > 1 and kblocks // split_k < SPLITK_MIN_BLOCKS:
+            split_k //= 2
+    return bn, warps, split_k
+
+
+def decode_dispatch(N: int, K: int, T: int, sm_count: int):
+    """Product-layer hint (ref :635-649): ``("dequant",)`` below the fused-traffic floor,
+    else ``("fused", BLOCK_N, num_warps, split_k)``.  The op itself always runs fused."""
+    traffic = T * N * (K // 2 + K // 16)
+    if traffic < DECODE_MIN_FUSED_BYTES:
+        return ("dequant",)
+    return ("fused", *_decode_plan(N, K, T, sm_count))
+
+
+def _prefill_block_m(max_rows: int) -> int:
+    """M-tile height rule of the reference (ref :686-694)."""
+    for bm in (16, 32, 64):
+        if max_rows <= bm:
+            return bm
+    return 128
+
+
+def _lut(device):
+    key = str(device)
+    if key not in _LUT_CACHE:
+        _LUT_CACHE[key] = torch.tensor(NF4_LUT, dtype=torch.float32, device=device)
+    return _LUT_CACHE[key]
+
+
+def repack_from_bnb(packed_list, states, N: int, K: int):
+    """bitsandbytes per-expert ``quantize_4bit`` outputs -> ``B [E,N,K/2] u8`` and
+    ``absmax [E,N,K/64] fp32`` (ref :74-96); nested statistics are de-nested here."""
+    assert K % BLOCKSIZE == 0, f"K={K} not a multiple of blocksize {BLOCKSIZE}"
+    E, dev = len(packed_list), packed_list[0].device
+    B = torch.empty(E, N, K // 2, dtype=torch.uint8, device=dev)
+    A = torch.empty(E, N, K // BLOCKSIZE, dtype=torch.float32, device=dev)
+    for e, (q, st) in enumerate(zip(packed_list, states)):
+        B[e] = q.reshape(N, K // 2)
+        am = st.absmax
+        if getattr(st, "nested", False):
+            from bitsandbytes import functional as F
+            am = F.dequantize_blockwise(st.absmax, st.state2) + st.offset
+        A[e] = am.to(torch.float32).reshape(N, K // BLOCKSIZE)
+    return B, A
+
+
+def dequant_ref(packed_row_major: torch.Tensor, absmax: torch.Tensor, N: int, K: int):
+    """Pure-torch element decode, any device: ``w = fp32(LUT[code]) * fp32(absmax)``, element
+    2j in the HIGH nibble of byte j (ref :910-929).  The CPU-checkable counterpart of what
+    the kernels decode in registers."""
+    lut = _lut(packed_row_major.device)
+    b = packed_row_major.reshape(-1).to(torch.int64)
+    codes = torch.stack((b >> 4, b & 15), dim=1).reshape(-1)
+    am = absmax.to(torch.float32).reshape(-1).repeat_interleave(BLOCKSIZE)
+    return (lut[codes] * am).reshape(N, K)
+
+
+# --------------------------------------------------------------------------- #
+# launch plumbing shared with mxfp4_grouped
+# --------------------------------------------------------------------------- #
+def _status_word(dev):
+    key = str(dev)
+    if key not in _STATUS:
+        _STATUS[key] = torch.zeros(1, dtype=torch.int32, device=dev)
+    return _STATUS[key]
+
+
+def last_status(device) -> int:
+    """OR of the GNF4B_ST_* bits kernels on ``device`` have raised since the last call of
+    this function (synchronises).  0 = nothing skipped, no wait timed out."""
+    w = _status_word(torch.device(device))
+    v = int(w.item())
+    if v:
+        w.zero_()
+    return v
+
+
+def _group_tables(sizes, expert_ids, T: int, E: int, dev):
+    """-> (group_offsets[G+1] dev, expert_ids[G] dev, G, max_rows).  Host inputs are checked
+    and travel in one transfer; device inputs are used where they are, with no host read."""
+    ids_dev = torch.is_tensor(expert_ids) and expert_ids.is_cuda
+    sz_dev = torch.is_tensor(sizes) and sizes.is_cuda
+    if sz_dev:
+        G = int(sizes.numel())
+        max_rows = -1
+    else:
+        sz = [int(v) for v in (sizes.tolist() if torch.is_tensor(sizes) else sizes)]
+        G = len(sz)
+        assert sum(sz) == T, (sum(sz), T)
+        if any(v < 0 for v in sz):
+            raise ValueError("negative group size")
+        max_rows = max(sz) if sz else 0
+        offs = [0] * (G + 1)
+        for i, v in enumerate(sz):
+            offs[i + 1] = offs[i] + v
+    if not ids_dev:
+        ids = [int(v) for v in (expert_ids.tolist() if torch.is_tensor(expert_ids) else expert_ids)]
+        if len(ids) != G:
+            raise ValueError(f"sizes has {G} groups but expert_ids has {len(ids)}")
+        if any(v < 0 or v >= E for v in ids):
+            raise ValueError(f"expert id out of range for a stack of {E} experts")
+    else:
+        if expert_ids.numel() != G:
+            raise ValueError(f"sizes has {G} groups but expert_ids has {expert_ids.numel()}")
+    if not sz_dev and not ids_dev:
+        off_t, ids_t = to_device_i32((offs, ids), dev)
+    elif not sz_dev:
+        off_t = to_device_i32((offs,), dev)[0]
+        ids_t = expert_ids.to(torch.int32).contiguous()
+    else:
+        lib = _gnf4b.load()
+        sz_t = sizes.to(torch.int32).contiguous()
+        off_t = torch.empty(G + 1, dtype=torch.int32, device=dev)
+        _gnf4b.check(lib.gnf4b_build_offsets(sz_t.data_ptr(), G, off_t.data_ptr(),
+                                             torch.cuda.current_stream(dev).cuda_stream),
+                     "gnf4b_build_offsets")
+        ids_t = (expert_ids.to(torch.int32).contiguous() if ids_dev else to_device_i32((ids,), dev)[0])
+    return off_t, ids_t, G, max_rows
+
+
+def _launch(fmt, op, x, W, S, sizes, expert_ids, n_out, *, split_k=None, path=_gnf4b.PATH_AUTO):
+    """One grouped launch.  x [T, C] bf16/fp16, W [E, N, K/2] u8, S scales -> bf16 [T, n_out]."""
+    dev = x.device
+    E, N, half = W.shape
+    K = half * 2
+    T = x.shape[0]
+    if x.dtype == torch.bfloat16:
+        xdt = _gnf4b.X_BF16
+    elif x.dtype == torch.float16:
+        xdt = _gnf4b.X_FP16
+    else:
+        raise TypeError(f"activations must be bfloat16 or float16, got {x.dtype}")
+    if W.dtype != torch.uint8:
+        raise TypeError(f"packed weights must be uint8, got {W.dtype}")
+    if W.device != dev or S.device != dev:
+        raise ValueError("activations, packed weights and scales must live on the same device")
+    x = x.contiguous()
+    if x.data_ptr() % 16:
+        x = x.clone()
+    if W.stride(2) != 1:
+        W = W.contiguous()
+    if fmt == _gnf4b.FMT_NF4:
+        if S.dtype == torch.float32:
+            sdt = _gnf4b.S_F32
+        elif S.dtype == torch.bfloat16:
+            sdt = _gnf4b.S_BF16
+        else:
+            S, sdt = S.to(torch.float32), _gnf4b.S_F32
+    else:
+        sdt = _gnf4b.S_E8M0
+    if S.stride(2) != 1:
+        S = S.contiguous()
+    out = torch.empty(T, n_out, dtype=torch.bfloat16, device=dev)
+    if T == 0:
+        return out
+    lib = _gnf4b.load()
+    with torch.cuda.device(dev):
+        off_t, ids_t, G, max_rows = _group_tables(sizes, expert_ids, T, E, dev)
+        if G == 0:
+            return out
+        flags = path
+        if split_k is not None:
+            flags |= max(1, int(split_k)) << _gnf4b.SPLITK_SHIFT
+        need = lib.gnf4b_workspace_bytes(fmt, op, T, G, N, K, max_rows, flags)
+        ws = torch.zeros(need, dtype=torch.uint8, device=dev) if need else None
+        rc = lib.gnf4b_gemm_grouped(
+            fmt, op, x.data_ptr(), xdt, T, W.data_ptr(), W.stride(0), W.stride(1),
+            S.data_ptr(), sdt, S.stride(0), S.stride(1), off_t.data_ptr(), ids_t.data_ptr(),
+            G, E, N, K, max_rows, out.data_ptr(), ws.data_ptr() if ws is not None else None,
+            need, _status_word(dev).data_ptr(), flags, torch.cuda.current_stream(dev).cuda_stream)
+    _gnf4b.check(rc, "gnf4b_gemm_grouped")
+    return out
+
+
+def _require_cuda(t, fn_name: str, hint: str):
+    if t.device.type != "cuda":
+        raise RuntimeError(
+            f"{fn_name} runs the fused sm_100a CUDA kernel and requires CUDA tensors "
+            f"(got device '{t.device.type}'). {hint}")
+
+
+# --------------------------------------------------------------------------- #
+# public entry points
+# --------------------------------------------------------------------------- #
+def gemm_4bit_grouped(a_cat, B, absmax, sizes, expert_ids, block_m: int | None = None,
+                      decode_config: tuple | None = None, split_k: int | None = None,
+                      prefill_config: tuple | None = None, prefill_variant: int | None = None,
+                      prefill_groups: int = 1):
+    """Single-launch grouped NF4 GEMM (ref :697-907).
+
+    ``a_cat [T,K]`` bf16/fp16 rows sorted by group, ``B [E,N,K//2]`` uint8 (any expert / row
+    stride, last dimension contiguous), ``absmax [E,N,K//64]`` fp32 or bf16, ``sizes`` the
+    per-group row counts (host sequence, CPU or CUDA tensor; zero-size groups produce no
+    rows), ``expert_ids [G]`` indices into the stack handed in (list, CPU or CUDA tensor).
+    Returns ``[T,N]`` bf16 in the same row order.
+
+    ``split_k`` forces the streaming kernel's split-K factor (None = planner, 1 = off).
+    ``block_m``, ``decode_config``, ``prefill_config``, ``prefill_variant`` and
+    ``prefill_groups`` are Triton launch knobs of the reference; they are accepted and
+    ignored -- results do not depend on them.
+    """
+    E, N, _ = B.shape
+    T, K = a_cat.shape
+    _require_cuda(a_cat, "gemm_4bit_grouped",
+                  "For a CPU-checkable decode of the same NF4 bytes, use dequant_ref(packed, absmax, N, K) "
+                  "-- the pure-torch reference the kernel is pinned against.")
+    if B.shape[2] * 2 != K:
+        raise ValueError(f"a_cat has K={K} but B packs K={B.shape[2] * 2}")
+    if tuple(absmax.shape) != (E, N, K // BLOCKSIZE):
+        raise ValueError(f"absmax shape {tuple(absmax.shape)} != {(E, N, K // BLOCKSIZE)}")
+    return _launch(_gnf4b.FMT_NF4, _gnf4b.OP_FWD, a_cat, B, absmax, sizes, expert_ids, N, split_k=split_k)
+
+
+def dgrad_eligible(grad_out, B, absmax, block_k: int = 64):
+    """None if ``dgrad_4bit_grouped`` can take this problem, else the reason (ref :1034-1053)."""
+    if grad_out.dtype != torch.bfloat16:
+        return f"grad_out dtype {grad_out.dtype} is not bfloat16"
+    if BLOCKSIZE % block_k:
+        return f"BLOCK_K {block_k} does not divide the quant blocksize {BLOCKSIZE}"
+    K = B.shape[2] * 2
+    if K % block_k:
+        return f"K {K} not divisible by BLOCK_K {block_k}"
+    if absmax.shape[2] * BLOCKSIZE != K:
+        return f"absmax blocks {absmax.shape[2]} do not tile K {K} at blocksize {BLOCKSIZE}"
+    if B.numel() == 0:
+        return "packed storage is empty (evicted?)"
+    return None
+
+
+def dgrad_4bit_grouped(grad_out, B, absmax, sizes, expert_ids, config=None):
+    """``grad_a[t,:] = grad_out[t,:] @ dequant_nf4(B[e(t)])`` in one launch (ref :1056-1121).
+
+    ``grad_out [T,N]`` bf16, same stack and grouping as the forward; returns ``[T,K]`` bf16.
+    ``config`` (a Triton tile tuple in the reference) only takes part in the eligibility
+    check; the result does not depend on it."""
+    E, N, half = B.shape
+    K = half * 2
+    T = grad_out.shape[0]
+    _require_cuda(grad_out, "dgrad_4bit_grouped",
+                  "The CPU-checkable equivalent is grad_out @ dequant_ref(packed, absmax, N, K) per group.")
+    block_k = (config or _DGRAD_DEFAULT)[2]
+    why = dgrad_eligible(grad_out, B, absmax, block_k)
+    if why is not None:
+        raise ValueError(
+            f"dgrad_4bit_grouped cannot run this problem: {why}. Callers that can fall back should "
+            "check dgrad_eligible() first rather than catching this.")
+    if grad_out.shape[1] != N:
+        raise ValueError(f"grad_out has {grad_out.shape[1]} columns but the stack has N={N}")
+    return _launch(_gnf4b.FMT_NF4, _gnf4b.OP_DGRAD, grad_out, B, absmax, sizes, expert_ids, K)
+
+
+def dequant_stack_cuda(B, absmax):
+    """Element decode of a whole stack by the CUDA library's own decode routines ->
+    ``[E,N,K]`` fp32.  Exists so the kernels' decode can be compared bit for bit with
+    ``dequant_ref``."""
+    _require_cuda(B, "dequant_stack_cuda", "Use dequant_ref on CPU tensors.")
+    E, N, half = B.shape
+    if B.stride(2) != 1:
+        B = B.contiguous()
+    if absmax.dtype not in (torch.float32, torch.bfloat16):
+        absmax = absmax.to(torch.float32)
+    if absmax.stride(2) != 1:
+        absmax = absmax.contiguous()
+    sdt = _gnf4b.S_F32 if absmax.dtype == torch.float32 else _gnf4b.S_BF16
+    out = torch.empty(E, N, half * 2, dtype=torch.float32, device=B.device)
+    lib = _gnf4b.load()
+    with torch.cuda.device(B.device):
+        rc = lib.gnf4b_dequant(_gnf4b.FMT_NF4, B.data_ptr(), B.stride(0), B.stride(1), absmax.data_ptr(), sdt,
+                               absmax.stride(0), absmax.stride(1), E, N, half * 2, out.data_ptr(),
+                               torch.cuda.current_stream(B.device).cuda_stream)
+    _gnf4b.check(rc, "gnf4b_dequant")
+    return out

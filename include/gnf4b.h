@@ -1,0 +1,129 @@
+/* gnf4b.h -- C ABI of libgnf4b.so: grouped 4-bit expert GEMM for NVIDIA B200 (sm_100a).
+ *
+ * One shared library, plain pointers and sizes, no framework types.  Every
+ * pointer is a DEVICE pointer unless its comment says "host".  Every launch
+ * goes to the CUDA stream passed as `cuda_stream` (a cudaStream_t cast to
+ * void*; NULL = the legacy default stream) and returns without synchronising.
+ * Functions return 0 on success and a negative GNF4B_E* code on a contract
+ * violation; nothing aborts and no kernel traps.
+ *
+ * Each entry point names the interface of the reference project
+ * (pjordanandrsn/grouped-nf4-gemm v0.13.2, paths relative to its root) that it
+ * stands in for.
+ */
+#ifndef GNF4B_H_
+#define GNF4B_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GNF4B_ABI_VERSION 1
+
+/* weight formats */
+#define GNF4B_FMT_NF4   0   /* bitsandbytes NF4: element 2j = HIGH nibble, absmax per 64 */
+#define GNF4B_FMT_MXFP4 1   /* OCP MXFP4: element 2j = LOW nibble, e8m0 scale per 32    */
+/* operations */
+#define GNF4B_OP_FWD    0   /* out[T,N] = x[T,K] . W[e]^T   (contract over K) */
+#define GNF4B_OP_DGRAD  1   /* out[T,K] = x[T,N] . W[e]     (contract over N) */
+/* activation dtypes */
+#define GNF4B_X_BF16    0
+#define GNF4B_X_FP16    1
+/* scale dtypes */
+#define GNF4B_S_F32     0   /* NF4 absmax, fp32                                  */
+#define GNF4B_S_BF16    1   /* NF4 absmax stored as bf16 (widened exactly)       */
+#define GNF4B_S_E8M0    2   /* MXFP4 block exponent byte, value 2^(e-127)        */
+
+/* flags */
+#define GNF4B_PATH_AUTO    0u
+#define GNF4B_PATH_STREAM  1u   /* CUDA-core streaming kernel (decode-sized groups)   */
+#define GNF4B_PATH_TENSOR  2u   /* tcgen05 / TMEM kernel (prefill-sized groups)       */
+#define GNF4B_PATH_MASK    3u
+#define GNF4B_SPLITK_SHIFT 8    /* bits 8..15: forced split-K factor, 0 = planner     */
+#define GNF4B_SPLITK_MASK  0xff00u
+
+/* error codes */
+#define GNF4B_OK            0
+#define GNF4B_EINVAL       -1   /* bad enum / null pointer / negative size            */
+#define GNF4B_ESHAPE       -2   /* K not a multiple of the quant block, N<=0, ...     */
+#define GNF4B_EWORKSPACE   -3   /* workspace missing or too small                     */
+#define GNF4B_ECUDA        -4   /* a CUDA runtime call failed (see gnf4b_last_cuda_error) */
+#define GNF4B_EUNSUPPORTED -5   /* combination not built (e.g. fp16 x on the tensor path) */
+#define GNF4B_ETOOBIG      -6   /* size beyond a stated fixed maximum                 */
+
+/* bits a kernel may OR into *status_word (device int32) */
+#define GNF4B_ST_BAD_EXPERT  1  /* an expert id outside [0,E) was skipped             */
+#define GNF4B_ST_BAD_OFFSETS 2  /* group_offsets not monotone / beyond T; group skipped */
+#define GNF4B_ST_TIMEOUT     4  /* a bounded device-side wait gave up                 */
+
+int gnf4b_abi_version(void);
+const char* gnf4b_strerror(int rc);
+/* text of the last CUDA error seen by this library on the calling thread */
+const char* gnf4b_last_cuda_error(void);
+
+/* The grouped GEMM.  Stands in for the launches inside
+ *   gemm_4bit_grouped   kernel/nf4_grouped.py:697-907  (fmt NF4,  op FWD)
+ *   dgrad_4bit_grouped  kernel/nf4_grouped.py:1056-1121 (fmt NF4, op DGRAD)
+ *   gemm_mxfp4_grouped  kernel/mxfp4_grouped.py:134-172 (fmt MXFP4, op FWD)
+ * and for their Triton kernels (_gemv_nf4_grouped[_splitk], _gemm_nf4_grouped,
+ * _dgrad_nf4_grouped, _gemv_mxfp4_grouped, _gemm_mxfp4_grouped).
+ *
+ *   x            [T, K] (FWD) or [T, N] (DGRAD), row-major contiguous, rows sorted by group
+ *   W            packed nibbles, logical [E, N, K/2]; byte strides w_stride_e, w_stride_n,
+ *                last dimension contiguous.  16-byte aligned base and strides take the
+ *                TMA loader, anything else a plain-load producer (same results).
+ *   S            scales, logical [E, N, K/64] (NF4) or [E, N, K/32] (MXFP4); ELEMENT strides
+ *   group_offsets[G+1] int32, exclusive prefix sum of the group sizes (zero-size groups allowed)
+ *   expert_ids   [G] int32, index into the stack handed in (may repeat, any order)
+ *   max_rows     largest group size if the host knows it, else <= 0 (path choice only;
+ *                results do not depend on it)
+ *   out          bf16 [T, N] (FWD) or [T, K] (DGRAD)
+ *   workspace    device scratch of at least gnf4b_workspace_bytes(...) bytes (may be NULL
+ *                when that is 0); must be zero-filled once before its first use, the
+ *                kernels leave it zeroed again
+ *   status_word  optional device int32 that kernels OR GNF4B_ST_* bits into
+ */
+int gnf4b_gemm_grouped(int fmt, int op,
+                       const void* x, int x_dtype, int64_t T,
+                       const uint8_t* W, int64_t w_stride_e, int64_t w_stride_n,
+                       const void* S, int s_dtype, int64_t s_stride_e, int64_t s_stride_n,
+                       const int32_t* group_offsets, const int32_t* expert_ids,
+                       int32_t G, int32_t E, int64_t N, int64_t K, int32_t max_rows,
+                       void* out, void* workspace, size_t workspace_bytes,
+                       int32_t* status_word, uint32_t flags, void* cuda_stream);
+
+/* Scratch the call above needs for the same arguments (0 when none).  Replaces the
+ * `ws = torch.empty(sk, T, N)` split-K buffer of kernel/nf4_grouped.py:784. */
+size_t gnf4b_workspace_bytes(int fmt, int op, int64_t T, int32_t G, int64_t N, int64_t K,
+                             int32_t max_rows, uint32_t flags);
+
+/* The split-K factor the planner picks (or the forced one in `flags`), so a caller can
+ * mirror _decode_plan (kernel/nf4_grouped.py:609-632) without launching. */
+int gnf4b_plan_split_k(int fmt, int op, int64_t T, int32_t G, int64_t N, int64_t K,
+                       int32_t max_rows, uint32_t flags);
+
+/* sizes[G] (device int32) -> group_offsets[G+1] (device int32), one small kernel, no
+ * host read.  Replaces the host loop of build_group_tiles (kernel/nf4_grouped.py:334-362)
+ * when the group sizes live on the device. */
+int gnf4b_build_offsets(const int32_t* sizes, int32_t G, int32_t* group_offsets,
+                        void* cuda_stream);
+
+/* Element decode of a whole stack with the SAME device decode routines the GEMM kernels
+ * use: out_f32 [E, N, K] contiguous.  Counterpart of dequant_ref
+ * (kernel/nf4_grouped.py:910-929) and dequant_mxfp4 (kernel/mxfp4_pack_ref.py:46-70);
+ * exists so decode can be compared bit for bit. */
+int gnf4b_dequant(int fmt,
+                  const uint8_t* W, int64_t w_stride_e, int64_t w_stride_n,
+                  const void* S, int s_dtype, int64_t s_stride_e, int64_t s_stride_n,
+                  int32_t E, int64_t N, int64_t K, float* out_f32, void* cuda_stream);
+
+/* Device properties this library plans with (SM count, opt-in shared memory). */
+int gnf4b_device_info(int32_t* sm_count, int32_t* smem_optin_bytes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GNF4B_H_ */
