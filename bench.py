@@ -1,0 +1,426 @@
+#!/usr/bin/env python
+"""Benchmark of the grouped 4-bit MoE expert GEMM: microseconds per MoE layer
+(gate_up call + down call), with decode HBM GB/s or prefill TFLOP/s against the roofline.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--tokens M] [--config NAME] [--impl reference]
+
+A step is one layer pass over one batch of synthetic tokens: the grouped gate_up GEMM and
+the grouped down GEMM of one MoE layer (the GLU between them is not part of the op and is
+left out; the down GEMM's input is a fresh bf16 N(0,1) tensor of the right shape).  Every
+step uses a different layer out of ``--layers`` resident layer stacks and its own seeded
+routing, so weights come from HBM, not from L2.
+
+One JSON line is printed by rank 0:
+  value       us/layer with all inputs resident in HBM, K steps captured in one CUDA graph,
+              timed with CUDA events (max over ranks)
+  e2e         us/layer through the public Python entry points with HOST inputs: pinned
+              activations and host routing lists are copied in, the layer output is read back
+  roofline    the dominant kernel (gate_up) timed alone: algorithmic bytes or flops / time
+  cpu_baseline  the reference project's own CPU kernels (oracle/_ref) on the host cores
+
+``--impl reference`` times only that CPU path with all host threads, same metric and config.
+With --gpus N > 1 (under torchrun) the layer is expert-parallel: experts are sharded
+across ranks, tokens are dispatched and combined with NCCL all-to-all, M tokens per rank.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+for p in (str(ROOT / "grouped-nf4-gemm_b200"), str(ROOT)):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+import torch  # noqa: E402
+
+import synth  # noqa: E402
+
+BASELINE_US = {  # reference's published B200 numbers (fused Triton, gate_up + down), us/layer
+    ("qwen3_30b_a3b", 1): 185.0 + 100.0,       # decode_bs1
+    ("qwen3_30b_a3b", 2048): 1428.0 + 794.0,   # prefill_s2048
+}
+
+
+def measured_peaks():
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        d = json.loads(f.read_text())
+        return dict(hbm_gbs=d["hbm_gbs"], tflops=d["bf16_tflops"], tflops_sustained=d.get("bf16_tflops_sustained"),
+                    source="measured")
+    return dict(hbm_gbs=6650.0, tflops=1590.0, tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.rows, self.proc, self.gpu = [], None, gpu_index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        sm, smax, reasons = [], 0, set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                smax = max(smax, float(r[2]))
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            except Exception:
+                continue
+        busy = [v for v in sm if v >= 0.5 * smax] or sm
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": smax or None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- workload
+def algorithmic(shape, proj, rows, active):
+    """Bytes and flops of one grouped call (each distinct expert's weights counted once)."""
+    N, K = getattr(shape, proj)
+    if shape.fmt == "nf4":
+        wbytes = active * N * (K // 2 + (K // 64) * 4)
+    else:
+        wbytes = active * N * (K // 2 + K // 32)
+    return wbytes + 2 * rows * (K + N), 2 * rows * N * K
+
+
+def make_steps(shape, tokens, n_steps, seed, zipf=None):
+    """Per-step routing and host activations (pinned)."""
+    gen = torch.Generator().manual_seed(seed)
+    steps = []
+    for _ in range(n_steps):
+        x, idx, w = synth.routed_batch(shape, tokens, gen, zipf)
+        tok, sizes, eids, _ = synth.dispatch(idx, shape.experts)
+        a_cat = x[tok].contiguous()
+        h = torch.randn(a_cat.shape[0], shape.inter, generator=gen).to(torch.bfloat16)
+        steps.append(dict(a=a_cat.pin_memory() if torch.cuda.is_available() else a_cat,
+                          h=h.pin_memory() if torch.cuda.is_available() else h,
+                          sizes=sizes, eids=eids, rows=a_cat.shape[0], active=len(eids)))
+    return steps
+
+
+def build_layers(shape, n_layers, device, seed):
+    gen = torch.Generator().manual_seed(seed)
+    layers = []
+    for _ in range(n_layers):
+        (n1, k1), (n2, k2) = shape.gate_up, shape.down
+        if shape.fmt == "nf4":
+            gu = synth.nf4_stack(shape.experts, n1, k1, gen, device=device, fast=True)
+            dn = synth.nf4_stack(shape.experts, n2, k2, gen, device=device, fast=True)
+        else:
+            gu = synth.mxfp4_stack(shape.experts, n1, k1, gen, device=device, fast=True)
+            dn = synth.mxfp4_stack(shape.experts, n2, k2, gen, device=device, fast=True)
+        layers.append((gu, dn))
+    return layers
+
+
+def grouped(shape):
+    import mxfp4_grouped
+    import nf4_grouped
+    return nf4_grouped.gemm_4bit_grouped if shape.fmt == "nf4" else mxfp4_grouped.gemm_mxfp4_grouped
+
+
+# --------------------------------------------------------------------------- CPU arm
+def cpu_layers(shape, n_layers, seed):
+    """Small random-byte stacks for the CPU arm (its speed does not depend on the values)."""
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    out = []
+    for _ in range(n_layers):
+        pair = []
+        for (n, k) in (shape.gate_up, shape.down):
+            W = rng.integers(0, 256, size=(shape.experts, n, k // 2), dtype=np.uint8)
+            if shape.fmt == "nf4":
+                S = (rng.random(size=(shape.experts, n, k // 64), dtype=np.float32) * 0.05 + 0.01)
+            else:
+                S = rng.integers(119, 126, size=(shape.experts, n, k // 32), dtype=np.uint8)
+            pair.append((W, S))
+        out.append(pair)
+    return out
+
+
+def time_cpu(shape, tokens, steps, warmup, seed, max_rows_per_group=None, budget_s=25.0):
+    """us/layer of the reference's compiled CPU kernels (oracle/_ref) with all host threads.
+    Groups are cut to ``max_rows_per_group`` rows when the full problem would take too long
+    and the time is scaled by rows/rows_sampled (flagged in ``sample``)."""
+    import numpy as np
+    from oracle import oracle as O
+    L = O.load_ref()
+    kind = "reference"
+    if L is None:
+        raise RuntimeError("oracle/_ref is not built; run `python oracle/build.py` where the reference checkout is")
+    threads = O.host_threads()
+    n_layers = min(4, max(2, steps))
+    layers = cpu_layers(shape, n_layers, seed)
+    st = make_steps(shape, tokens, warmup + steps, seed + 1)
+    L.gnf4_pool_start(0)
+    times, scale_note = [], "full workload"
+    try:
+        for i, s in enumerate(st):
+            sizes, eids = list(s["sizes"]), list(s["eids"])
+            rows = sum(sizes)
+            if max_rows_per_group:
+                sizes = [min(v, max_rows_per_group) for v in sizes]
+            # the reference's CPU kernels take at most 512 groups per call
+            sub_rows = sum(sizes)
+            a = np.random.default_rng(i).standard_normal((sub_rows, shape.hidden), dtype=np.float32)
+            h = np.random.default_rng(i + 1).standard_normal((sub_rows, shape.inter), dtype=np.float32)
+            (Wg, Sg), (Wd, Sd) = layers[i % n_layers]
+            t0 = time.perf_counter()
+            for c0 in range(0, len(sizes), 512):
+                sz, ei = sizes[c0:c0 + 512], eids[c0:c0 + 512]
+                r0, r1 = sum(sizes[:c0]), sum(sizes[:c0 + 512])
+                O.ref_call("gemv", shape.fmt, a[r0:r1], Wg, Sg, sz, ei, threads=0)
+                O.ref_call("gemv", shape.fmt, h[r0:r1], Wd, Sd, sz, ei, threads=0)
+            dt = time.perf_counter() - t0
+            if i >= warmup:
+                times.append(dt * (rows / max(sub_rows, 1)))
+            if sub_rows != rows:
+                scale_note = (f"groups cut to <= {max_rows_per_group} rows ({sub_rows} of {rows} rows timed), "
+                              f"time extrapolated x rows/rows_timed")
+            if sum(times) > budget_s and len(times) >= 3:
+                break
+    finally:
+        L.gnf4_pool_stop()
+    us = statistics.median(times) * 1e6
+    return dict(value=us, unit="us/layer", cores=threads, kind=kind,
+                sample=f"{len(times)} layer passes, tokens={tokens}, {scale_note}; pool of {threads} threads; "
+                       f"variant {L.variant}")
+
+
+# --------------------------------------------------------------------------- GPU arm
+def run_gpu(args, shape, rank, world):
+    import nf4_grouped
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
+    torch.cuda.set_device(dev)
+    fn = grouped(shape)
+    K, W = args.steps, args.warmup
+    layers = build_layers(shape, args.layers, dev, seed=1234 + rank)
+    steps = make_steps(shape, args.tokens, K + W, seed=99 + rank)
+    dsteps = []
+    for s in steps:
+        off = [0]
+        for v in s["sizes"]:
+            off.append(off[-1] + v)
+        dsteps.append(dict(a=s["a"].to(dev), h=s["h"].to(dev),
+                           off=torch.tensor(off, dtype=torch.int32, device=dev),
+                           eids=torch.tensor(s["eids"], dtype=torch.int32, device=dev),
+                           max_rows=max(s["sizes"]) if s["sizes"] else 0))
+    torch.cuda.synchronize()
+
+    def layer_resident(i, what="both"):
+        (gu, dn), d = layers[i % args.layers], dsteps[i]
+        o = None
+        if what in ("both", "gate_up"):
+            o = fn(d["a"], gu[0], gu[1], None, d["eids"], group_offsets=d["off"], max_rows=d["max_rows"])
+        if what in ("both", "down"):
+            o = fn(d["h"], dn[0], dn[1], None, d["eids"], group_offsets=d["off"], max_rows=d["max_rows"])
+        return o
+
+    def layer_e2e(i):
+        (gu, dn), s = layers[i % args.layers], steps[i]
+        a = s["a"].to(dev, non_blocking=True)
+        fn(a, gu[0], gu[1], s["sizes"], s["eids"])
+        h = s["h"].to(dev, non_blocking=True)
+        o = fn(h, dn[0], dn[1], s["sizes"], s["eids"])
+        return o.to("cpu", non_blocking=False)
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    def capture(what):
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            layer_resident(W, what)
+        torch.cuda.current_stream().wait_stream(side)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(W, W + K):
+                layer_resident(i, what)
+        return g
+
+    def timed_replay(g, repeats):
+        out = []
+        for _ in range(repeats):
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g.replay()
+            e1.record()
+            barrier()
+            out.append(e0.elapsed_time(e1))
+        return out
+
+    for i in range(W):                       # W untimed warm-up steps
+        layer_resident(i)
+    g_layer = capture("both")
+    g_gu = capture("gate_up")
+    g_layer.replay()
+    g_gu.replay()
+    torch.cuda.synchronize()
+
+    with ClockSampler(dev.index) as clk:
+        t_layer = timed_replay(g_layer, args.repeats)
+        t_gu = timed_replay(g_gu, args.repeats)
+        # end to end through the public entry points with host inputs
+        for i in range(W):
+            layer_e2e(i)
+        e2e_t = []
+        for _ in range(max(1, args.repeats // 2)):
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(W, W + K):
+                layer_e2e(i)
+            e1.record()
+            barrier()
+            e2e_t.append(e0.elapsed_time(e1))
+    status = nf4_grouped.last_status(dev)
+
+    ms_layer = statistics.median(t_layer)
+    ms_gu = statistics.median(t_gu)
+    ms_e2e = statistics.median(e2e_t)
+    if world > 1:
+        t = torch.tensor([ms_layer, ms_gu, ms_e2e], device=dev)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms_layer, ms_gu, ms_e2e = t.tolist()
+
+    rows = [s["rows"] for s in steps[W:]]
+    act = [s["active"] for s in steps[W:]]
+    by, fl = zip(*(algorithmic(shape, "gate_up", r, a) for r, a in zip(rows, act)))
+    by_l = [algorithmic(shape, "gate_up", r, a)[0] + algorithmic(shape, "down", r, a)[0] for r, a in zip(rows, act)]
+    fl_l = [algorithmic(shape, "gate_up", r, a)[1] + algorithmic(shape, "down", r, a)[1] for r, a in zip(rows, act)]
+    peaks = measured_peaks()
+    us_gu = ms_gu * 1e3 / K
+    rows_per_group = statistics.mean(r / max(a, 1) for r, a in zip(rows, act))
+    hbm_bound = rows_per_group <= 16
+    if hbm_bound:
+        ach = statistics.mean(by) / (us_gu * 1e-6) / 1e9
+        roof = dict(bound="hbm", achieved=ach, peak=peaks["hbm_gbs"], unit="GB/s", frac=ach / peaks["hbm_gbs"])
+    else:
+        ach = statistics.mean(fl) / (us_gu * 1e-6) / 1e12
+        roof = dict(bound="tensor", achieved=ach, peak=peaks["tflops"], unit="TFLOP/s", frac=ach / peaks["tflops"])
+    roof.update(traffic=None, kernel="gate_up grouped GEMM", us_per_launch=us_gu, peak_source=peaks["source"],
+                algorithmic_bytes=statistics.mean(by), algorithmic_flops=statistics.mean(fl))
+    us_layer = ms_layer * 1e3 / K
+    us_e2e = ms_e2e * 1e3 / K
+    h2d = statistics.mean((s["a"].numel() + s["h"].numel()) * 2 + (2 * len(s["sizes"]) + 1) * 8 for s in steps[W:])
+    d2h = statistics.mean(s["rows"] * shape.hidden * 2 for s in steps[W:])
+    base = BASELINE_US.get((shape.name, args.tokens))
+    line = {
+        "metric": "grouped 4-bit MoE GEMM us/layer", "value": us_layer, "unit": "us/layer",
+        "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_layer / K, "higher_is_better": False,
+        "scaling": "weak", "vs_baseline": (us_layer / base) if base else None,
+        "dtype": "bf16 activations x 4-bit weights, fp32 accumulate", "data": "synthetic",
+        "config": {"workload": f"{shape.name} {shape.fmt} MoE layer, {args.tokens} tokens per GPU, top-{shape.top_k} of "
+                               f"{shape.experts} experts, gate_up {shape.gate_up} + down {shape.down}",
+                   "tokens": args.tokens, "layers_resident": args.layers,
+                   "l2": f"inputs larger than L2: {args.layers} layer stacks walked round-robin, fresh routing per step",
+                   "timing": f"K steps in one CUDA graph, median of {args.repeats} replays, CUDA events"},
+        "e2e": {"value": us_e2e, "unit": "us/layer", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": 2 * K,
+        "roofline": roof,
+        "layer": {"decode_gbs": statistics.mean(by_l) / (us_layer * 1e-6) / 1e9,
+                  "tflops": statistics.mean(fl_l) / (us_layer * 1e-6) / 1e12,
+                  "rows_per_active_expert": rows_per_group, "active_experts": statistics.mean(act)},
+        "clocks": clk.summary(), "device_status": status, "repeats_ms": t_layer,
+    }
+    return line
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--tokens", type=int, default=1, help="tokens per GPU per layer pass (1 = batch-1 decode)")
+    ap.add_argument("--config", default="qwen3_30b_a3b", choices=sorted(synth.CONFIGS))
+    ap.add_argument("--layers", type=int, default=16)
+    ap.add_argument("--repeats", type=int, default=7)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    shape = synth.CONFIGS[args.config]
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    cpu_cut = None if args.tokens * shape.top_k <= 2048 else 2
+
+    if args.impl == "reference":
+        if rank != 0:
+            return 0
+        cb = time_cpu(shape, args.tokens, args.steps, args.warmup, seed=7, max_rows_per_group=cpu_cut, budget_s=120.0)
+        base = BASELINE_US.get((shape.name, args.tokens))
+        print(json.dumps({
+            "impl": "reference", "metric": "grouped 4-bit MoE GEMM us/layer", "value": cb["value"], "unit": "us/layer",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": cb["value"] / 1e3,
+            "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+            "dtype": "fp32 activations x 4-bit weights, fp32 accumulate (CPU)", "data": "synthetic",
+            "config": {"workload": f"{shape.name} {shape.fmt} MoE layer, {args.tokens} tokens, top-{shape.top_k} of "
+                                   f"{shape.experts} experts, gate_up {shape.gate_up} + down {shape.down}",
+                       "tokens": args.tokens},
+            "cpu_baseline": cb,
+            "e2e": {"value": cb["value"], "unit": "us/layer", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0,
+        }))
+        return 0
+
+    if world > 1:
+        torch.distributed.init_process_group("nccl")
+    line = run_gpu(args, shape, rank, world) if world == 1 else run_gpu_ep(args, shape, rank, world)
+    if rank == 0:
+        if world == 1 and not args.no_cpu:
+            try:
+                line["cpu_baseline"] = time_cpu(shape, args.tokens, 8, 3, seed=7, max_rows_per_group=cpu_cut)
+            except Exception as e:  # the CPU leg must not cost the GPU number
+                line["cpu_baseline"] = {"value": None, "unit": "us/layer", "cores": 0, "kind": "reference",
+                                        "sample": f"unavailable: {e}"}
+        print(json.dumps(line))
+    if world > 1:
+        torch.distributed.destroy_process_group()
+    return 0
+
+
+def run_gpu_ep(args, shape, rank, world):
+    import ep_moe
+    return ep_moe.bench_ep(args, shape, rank, world, sys.modules[__name__])
+
+
+if __name__ == "__main__":
+    sys.exit(main())

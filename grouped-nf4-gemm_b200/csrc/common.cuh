@@ -87,21 +87,22 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
     return t;
 }
 
-// Every wait in these kernels is bounded: after kWaitLimitNs without progress the
-// waiter raises *abort_flag (shared memory), and every other waiter of the CTA sees it
-// and leaves too; the kernel then records GNF4B_ST_TIMEOUT and returns.
-constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
+// Every wait in these kernels is bounded: after kWaitLimitCycles SM cycles (about two
+// seconds) without progress the waiter raises *abort_flag (shared memory), every other
+// waiter of the CTA sees it and leaves too; the kernel then records GNF4B_ST_TIMEOUT and
+// returns.  The SM cycle counter is used because it is cheap to read.
+constexpr long long kWaitLimitCycles = 4000000000ll;
 
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity,
                                                   volatile int* abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = global_timer_ns();
+    const long long t0 = clock64();
     uint32_t spins = 0;
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((++spins & 63u) == 0) {
+        if ((++spins & 255u) == 0) {
             if (*abort_flag) return false;
-            if (global_timer_ns() - t0 > kWaitLimitNs) {
+            if (clock64() - t0 > kWaitLimitCycles) {
                 *abort_flag = 1;
                 return false;
             }

@@ -278,9 +278,16 @@ int gnf4b_gemm_grouped(int fmt, int op, const void* x, int x_dtype, int64_t T, c
     g.T = T; g.N = N; g.K = K; g.G = G; g.E = E; g.x_dtype = x_dtype; g.split_k = 1;
 
     if (p.path == GNF4B_PATH_TENSOR) {
-        rc = launch_tensor(fmt, op, s_dtype, g, max_rows, di.sm_count, di.smem_optin, st);
+        rc = launch_tensor(fmt, op, s_dtype, g, max_rows, di.sm_count, di.smem_optin,
+                           align_class(W, w_stride_e, w_stride_n), st);
         if (rc == GNF4B_ECUDA) return cuda_fail(cudaGetLastError(), "tensor kernel launch");
-        return rc;
+        // A forward the tensor kernel declines (e.g. fp16 activations) still has a CUDA
+        // kernel that takes it when the caller left the choice to the planner.
+        const bool may_stream = rc == GNF4B_EUNSUPPORTED && op == GNF4B_OP_FWD &&
+                                (flags & GNF4B_PATH_MASK) == GNF4B_PATH_AUTO;
+        if (!may_stream) return rc;
+        rc = make_plan(fmt, op, T, G, N, K, max_rows, (flags & ~GNF4B_PATH_MASK) | GNF4B_PATH_STREAM, di, &p);
+        if (rc) return rc;
     }
 
     if (p.split_k > 1) {

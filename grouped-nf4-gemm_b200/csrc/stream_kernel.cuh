@@ -1,9 +1,10 @@
 // Streaming (CUDA-core) grouped GEMM for decode-sized groups.
 //
-// One persistent CTA per SM.  Warp 8 is the producer: it walks this CTA's contiguous
-// range of work items and streams each item's packed rows from HBM into an 8-stage
-// shared-memory ring with 1-D bulk copies (TMA engine) counted on mbarriers, and stages
-// the block scales beside them.  Warps 0..7 are consumers: consumer w owns weight row
+// One persistent CTA per SM.  Warps 8..11 are producers: they walk this CTA's contiguous
+// range of work items and stream each item's packed rows from HBM into an 8-stage
+// shared-memory ring with 1-D bulk copies (TMA engine) counted on mbarriers, and stage
+// the block scales beside them.  Stage number q belongs to producer warp q % 4, so four
+// global-memory latencies of the scale loads are in flight at once.  Warps 0..7 are consumers: consumer w owns weight row
 // (tile*8 + w); its lanes split the row into 16-byte units (32 elements), decode each
 // byte through a bank-conflict-free 256-entry pair table, multiply-accumulate in fp32
 // against the activation rows, apply the block scale once per unit, and reduce with
@@ -22,7 +23,8 @@
 namespace gnf4b {
 
 constexpr int kSConsumerWarps = 8;
-constexpr int kSThreads = (kSConsumerWarps + 1) * 32;
+constexpr int kSProducerWarps = 4;
+constexpr int kSThreads = (kSConsumerWarps + kSProducerWarps) * 32;
 constexpr int kSTileN = 8;              // weight rows per stage (one per consumer warp)
 constexpr int kSRowPitch = 1024;        // bytes of one row slot in a stage
 constexpr int kSStages = 8;
@@ -146,9 +148,10 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_gemm_kernel(const StreamA
     const int scales_per_chunk = a.chunk_bytes * 2 / (int)scale_blk;
     const int64_t row_bytes = a.g.K / 2;
 
-    if (warp == kSConsumerWarps) {
-        // ------------------------------------------------------------ producer
-        uint32_t stage = 0, phase = 0;
+    if (warp >= kSConsumerWarps) {
+        // ------------------------------------------------------------ producers
+        const uint32_t pw = (uint32_t)(warp - kSConsumerWarps);
+        uint32_t stage = 0, phase = 0, seq = 0;
         bool poisoned = false;
         for (int64_t item = item_lo; item < item_hi; ++item) {
             const StreamItem it = stream_decode_item(a, item);
@@ -159,9 +162,10 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_gemm_kernel(const StreamA
             const int n_valid = min(kSTileN, (int)(a.g.N - n0));
             for (int rc = 0; rc < row_chunks; ++rc) {
                 for (int c = it.c0; c < it.c1; ++c) {
-                    if (!poisoned && !mbar_wait_bounded(empty_bar + stage, phase ^ 1, abort_flag))
+                    const bool mine = (seq++ % kSProducerWarps) == pw;
+                    if (mine && !poisoned && !mbar_wait_bounded(empty_bar + stage, phase ^ 1, abort_flag))
                         poisoned = true;
-                    if (!poisoned) {
+                    if (mine && !poisoned) {
                         uint8_t* st = ring + stage * kSStageBytes;
                         float* st_sc = reinterpret_cast<float*>(st + kSTileN * kSRowPitch);
                         const int64_t boff = (int64_t)c * a.chunk_bytes;

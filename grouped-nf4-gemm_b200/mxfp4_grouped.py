@@ -35,12 +35,14 @@ def _lut(device):
 
 
 def gemm_mxfp4_grouped(a_cat, blocks, scales, sizes, expert_ids,
-                       block_m: int | None = None, prefill_variant: int | None = None):
+                       block_m: int | None = None, prefill_variant: int | None = None, *,
+                       group_offsets=None, max_rows=None, path: int = 0):
     """Single-launch grouped MXFP4 GEMM (ref :134-172).  ``a_cat [T,K]`` bf16/fp16 rows
     sorted by group; ``blocks [E,N,K//2]`` uint8; ``scales [E,N,K//32]`` uint8 (e8m0);
     ``sizes`` per-group row counts; ``expert_ids [G]`` list / CPU / CUDA int tensor.
     Returns ``[T,N]`` bf16 in the same row order.  ``block_m`` and ``prefill_variant`` are
-    Triton knobs of the reference, accepted and ignored."""
+    Triton knobs of the reference, accepted and ignored.  ``group_offsets`` / ``max_rows`` /
+    ``path`` are the keyword-only additions described at ``nf4_grouped.gemm_4bit_grouped``."""
     E, N, _ = blocks.shape
     T, K = a_cat.shape
     assert scales.shape == (E, N, K // MX_BLOCK), (scales.shape, (E, N, K // MX_BLOCK))
@@ -50,10 +52,11 @@ def gemm_mxfp4_grouped(a_cat, blocks, scales, sizes, expert_ids,
                   "mxfp4_pack_ref.dequant_mxfp4(blocks, scales).")
     if blocks.shape[2] * 2 != K:
         raise ValueError(f"a_cat has K={K} but blocks pack K={blocks.shape[2] * 2}")
-    return _launch(_gnf4b.FMT_MXFP4, _gnf4b.OP_FWD, a_cat, blocks, scales, sizes, expert_ids, N)
+    return _launch(_gnf4b.FMT_MXFP4, _gnf4b.OP_FWD, a_cat, blocks, scales, sizes, expert_ids, N,
+                   group_offsets=group_offsets, max_rows=max_rows, path=path)
 
 
-def dgrad_mxfp4_grouped(grad_out, blocks, scales, sizes, expert_ids):
+def dgrad_mxfp4_grouped(grad_out, blocks, scales, sizes, expert_ids, *, group_offsets=None, max_rows=None):
     """``grad_a[t,:] = grad_out[t,:] @ dequant_mxfp4(blocks[e(t)])`` in one launch, ``[T,K]``
     bf16.  The reference has this only as a per-expert Python loop on the GPU
     (kernel/mxfp4_qlora.py:105-122) and as a CPU kernel (gnf4_native/cpu_kernels.c:1386-1397)."""
@@ -64,7 +67,8 @@ def dgrad_mxfp4_grouped(grad_out, blocks, scales, sizes, expert_ids):
         raise ValueError(f"dgrad_mxfp4_grouped cannot run this problem: grad_out dtype {grad_out.dtype} is not bfloat16")
     if grad_out.shape[1] != N:
         raise ValueError(f"grad_out has {grad_out.shape[1]} columns but the stack has N={N}")
-    return _launch(_gnf4b.FMT_MXFP4, _gnf4b.OP_DGRAD, grad_out, blocks, scales, sizes, expert_ids, half * 2)
+    return _launch(_gnf4b.FMT_MXFP4, _gnf4b.OP_DGRAD, grad_out, blocks, scales, sizes, expert_ids, half * 2,
+                   group_offsets=group_offsets, max_rows=max_rows)
 
 
 def dequant_stack_cuda(blocks, scales):

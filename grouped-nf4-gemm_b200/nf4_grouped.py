@@ -295,6 +295,9 @@ def dequant_ref(packed_row_major: torch.Tensor, absmax: torch.Tensor, N: int, K:
 # launch plumbing shared with mxfp4_grouped
 # --------------------------------------------------------------------------- #
 def _status_word(dev):
+    dev = torch.device(dev)
+    if dev.type == "cuda" and dev.index is None:
+        dev = torch.device("cuda", torch.cuda.current_device())
     key = str(dev)
     if key not in _STATUS:
         _STATUS[key] = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -311,10 +314,20 @@ def last_status(device) -> int:
     return v
 
 
-def _group_tables(sizes, expert_ids, T: int, E: int, dev):
+def _group_tables(sizes, expert_ids, T: int, E: int, dev, group_offsets=None, max_rows=None):
     """-> (group_offsets[G+1] dev, expert_ids[G] dev, G, max_rows).  Host inputs are checked
     and travel in one transfer; device inputs are used where they are, with no host read."""
     ids_dev = torch.is_tensor(expert_ids) and expert_ids.is_cuda
+    if group_offsets is not None:
+        # caller-built device prefix sum: nothing to transfer, nothing to read back
+        if not (torch.is_tensor(group_offsets) and group_offsets.is_cuda and group_offsets.dtype == torch.int32):
+            raise TypeError("group_offsets must be a CUDA int32 tensor of G+1 entries")
+        G = int(group_offsets.numel()) - 1
+        ids_t = (expert_ids.to(torch.int32).contiguous() if ids_dev
+                 else to_device_i32(([int(v) for v in expert_ids],), dev)[0])
+        if ids_t.numel() != G:
+            raise ValueError(f"group_offsets has {G} groups but expert_ids has {ids_t.numel()}")
+        return group_offsets.contiguous(), ids_t, G, int(max_rows) if max_rows else -1
     sz_dev = torch.is_tensor(sizes) and sizes.is_cuda
     if sz_dev:
         G = int(sizes.numel())
@@ -354,7 +367,8 @@ def _group_tables(sizes, expert_ids, T: int, E: int, dev):
     return off_t, ids_t, G, max_rows
 
 
-def _launch(fmt, op, x, W, S, sizes, expert_ids, n_out, *, split_k=None, path=_gnf4b.PATH_AUTO):
+def _launch(fmt, op, x, W, S, sizes, expert_ids, n_out, *, split_k=None, path=_gnf4b.PATH_AUTO,
+            group_offsets=None, max_rows=None):
     """One grouped launch.  x [T, C] bf16/fp16, W [E, N, K/2] u8, S scales -> bf16 [T, n_out]."""
     dev = x.device
     E, N, half = W.shape
@@ -391,7 +405,7 @@ def _launch(fmt, op, x, W, S, sizes, expert_ids, n_out, *, split_k=None, path=_g
         return out
     lib = _gnf4b.load()
     with torch.cuda.device(dev):
-        off_t, ids_t, G, max_rows = _group_tables(sizes, expert_ids, T, E, dev)
+        off_t, ids_t, G, max_rows = _group_tables(sizes, expert_ids, T, E, dev, group_offsets, max_rows)
         if G == 0:
             return out
         flags = path
@@ -421,7 +435,7 @@ def _require_cuda(t, fn_name: str, hint: str):
 def gemm_4bit_grouped(a_cat, B, absmax, sizes, expert_ids, block_m: int | None = None,
                       decode_config: tuple | None = None, split_k: int | None = None,
                       prefill_config: tuple | None = None, prefill_variant: int | None = None,
-                      prefill_groups: int = 1):
+                      prefill_groups: int = 1, *, group_offsets=None, max_rows=None, path: int = 0):
     """Single-launch grouped NF4 GEMM (ref :697-907).
 
     ``a_cat [T,K]`` bf16/fp16 rows sorted by group, ``B [E,N,K//2]`` uint8 (any expert / row
@@ -434,6 +448,12 @@ def gemm_4bit_grouped(a_cat, B, absmax, sizes, expert_ids, block_m: int | None =
     ``block_m``, ``decode_config``, ``prefill_config``, ``prefill_variant`` and
     ``prefill_groups`` are Triton launch knobs of the reference; they are accepted and
     ignored -- results do not depend on them.
+
+    Additions (keyword only): ``group_offsets`` -- a CUDA int32 ``[G+1]`` exclusive prefix sum
+    of the group sizes; when given, ``sizes`` is not read at all, nothing is copied to the
+    device and the call never synchronises (routing can change under CUDA-graph replay).
+    ``max_rows`` -- the largest group size if the caller knows it (a path hint only).
+    ``path`` -- 0 planner, 1 streaming kernel, 2 tensor-core kernel (ablation).
     """
     E, N, _ = B.shape
     T, K = a_cat.shape
@@ -444,7 +464,8 @@ def gemm_4bit_grouped(a_cat, B, absmax, sizes, expert_ids, block_m: int | None =
         raise ValueError(f"a_cat has K={K} but B packs K={B.shape[2] * 2}")
     if tuple(absmax.shape) != (E, N, K // BLOCKSIZE):
         raise ValueError(f"absmax shape {tuple(absmax.shape)} != {(E, N, K // BLOCKSIZE)}")
-    return _launch(_gnf4b.FMT_NF4, _gnf4b.OP_FWD, a_cat, B, absmax, sizes, expert_ids, N, split_k=split_k)
+    return _launch(_gnf4b.FMT_NF4, _gnf4b.OP_FWD, a_cat, B, absmax, sizes, expert_ids, N, split_k=split_k,
+                   group_offsets=group_offsets, max_rows=max_rows, path=path)
 
 
 def dgrad_eligible(grad_out, B, absmax, block_k: int = 64):
@@ -463,7 +484,8 @@ def dgrad_eligible(grad_out, B, absmax, block_k: int = 64):
     return None
 
 
-def dgrad_4bit_grouped(grad_out, B, absmax, sizes, expert_ids, config=None):
+def dgrad_4bit_grouped(grad_out, B, absmax, sizes, expert_ids, config=None, *, group_offsets=None,
+                       max_rows=None):
     """``grad_a[t,:] = grad_out[t,:] @ dequant_nf4(B[e(t)])`` in one launch (ref :1056-1121).
 
     ``grad_out [T,N]`` bf16, same stack and grouping as the forward; returns ``[T,K]`` bf16.
@@ -482,7 +504,8 @@ def dgrad_4bit_grouped(grad_out, B, absmax, sizes, expert_ids, config=None):
             "check dgrad_eligible() first rather than catching this.")
     if grad_out.shape[1] != N:
         raise ValueError(f"grad_out has {grad_out.shape[1]} columns but the stack has N={N}")
-    return _launch(_gnf4b.FMT_NF4, _gnf4b.OP_DGRAD, grad_out, B, absmax, sizes, expert_ids, K)
+    return _launch(_gnf4b.FMT_NF4, _gnf4b.OP_DGRAD, grad_out, B, absmax, sizes, expert_ids, K,
+                   group_offsets=group_offsets, max_rows=max_rows)
 
 
 def dequant_stack_cuda(B, absmax):

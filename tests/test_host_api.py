@@ -1,0 +1,141 @@
+"""Host-side behaviour of the drop-in modules that needs no GPU: importability, the
+planning helpers' values (pinned to the reference's answers), error behaviour, and that
+the C-ABI library loads and exports every symbol the header declares."""
+import ctypes
+import json
+import re
+from pathlib import Path
+
+import pytest
+import torch
+
+import _gnf4b
+import mxfp4_grouped
+import nf4_grouped
+from mxfp4_pack_ref import dequant_mxfp4, quantize_pack_mxfp4
+from nf4_pack_ref import make_stack
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def test_modules_import_without_gpu_and_export_reference_names():
+    for name in ("gemm_4bit_grouped", "dgrad_4bit_grouped", "dgrad_eligible", "dequant_ref", "repack_from_bnb",
+                 "build_group_tiles", "to_device_i32", "decode_dispatch", "_decode_plan", "_prefill_block_m",
+                 "_sm_count", "_DGRAD_DEFAULT", "_lut", "_arena", "_ARENAS", "_PinnedIndexArena", "NF4_LUT",
+                 "BLOCKSIZE", "DECODE_MIN_FUSED_BYTES", "SPLITK_MIN_BLOCKS"):
+        assert hasattr(nf4_grouped, name), name
+    for name in ("gemm_mxfp4_grouped", "FP4_VALUES", "MX_BLOCK", "E8M0_BIAS", "build_group_tiles", "_prefill_block_m"):
+        assert hasattr(mxfp4_grouped, name), name
+
+
+def test_constants_and_plans_match_reference(golden_dir):
+    rec = json.loads((golden_dir / "plans.json").read_text())
+    c = rec["constants"]
+    assert nf4_grouped.NF4_LUT == c["NF4_LUT"] and nf4_grouped.BLOCKSIZE == c["BLOCKSIZE"]
+    assert mxfp4_grouped.FP4_VALUES == c["FP4_VALUES"] and mxfp4_grouped.MX_BLOCK == c["MX_BLOCK"]
+    assert mxfp4_grouped.E8M0_BIAS == c["E8M0_BIAS"]
+    assert nf4_grouped.DECODE_MIN_FUSED_BYTES == c["DECODE_MIN_FUSED_BYTES"]
+    assert nf4_grouped.SPLITK_MIN_BLOCKS == c["SPLITK_MIN_BLOCKS"]
+    assert list(nf4_grouped._DGRAD_DEFAULT) == c["DGRAD_DEFAULT"]
+    for args, want in rec["decode_plan"]:
+        assert list(nf4_grouped._decode_plan(*args)) == want, args
+    for args, want in rec["decode_dispatch"]:
+        assert list(nf4_grouped.decode_dispatch(*args)) == want, args
+    for m, want in rec["prefill_block_m"]:
+        assert nf4_grouped._prefill_block_m(m) == want
+    for sizes, bm, r0, rows, grp in rec["group_tiles"]:
+        a, b, c_ = nf4_grouped.build_group_tiles(sizes, bm, "cpu")
+        assert (a.tolist(), b.tolist(), c_.tolist()) == (r0, rows, grp)
+        assert a.dtype == torch.int32
+
+
+def test_build_group_tiles_does_not_mutate_tensor_sizes():
+    t = torch.tensor([3, 2, 0, 5], dtype=torch.int32)
+    nf4_grouped.build_group_tiles(t, 2, "cpu")
+    nf4_grouped.build_group_tiles(t, 2, "cpu")
+    assert t.tolist() == [3, 2, 0, 5]
+
+
+def test_dequant_ref_matches_golden(golden_dir):
+    import numpy as np
+    g = np.load(golden_dir / "decode.npz")
+    B = torch.from_numpy(g["nf4_packed"])
+    am = torch.from_numpy(g["nf4_absmax"])
+    w = nf4_grouped.dequant_ref(B, am, *B.shape[:1], B.shape[1] * 2)
+    assert np.array_equal(w.view(torch.int32).numpy().view(np.uint32), g["nf4_w_bits"])
+    B2, S2 = torch.from_numpy(g["mx_packed"]), torch.from_numpy(g["mx_scales"])
+    w2 = dequant_mxfp4(B2.reshape(B2.shape[0], -1, 16), S2)
+    assert np.array_equal(w2.view(torch.int32).numpy().view(np.uint32), g["mx_w_bits"])
+
+
+def test_pack_round_trip():
+    B, A = make_stack(2, 16, 128, seed=3)
+    w = nf4_grouped.dequant_ref(B[0], A[0], 16, 128)
+    assert w.shape == (16, 128) and torch.isfinite(w).all()
+    blocks, scales = quantize_pack_mxfp4(torch.randn(8, 64))
+    assert blocks.shape == (8, 2, 16) and scales.shape == (8, 2)
+    w2 = dequant_mxfp4(blocks, scales)
+    b2, s2 = quantize_pack_mxfp4(w2)          # decoded values re-quantise to the same bytes
+    assert torch.equal(dequant_mxfp4(b2, s2), w2)
+
+
+def test_cpu_tensors_are_refused_with_the_taught_error():
+    B, A = make_stack(2, 16, 64)
+    a = torch.randn(2, 64, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="requires CUDA tensors.*dequant_ref"):
+        nf4_grouped.gemm_4bit_grouped(a, B, A, [1, 1], [0, 1])
+    with pytest.raises(RuntimeError, match="requires CUDA tensors"):
+        nf4_grouped.dgrad_4bit_grouped(torch.randn(2, 16, dtype=torch.bfloat16), B, A, [1, 1], [0, 1])
+    blocks, scales = quantize_pack_mxfp4(torch.randn(1, 16, 64))
+    with pytest.raises(RuntimeError, match="requires CUDA tensors.*dequant_mxfp4"):
+        mxfp4_grouped.gemm_mxfp4_grouped(a, blocks.reshape(1, 16, 32), scales, [2], [0])
+
+
+def test_dgrad_eligibility_rules():
+    B, A = make_stack(2, 16, 128)
+    go = torch.randn(3, 16, dtype=torch.bfloat16)
+    assert nf4_grouped.dgrad_eligible(go, B, A) is None
+    assert "bfloat16" in nf4_grouped.dgrad_eligible(go.to(torch.float16), B, A)
+    assert "does not divide" in nf4_grouped.dgrad_eligible(go, B, A, block_k=48)
+    assert "do not tile" in nf4_grouped.dgrad_eligible(go, B, A[:, :, :1])
+    assert "empty" in nf4_grouped.dgrad_eligible(go, B[:0], A)
+
+
+def test_to_device_i32_cpu_path_keeps_values_and_order():
+    a, b, c = nf4_grouped.to_device_i32(([1, 2, 3], [], torch.tensor([7, 8])), "cpu")
+    assert a.tolist() == [1, 2, 3] and b.numel() == 0 and c.tolist() == [7, 8]
+    assert a.dtype == torch.int32
+
+
+def test_header_symbols_are_exported_by_the_built_library():
+    """include/gnf4b.h is the contract: the loader's EXPORTS list must name every function
+    it declares, and the built library must export each one (no compute call here)."""
+    header = (ROOT / "include" / "gnf4b.h").read_text()
+    declared = set(re.findall(r"\b(gnf4b_[a-z0-9_]+)\s*\(", header))
+    assert declared == set(_gnf4b.EXPORTS), declared ^ set(_gnf4b.EXPORTS)
+    if not _gnf4b.LIB_PATH.exists():
+        _gnf4b.build()
+    lib = ctypes.CDLL(str(_gnf4b.LIB_PATH))
+    for sym in declared:
+        assert hasattr(lib, sym), sym
+    lib.gnf4b_abi_version.restype = ctypes.c_int
+    assert lib.gnf4b_abi_version() == 1
+    lib.gnf4b_strerror.restype = ctypes.c_char_p
+    assert b"workspace" in lib.gnf4b_strerror(-3)
+
+
+def test_c_abi_rejects_contract_violations_without_a_gpu():
+    if not _gnf4b.LIB_PATH.exists():
+        _gnf4b.build()
+    lib = _gnf4b.load()
+    # K not a multiple of 64 for NF4 -> ESHAPE, before any CUDA call
+    rc = lib.gnf4b_gemm_grouped(0, 0, None, 0, 4, None, 0, 0, None, 0, 0, 0, None, None, 1, 1, 16, 96, 1,
+                                None, None, 0, None, 0, None)
+    assert rc == -2
+    rc = lib.gnf4b_gemm_grouped(7, 0, None, 0, 4, None, 0, 0, None, 0, 0, 0, None, None, 1, 1, 16, 128, 1,
+                                None, None, 0, None, 0, None)
+    assert rc == -1
+    with pytest.raises(ValueError):
+        _gnf4b.check(-2, "x")
+    with pytest.raises(RuntimeError):
+        _gnf4b.check(-5, "x")
