@@ -59,6 +59,7 @@ struct Plan {
     int rows_cap = 1;
     int a_units_pad = 32;
     int au = 0;
+    int g_cache = 0;
     int64_t n_tiles = 0;
     size_t counters_bytes = 0;
     size_t ws_bytes = 0;
@@ -118,14 +119,18 @@ static int make_plan(int fmt, int op, int64_t T, int32_t G, int64_t N, int64_t K
     p->chunks_per_split = (int)ceil_div(p->n_chunks, S);
     p->split_k = (int)ceil_div(p->n_chunks, p->chunks_per_split);   // no empty splits
     p->a_units_pad = (int)round_up(K / 32, 32);
-    const int64_t fixed = (int64_t)kSTableBytes + (int64_t)kSStages * kSStageBytes + 256;
+    // the first g_cache groups' offsets and expert ids live in shared memory
+    p->g_cache = (int)std::min<int64_t>(G, 1024);
+    const int64_t fixed = (int64_t)kSTableBytes + (int64_t)kSStages * kSStageBytes + 256 +
+                          (int64_t)(2 * p->g_cache + 1) * 4;
     const int64_t per_row = (int64_t)p->a_units_pad * 128;
     int64_t cap = (di.smem_optin - fixed) / per_row;
     if (cap < 1) return GNF4B_EUNSUPPORTED;
     cap = std::min<int64_t>(cap, kSRowsMax);
     if (max_rows > 0) cap = std::min<int64_t>(cap, max_rows);
     p->rows_cap = (int)cap;
-    p->au = (chunk == kSRowPitch) ? (K <= 2048 ? 2 : (K <= 3072 ? 3 : 0)) : 0;
+    // decode specialisation: the host knows every group has at most one row, one K pass
+    p->au = (max_rows == 1 && p->split_k == 1 && chunk == kSRowPitch) ? (K <= 2048 ? 2 : (K <= 3072 ? 3 : 0)) : 0;
     if (p->split_k > 1) {
         p->counters_bytes = (size_t)round_up((int64_t)G * p->n_tiles * 4, 256);
         p->ws_bytes = (size_t)p->split_k * (size_t)T * (size_t)N * 4;
@@ -305,8 +310,9 @@ int gnf4b_gemm_grouped(int fmt, int op, const void* x, int x_dtype, int64_t T, c
     sa.rows_cap = p.rows_cap;
     sa.a_units_pad = p.a_units_pad;
     sa.w_align = align_class(W, w_stride_e, w_stride_n);
+    sa.g_cache = p.g_cache;
     sa.total_items = (int64_t)G * p.n_tiles * p.split_k;
-    const size_t smem = stream_smem_bytes(p.rows_cap, p.a_units_pad);
+    const size_t smem = stream_smem_bytes(p.rows_cap, p.a_units_pad, p.g_cache);
     const int grid = (int)std::min<int64_t>(di.sm_count, sa.total_items);
     cudaError_t e;
     if (fmt == GNF4B_FMT_NF4 && s_dtype == GNF4B_S_F32)

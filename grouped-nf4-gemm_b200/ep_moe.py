@@ -1,0 +1,261 @@
+"""Expert-parallel MoE layer around the grouped 4-bit GEMM (one process per GPU).
+
+The reference project is single-GPU; its 128- and 256-expert configurations are sharded
+here the way its routing producers lay tokens out (stable sort of token-expert pairs by
+expert, ``kernel/mxfp4_qlora.py:294-329``), with one exchange each way:
+
+  rank r owns experts [r*E/W, (r+1)*E/W) as a contiguous slice of every stack;
+  1. top-k ids per token -> stable sort of the pairs by global expert id (= by destination
+     rank, then local expert), per-(rank, expert) counts;
+  2. counts exchanged with all_to_all_single (int32 [W * E/W]) -> receive splits and the
+     local group sizes;
+  3. DISPATCH: all_to_all_single of the bf16 hidden rows (they land in this GPU's HBM
+     before any kernel reads them);
+  4. received rows regrouped expert-major, then grouped gate_up -> GLU -> grouped down,
+     each ONE launch over all local experts;
+  5. COMBINE: the reverse all_to_all_single of the bf16 output rows;
+  6. un-sort and routing-weight sum in fp32.
+
+The collectives are NCCL over NVLink/NVSwitch on GPUs and gloo in the CPU tests; the GEMM is
+injectable (``grouped_fn``) so the exchange logic can be tested on CPU ranks against the
+oracle.  There is no TMA multicast anywhere on this path.
+"""
+from __future__ import annotations
+
+import statistics
+import time
+
+import torch
+import torch.distributed as dist
+
+
+def silu_glu(gu: torch.Tensor) -> torch.Tensor:
+    """silu(gate) * up with gate = first half, up = second half of the gate_up output
+    (the split of the reference's offload decode, bench/phase3/offload_decode_235b.py:232-233)."""
+    h = gu.shape[1] // 2
+    return (torch.nn.functional.silu(gu[:, :h].float()) * gu[:, h:].float()).to(gu.dtype)
+
+
+def plan_dispatch(idx: torch.Tensor, n_experts: int, world: int):
+    """Routing ids [M, k] (global expert ids) -> (order [P], tok_of_pair [P], counts [W, E/W]).
+    ``order`` is the stable argsort of the flattened ids, so pairs are grouped by destination
+    rank, then by local expert, and keep token order inside an expert."""
+    k = idx.shape[1]
+    flat = idx.reshape(-1)
+    order = torch.argsort(flat, stable=True)
+    counts = torch.bincount(flat, minlength=n_experts).reshape(world, n_experts // world)
+    return order, order // k, counts
+
+
+def regroup_index(recv_counts: torch.Tensor):
+    """recv_counts [W, E_local]: rows arrive source-major (source rank, then local expert).
+    Returns (perm, sizes): ``recv[perm]`` is expert-major (expert, then source rank, token
+    order kept) and ``sizes[e]`` the rows of local expert e."""
+    W, E = recv_counts.shape
+    rc = recv_counts.to(torch.int64)
+    start = (torch.cumsum(rc.reshape(-1), 0) - rc.reshape(-1)).reshape(W, E)   # block starts, source-major
+    blk_start = start.t().reshape(-1)                                         # expert-major block order
+    blk_len = rc.t().reshape(-1)
+    total = int(blk_len.sum())
+    if total == 0:
+        return torch.empty(0, dtype=torch.int64, device=rc.device), rc.sum(0)
+    within = torch.arange(total, device=rc.device) - torch.repeat_interleave(torch.cumsum(blk_len, 0) - blk_len, blk_len)
+    perm = torch.repeat_interleave(blk_start, blk_len) + within
+    return perm, rc.sum(0)
+
+
+class EPGroupedMoE:
+    """One expert-parallel MoE layer.  ``gate_up`` / ``down`` are this rank's shards
+    ``(W [E/W, N, K/2] u8, S scales)``; ``grouped_fn(a_cat, W, S, sizes, expert_ids)`` is the
+    grouped GEMM (the CUDA op by default)."""
+
+    def __init__(self, n_experts: int, gate_up, down, group=None, grouped_fn=None, fmt: str = "nf4"):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.n_experts = n_experts
+        self.e_local = n_experts // self.world
+        assert self.e_local * self.world == n_experts, "experts must divide evenly over the ranks"
+        self.gate_up, self.down = gate_up, down
+        if grouped_fn is None:
+            if fmt == "nf4":
+                from nf4_grouped import gemm_4bit_grouped as grouped_fn
+            else:
+                from mxfp4_grouped import gemm_mxfp4_grouped as grouped_fn
+        self.grouped_fn = grouped_fn
+        self.timers = None           # set to a dict of CUDA-event lists to get a phase breakdown
+        self.last_rows = 0
+
+    # -- helpers ---------------------------------------------------------------
+    def _a2a(self, out, inp, out_splits, in_splits):
+        if self.world == 1:
+            out.copy_(inp)
+        else:
+            dist.all_to_all_single(out, inp, out_splits, in_splits, group=self.group)
+
+    def _mark(self, name):
+        if self.timers is not None and torch.cuda.is_available():
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            self.timers.setdefault(name, []).append(e)
+
+    # -- the layer ---------------------------------------------------------------
+    def forward(self, hidden: torch.Tensor, idx: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+        """hidden [M, H] bf16, idx [M, k] global expert ids, weights [M, k] fp32 -> [M, H] bf16."""
+        W, El = self.world, self.e_local
+        dev = hidden.device
+        self._mark("start")
+        order, tok, counts = plan_dispatch(idx, self.n_experts, W)
+        counts32 = counts.to(torch.int32).contiguous()
+        recv_counts = torch.empty_like(counts32)
+        self._a2a(recv_counts.reshape(-1), counts32.reshape(-1), None, None)
+        # the exchange needs its split sizes on the host: one small read per layer
+        both = torch.stack((counts32.sum(1), recv_counts.sum(1))).tolist()
+        send_splits, recv_splits = both
+        send = hidden[tok]
+        recv = torch.empty(sum(recv_splits), hidden.shape[1], dtype=hidden.dtype, device=dev)
+        self._a2a(recv, send, recv_splits, send_splits)
+        self._mark("dispatch")
+        perm, sizes = regroup_index(recv_counts)
+        a_cat = recv[perm]
+        sizes_l = sizes.tolist()
+        self.last_rows = int(a_cat.shape[0])
+        eids = list(range(El))
+        gu = self.grouped_fn(a_cat, self.gate_up[0], self.gate_up[1], sizes_l, eids)
+        self._mark("gate_up")
+        h = silu_glu(gu)
+        self._mark("glu")
+        y = self.grouped_fn(h, self.down[0], self.down[1], sizes_l, eids)
+        self._mark("down")
+        back = torch.empty_like(recv)
+        back[perm] = y
+        ret = torch.empty_like(send)
+        self._a2a(ret, back, send_splits, recv_splits)
+        self._mark("combine")
+        out = torch.zeros(hidden.shape[0], hidden.shape[1], dtype=torch.float32, device=dev)
+        w_sorted = weights.reshape(-1)[order].to(torch.float32)
+        out.index_add_(0, tok, ret.float() * w_sorted[:, None])
+        self._mark("sum")
+        return out.to(hidden.dtype)
+
+
+# --------------------------------------------------------------------------- benchmark leg
+def bench_ep(args, shape, rank, world, B):
+    """Expert-parallel leg of bench.py: ``args.tokens`` tokens per rank, experts sharded over
+    the ranks, one EP layer per step (dispatch, gate_up, GLU, down, combine, weighted sum).
+    Times K steps with CUDA events, max over ranks."""
+    import os
+
+    import nf4_grouped
+    import synth
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
+    torch.cuda.set_device(dev)
+    K, Wm = args.steps, args.warmup
+    e_local = shape.experts // world
+    n_layers = max(2, min(args.layers, 8))
+    # this rank's expert shards (seeded per global expert slice)
+    gen = torch.Generator().manual_seed(4321 + rank)
+    layers = []
+    for _ in range(n_layers):
+        (n1, k1), (n2, k2) = shape.gate_up, shape.down
+        mk = synth.nf4_stack if shape.fmt == "nf4" else synth.mxfp4_stack
+        layers.append((mk(e_local, n1, k1, gen, device=dev, fast=True), mk(e_local, n2, k2, gen, device=dev, fast=True)))
+    zipf = 1.1 if shape.name == "deepseek_v3" else None
+    gen2 = torch.Generator().manual_seed(777 + rank)
+    steps = []
+    for _ in range(K + Wm):
+        x, idx, w = synth.routed_batch(shape, args.tokens, gen2, zipf)
+        steps.append((x.pin_memory(), idx.pin_memory(), w.pin_memory()))
+    dsteps = [(x.to(dev), idx.to(dev), w.to(dev)) for x, idx, w in steps]
+    mods = [EPGroupedMoE(shape.experts, gu, dn, fmt=shape.fmt) for gu, dn in layers]
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    def run(i, host):
+        m = mods[i % n_layers]
+        if host:
+            x, idx, w = (t.to(dev, non_blocking=True) for t in steps[i])
+            return m.forward(x, idx, w).to("cpu")
+        return m.forward(*dsteps[i])
+
+    for i in range(Wm):
+        run(i, False)
+    with B.ClockSampler(dev.index) as clk:
+        t_res = []
+        for _ in range(max(1, args.repeats // 2)):
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(Wm, Wm + K):
+                run(i, False)
+            e1.record()
+            barrier()
+            t_res.append(e0.elapsed_time(e1))
+        for i in range(Wm):
+            run(i, True)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(Wm, Wm + K):
+            run(i, True)
+        e1.record()
+        barrier()
+        t_e2e = e0.elapsed_time(e1)
+        # phase breakdown and per-rank load, one instrumented pass
+        for m in mods:
+            m.timers = {}
+        rows = []
+        for i in range(Wm, Wm + K):
+            run(i, False)
+            rows.append(mods[i % n_layers].last_rows)
+        torch.cuda.synchronize()
+        names = ["dispatch", "gate_up", "glu", "down", "combine", "sum"]
+        phase = {n: [] for n in names}
+        for m in mods:
+            ev = m.timers
+            for j in range(len(ev.get("start", []))):
+                prev = ev["start"][j]
+                for n in names:
+                    phase[n].append(prev.elapsed_time(ev[n][j]) * 1e3)
+                    prev = ev[n][j]
+            m.timers = None
+    t = torch.tensor([statistics.median(t_res), t_e2e, float(statistics.mean(rows))], device=dev)
+    tmax = t.clone()
+    dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+    tsum = t.clone()
+    dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
+    ms_layer, ms_e2e = tmax[0].item(), tmax[1].item()
+    us_layer = ms_layer * 1e3 / K
+    rows_mean = tsum[2].item() / world
+    pairs = args.tokens * shape.top_k
+    fl = sum(2 * pairs * n * k for n, k in (shape.gate_up, shape.down)) * world
+    peaks = B.measured_peaks()
+    us_gu = statistics.median(phase["gate_up"])
+    fl_gu_rank = 2 * rows_mean * shape.gate_up[0] * shape.gate_up[1]
+    ach = fl_gu_rank / (us_gu * 1e-6) / 1e12
+    line = {
+        "metric": "grouped 4-bit MoE GEMM us/layer", "value": us_layer, "unit": "us/layer", "n_gpus": world,
+        "steps": K, "warmup": Wm, "ms_per_step": ms_layer / K, "higher_is_better": False, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16 activations x 4-bit weights, fp32 accumulate", "data": "synthetic",
+        "config": {"workload": f"{shape.name} {shape.fmt} MoE layer, expert-parallel over {world} GPUs "
+                               f"({e_local} experts per GPU), {args.tokens} tokens per GPU, top-{shape.top_k}, "
+                               f"dispatch/combine by NCCL all_to_all",
+                   "tokens": args.tokens, "layers_resident": n_layers, "zipf": zipf,
+                   "l2": "inputs larger than L2 per step: resident layer stacks walked round-robin, fresh routing per step",
+                   "timing": "K eager steps, CUDA events, max over ranks"},
+        "e2e": {"value": ms_e2e * 1e3 / K, "unit": "us/layer",
+                "h2d_bytes_per_step": args.tokens * (shape.hidden * 2 + shape.top_k * 12),
+                "d2h_bytes_per_step": args.tokens * shape.hidden * 2},
+        "gpu_launches": 2 * K,
+        "roofline": {"bound": "tensor" if pairs / shape.experts > 16 else "hbm", "achieved": ach, "peak": peaks["tflops"],
+                     "unit": "TFLOP/s", "frac": ach / peaks["tflops"], "traffic": None,
+                     "kernel": "gate_up grouped GEMM (per rank)", "us_per_launch": us_gu, "peak_source": peaks["source"]},
+        "ep": {"phase_us_median": {n: statistics.median(v) for n, v in phase.items()},
+               "rows_per_rank_mean": rows_mean, "rows_per_rank_max": tmax[2].item(),
+               "imbalance_max_over_mean": tmax[2].item() / max(rows_mean, 1e-9),
+               "aggregate_tflops": fl / (us_layer * 1e-6) / 1e12},
+        "clocks": clk.summary(), "device_status": nf4_grouped.last_status(dev),
+    }
+    return line
