@@ -1,0 +1,295 @@
+// Batch-1 decode kernel: every group is ONE activation row, weights are streamed once.
+//
+// The tight special case of the streaming path, taken when the host knows that no group has
+// more than one row, K <= 3072, N % 8 == 0 and the stack is laid out so that consecutive
+// weight rows (and their scale rows) are contiguous and 16-byte aligned.  Then a work item
+// (group, tile of R = 8m weight rows) is ONE contiguous span of packed bytes and ONE
+// contiguous span of scale bytes, so a stage of the ring is filled by two bulk copies
+// (TMA engine) issued by a single producer lane -- no per-row copies, no register-staged
+// scale loads -- and the stage index is a closed-form function of the item index.
+//
+//   warp 8       producer: one lane walks this CTA's contiguous item range and issues, per
+//                item, cp.async.bulk(weights) + cp.async.bulk(raw scales) on full[stage]
+//   warps 0..7   consumers: warp w owns rows w, w + 8, ... of the stage; a lane owns the
+//                16-byte units lane, lane + 32, ... of a row, decodes through the
+//                conflict-free byte-pair table, FMAs against the activation row it keeps in
+//                registers, applies the block scale once per unit, warp-shuffle reduces.
+//
+// Summation order per output element is the same as in stream_kernel.cuh, so both kernels
+// give bit-identical results.
+#pragma once
+
+#include "common.cuh"
+#include "stream_kernel.cuh"
+
+namespace gnf4b {
+
+constexpr int kDConsumerWarps = 8;
+constexpr int kDThreads = (kDConsumerWarps + 1) * 32;
+constexpr int kDMaxStages = 8;
+
+struct DecodeArgs {
+    GemmArgs g;
+    int32_t rows_per_stage;     // R, a multiple of 8
+    int32_t tiles_per_group;    // ceil(N / R)
+    int32_t row_bytes;          // K / 2
+    int32_t scale_row_bytes;    // (K / block) * sizeof(scale)
+    int32_t slot_bytes;         // ring slot, >= R * (row_bytes + scale_row_bytes), multiple of 128
+    int32_t g_cache;
+    int32_t stages;             // ring depth, 3..8, as many slots as shared memory holds
+    int32_t items_per_cta;      // total_items / grid
+    int32_t items_extra;        // total_items % grid: the first items_extra CTAs take one more
+    int64_t total_items;        // G * tiles_per_group
+};
+
+__host__ __device__ inline size_t decode_smem_bytes(int slot_bytes, int stages, int g_cache) {
+    return (size_t)kSTableBytes + (size_t)stages * slot_bytes + 256 + (size_t)(2 * g_cache + 1) * 4;
+}
+
+// Two weight rows at once against the same activation registers: two independent sets of
+// FMA chains and twice the table lookups in flight per lane.  Each row is summed exactly as
+// unit_dot_regs sums it.
+__device__ __forceinline__ void unit_dot_regs2(const uint4 wa, const uint4 wb, const float* a32, uint32_t tab_lane,
+                                               float* ra, float* rb) {
+    const uint32_t xa[4] = {wa.x, wa.y, wa.z, wa.w};
+    const uint32_t xb[4] = {wb.x, wb.y, wb.z, wb.w};
+    float pa[4] = {0.f, 0.f, 0.f, 0.f}, pb[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const float2 p = ld_shared_f32x2(tab_lane + prmt(xa[i], 0u, 0x4404u | (b << 4)));
+            const float2 q = ld_shared_f32x2(tab_lane + prmt(xb[i], 0u, 0x4404u | (b << 4)));
+            pa[b] = fmaf(p.x, a32[i * 8 + b * 2], pa[b]);
+            pb[b] = fmaf(q.x, a32[i * 8 + b * 2], pb[b]);
+            pa[b] = fmaf(p.y, a32[i * 8 + b * 2 + 1], pa[b]);
+            pb[b] = fmaf(q.y, a32[i * 8 + b * 2 + 1], pb[b]);
+        }
+    }
+    *ra = (pa[0] + pa[1]) + (pa[2] + pa[3]);
+    *rb = (pb[0] + pb[1]) + (pb[2] + pb[3]);
+}
+
+template <int SDT>
+__device__ __forceinline__ float ld_shared_scale(uint32_t row_addr, int idx) {
+    if (SDT == GNF4B_S_F32) return ld_shared_f32(row_addr + idx * 4);
+    if (SDT == GNF4B_S_BF16) {
+        uint32_t h;
+        asm volatile("ld.shared.u16 %0, [%1];" : "=r"(h) : "r"(row_addr + idx * 2));
+        return __uint_as_float(h << 16);
+    }
+    uint32_t e;
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(e) : "r"(row_addr + idx));
+    return __uint_as_float(e >= 2 ? (e - 1) << 23 : 0x00200000u << e);
+}
+
+struct DGroup {
+    int32_t row0, eid;
+    bool valid;
+};
+
+__device__ __forceinline__ DGroup decode_group(const DecodeArgs& a, const int32_t* s_grp, int g) {
+    int32_t row0, end, eid;
+    if (g < a.g_cache) {
+        row0 = s_grp[g];
+        end = s_grp[g + 1];
+        eid = s_grp[a.g_cache + 1 + g];
+    } else {
+        row0 = __ldg(a.g.off + g);
+        end = __ldg(a.g.off + g + 1);
+        eid = __ldg(a.g.eids + g);
+    }
+    DGroup d;
+    d.row0 = row0;
+    d.eid = eid;
+    const bool bad_e = eid < 0 || eid >= a.g.E;
+    const bool bad_o = end < row0 || row0 < 0 || end > a.g.T;
+    d.valid = !bad_e && !bad_o && end > row0;
+    if ((bad_e || bad_o) && end != row0 && a.g.status && (threadIdx.x & 31) == 0)
+        atomicOr(a.g.status, bad_e ? GNF4B_ST_BAD_EXPERT : GNF4B_ST_BAD_OFFSETS);
+    return d;
+}
+
+template <int FMT, int SDT, int AU>
+__global__ void __launch_bounds__(kDThreads, 1) decode_gemv_kernel(const DecodeArgs a) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint8_t* tab_raw = smem;
+    uint8_t* ring = smem + kSTableBytes;
+    uint8_t* tail = ring + (size_t)a.stages * a.slot_bytes;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(tail);
+    uint64_t* empty_bar = full_bar + kDMaxStages;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_bar + kDMaxStages);
+    int32_t* s_grp = reinterpret_cast<int32_t*>(tail + 256);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < a.stages; ++s) {
+            mbar_init(full_bar + s, 1);
+            mbar_init(empty_bar + s, kDConsumerWarps);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    for (int i = threadIdx.x; i < 2 * a.g_cache + 1; i += kDThreads)
+        s_grp[i] = (i <= a.g_cache) ? __ldg(a.g.off + i) : __ldg(a.g.eids + (i - a.g_cache - 1));
+    __syncthreads();
+
+    const int bid = (int)blockIdx.x;
+    const int64_t item_lo = (int64_t)bid * a.items_per_cta + min(bid, a.items_extra);
+    const int64_t item_hi = item_lo + a.items_per_cta + (bid < a.items_extra ? 1 : 0);
+    const int R = a.rows_per_stage;
+    int g = (int)((uint32_t)item_lo / (uint32_t)a.tiles_per_group);
+    int tile = (int)((uint32_t)item_lo - (uint32_t)g * (uint32_t)a.tiles_per_group);
+
+    if (warp == kDConsumerWarps) {
+        // ------------------------------------------------------------ producer (two lanes)
+        // lane 0 copies the packed rows, lane 1 the scale rows of the same stage
+        if (lane < 2) {
+            const int elt = (SDT == GNF4B_S_F32) ? 4 : (SDT == GNF4B_S_BF16 ? 2 : 1);
+            const uint8_t* Sb = reinterpret_cast<const uint8_t*>(a.g.S);
+            uint32_t stage = 0, phase = 0;
+            int cur_g = -1;
+            DGroup grp;
+            grp.valid = false;
+            bool ok = true;
+            for (int64_t item = item_lo; item < item_hi && ok; ++item) {
+                if (cur_g != g) { grp = decode_group(a, s_grp, g); cur_g = g; }
+                ok = mbar_wait_bounded(empty_bar + stage, phase ^ 1, abort_flag);
+                if (!ok) break;
+                if (grp.valid) {
+                    uint8_t* st = ring + (size_t)stage * a.slot_bytes;
+                    const int n0 = tile * R;
+                    const int rows = min(R, (int)(a.g.N - n0));
+                    const uint32_t wb = (uint32_t)rows * (uint32_t)a.row_bytes;
+                    const uint32_t sb = (uint32_t)rows * (uint32_t)a.scale_row_bytes;
+                    if (lane == 0) mbar_arrive_expect_tx(full_bar + stage, wb + sb);
+                    __syncwarp(0x3u);
+                    const uint8_t* src = (lane == 0)
+                        ? a.g.W + (int64_t)grp.eid * a.g.w_se + (int64_t)n0 * a.row_bytes
+                        : Sb + ((int64_t)grp.eid * a.g.s_se + (int64_t)n0 * a.g.s_sn) * elt;
+                    bulk_g2s(lane == 0 ? st : st + (size_t)R * a.row_bytes, src, lane == 0 ? wb : sb, full_bar + stage);
+                } else if (lane == 0) {
+                    mbar_arrive(full_bar + stage);      // empty group: the stage carries nothing
+                }
+                if (++stage == (uint32_t)a.stages) { stage = 0; phase ^= 1; }
+                if (++tile == a.tiles_per_group) { tile = 0; ++g; }
+            }
+            if (!ok && lane == 0 && a.g.status) atomicOr(a.g.status, GNF4B_ST_TIMEOUT);
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------- consumers
+    const int n_units = a.row_bytes >> 4;
+    int cur_g = -1;
+    DGroup grp;
+    grp.valid = false;
+    grp.row0 = 0;
+    float a_reg[AU * 32];
+
+    // The first group's activation row is requested before the table is built, so its
+    // global-memory latency overlaps the table construction.
+    auto load_a = [&](const DGroup& gr, uint4 (&raw)[AU * 4]) {
+        const uint8_t* xrow = reinterpret_cast<const uint8_t*>(a.g.x) + (int64_t)gr.row0 * a.g.K * 2;
+#pragma unroll
+        for (int q = 0; q < AU; ++q) {
+            const int U = lane + 32 * q;
+#pragma unroll
+            for (int v = 0; v < 4; ++v)
+                raw[q * 4 + v] = (gr.valid && U < n_units)
+                                     ? __ldg(reinterpret_cast<const uint4*>(xrow + (int64_t)U * 64 + v * 16))
+                                     : make_uint4(0, 0, 0, 0);
+        }
+    };
+    auto cvt_a = [&](const uint4 (&raw)[AU * 4]) {
+#pragma unroll
+        for (int i = 0; i < AU * 4; ++i) cvt8(raw[i], a.g.x_dtype, &a_reg[i * 8]);
+    };
+    {
+        uint4 raw[AU * 4];
+        if (item_lo < item_hi) {
+            grp = decode_group(a, s_grp, g);
+            cur_g = g;
+        }
+        load_a(grp, raw);
+        // pair table: tab[byte][slot], 32 slots of float2 per byte, all holding the same pair,
+        // so a lane reading slot == its lane id never conflicts with another lane.  A half
+        // warp writes one byte's 256-byte row per step with 16-byte stores.
+        const int half = lane >> 4, hl = lane & 15;
+#pragma unroll 4
+        for (int j = 0; j < 32; j += 2) {
+            const int b = warp * 32 + j + half;
+            const float2 p = byte_pair<FMT>(b);
+            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(smem_u32(tab_raw) + b * 256 + hl * 16),
+                         "f"(p.x), "f"(p.y), "f"(p.x), "f"(p.y)
+                         : "memory");
+        }
+        cvt_a(raw);
+    }
+    named_bar_sync(1, kDConsumerWarps * 32);
+
+    const uint32_t tab_lane = smem_u32(tab_raw) + lane * 8;
+    uint16_t* out_bf = reinterpret_cast<uint16_t*>(a.g.out);
+    uint32_t stage = 0, phase = 0;
+    bool poisoned = false;
+
+    for (int64_t item = item_lo; item < item_hi; ++item) {
+        if (cur_g != g) {
+            grp = decode_group(a, s_grp, g);
+            cur_g = g;
+            uint4 raw[AU * 4];
+            load_a(grp, raw);
+            cvt_a(raw);
+        }
+        if (!poisoned && !mbar_wait_bounded(full_bar + stage, phase, abort_flag)) poisoned = true;
+        if (!poisoned && grp.valid) {
+            const uint32_t st = smem_u32(ring + (size_t)stage * a.slot_bytes);
+            const int n0 = tile * R;
+            const int rows = min(R, (int)(a.g.N - n0));
+            // rows of the stage are taken two at a time: (r, r + 8)
+            for (int r = warp; r < rows; r += 2 * kDConsumerWarps) {
+                const bool two = r + kDConsumerWarps < rows;
+                const int rb = two ? r + kDConsumerWarps : r;
+                const uint32_t wrow_a = st + (uint32_t)(r * a.row_bytes);
+                const uint32_t wrow_b = st + (uint32_t)(rb * a.row_bytes);
+                const uint32_t srow_a = st + (uint32_t)(R * a.row_bytes + r * a.scale_row_bytes);
+                const uint32_t srow_b = st + (uint32_t)(R * a.row_bytes + rb * a.scale_row_bytes);
+                float acc_a = 0.f, acc_b = 0.f;
+#pragma unroll
+                for (int q = 0; q < AU; ++q) {
+                    const int u = lane + 32 * q;
+                    if (u < n_units) {
+                        const uint4 wa = ld_shared_u32x4(wrow_a + u * 16);
+                        const uint4 wb = ld_shared_u32x4(wrow_b + u * 16);
+                        const int si = (FMT == GNF4B_FMT_NF4) ? (u >> 1) : u;
+                        const float sa = ld_shared_scale<SDT>(srow_a, si);
+                        const float sb = ld_shared_scale<SDT>(srow_b, si);
+                        float da, db;
+                        unit_dot_regs2(wa, wb, &a_reg[q * 32], tab_lane, &da, &db);
+                        acc_a += da * sa;
+                        acc_b += db * sb;
+                    }
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    acc_a += __shfl_xor_sync(0xffffffffu, acc_a, o);
+                    acc_b += __shfl_xor_sync(0xffffffffu, acc_b, o);
+                }
+                if (lane == 0) {
+                    uint16_t* dst = out_bf + (int64_t)grp.row0 * a.g.N + n0;
+                    dst[r] = f32_to_bf16_bits(acc_a);
+                    if (two) dst[rb] = f32_to_bf16_bits(acc_b);
+                }
+            }
+        }
+        __syncwarp();
+        if (!poisoned && lane == 0) mbar_arrive(empty_bar + stage);
+        if (++stage == (uint32_t)a.stages) { stage = 0; phase ^= 1; }
+        if (++tile == a.tiles_per_group) { tile = 0; ++g; }
+    }
+    if (poisoned && threadIdx.x == 0 && a.g.status) atomicOr(a.g.status, GNF4B_ST_TIMEOUT);
+}
+
+}  // namespace gnf4b

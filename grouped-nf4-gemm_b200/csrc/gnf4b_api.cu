@@ -9,6 +9,7 @@
 
 #include "common.cuh"
 #include "stream_kernel.cuh"
+#include "decode_kernel.cuh"
 #include "tensor_kernel.cuh"
 
 namespace gnf4b {
@@ -153,6 +154,22 @@ static cudaError_t launch_stream_au(const StreamArgs& sa, int au, int grid, size
     if (au == 3) GNF4B_LAUNCH_AU(3);
     GNF4B_LAUNCH_AU(0);
 #undef GNF4B_LAUNCH_AU
+}
+
+template <int FMT, int SDT>
+static cudaError_t launch_decode_au(const DecodeArgs& da, int au, int grid, size_t smem, cudaStream_t st) {
+#define GNF4B_LAUNCH_D(AUV)                                                                           \
+    do {                                                                                              \
+        auto kfn = decode_gemv_kernel<FMT, SDT, AUV>;                                                 \
+        cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        if (e != cudaSuccess) return e;                                                               \
+        kfn<<<grid, kDThreads, smem, st>>>(da);                                                       \
+        return cudaGetLastError();                                                                    \
+    } while (0)
+    if (au <= 1) GNF4B_LAUNCH_D(1);
+    if (au == 2) GNF4B_LAUNCH_D(2);
+    GNF4B_LAUNCH_D(3);
+#undef GNF4B_LAUNCH_D
 }
 
 static int align_class(const void* p, int64_t a, int64_t b) {
@@ -301,6 +318,47 @@ int gnf4b_gemm_grouped(int fmt, int op, const void* x, int x_dtype, int64_t T, c
         g.ws = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + p.counters_bytes);
     }
     g.split_k = p.split_k;
+    {
+        // Batch-1 decode kernel: one row per group, contiguous 16-byte aligned rows and scale
+        // rows, so a stage is two bulk copies (see decode_kernel.cuh).
+        const int elt = (s_dtype == GNF4B_S_F32) ? 4 : (s_dtype == GNF4B_S_BF16 ? 2 : 1);
+        const int64_t blk = (fmt == GNF4B_FMT_NF4) ? 64 : 32;
+        const int64_t row_bytes = K / 2, srow = (K / blk) * elt;
+        const bool contiguous = w_stride_n == row_bytes && s_stride_n == K / blk &&
+                                (((uintptr_t)W | (uint64_t)w_stride_e) & 15) == 0 &&
+                                (((uintptr_t)S | (uint64_t)(s_stride_e * elt)) & 15) == 0 && ((8 * srow) & 15) == 0;
+        if (max_rows == 1 && p.split_k == 1 && K <= 3072 && (N % 8) == 0 && contiguous && G <= T) {
+            DecodeArgs da;
+            da.g = g;
+            // rows per stage: 16 (two per consumer warp, processed together), more for short rows
+            const int m = (int)std::max<int64_t>(2, std::min<int64_t>(4, 16384 / (8 * row_bytes)));
+            da.rows_per_stage = 8 * m;
+            da.tiles_per_group = (int32_t)ceil_div(N, da.rows_per_stage);
+            da.row_bytes = (int32_t)row_bytes;
+            da.scale_row_bytes = (int32_t)srow;
+            da.slot_bytes = (int32_t)round_up((int64_t)da.rows_per_stage * (row_bytes + srow), 128);
+            da.g_cache = p.g_cache;
+            da.total_items = (int64_t)G * da.tiles_per_group;
+            const int64_t room = (int64_t)di.smem_optin - (int64_t)decode_smem_bytes(0, 0, da.g_cache);
+            da.stages = (int32_t)std::min<int64_t>(kDMaxStages, room / da.slot_bytes);
+            const int dgrid = (int)std::min<int64_t>(di.sm_count, da.total_items);
+            da.items_per_cta = (int32_t)(da.total_items / dgrid);
+            da.items_extra = (int32_t)(da.total_items % dgrid);
+            const size_t dsmem = decode_smem_bytes(da.slot_bytes, std::max(da.stages, 1), da.g_cache);
+            if (da.stages >= 3 && da.total_items < (int64_t)1 << 31) {
+                const int au = (int)ceil_div(K, 1024);
+                cudaError_t e;
+                if (fmt == GNF4B_FMT_NF4 && s_dtype == GNF4B_S_F32)
+                    e = launch_decode_au<GNF4B_FMT_NF4, GNF4B_S_F32>(da, au, dgrid, dsmem, st);
+                else if (fmt == GNF4B_FMT_NF4)
+                    e = launch_decode_au<GNF4B_FMT_NF4, GNF4B_S_BF16>(da, au, dgrid, dsmem, st);
+                else
+                    e = launch_decode_au<GNF4B_FMT_MXFP4, GNF4B_S_E8M0>(da, au, dgrid, dsmem, st);
+                if (e != cudaSuccess) return cuda_fail(e, "decode kernel launch");
+                return GNF4B_OK;
+            }
+        }
+    }
     StreamArgs sa;
     sa.g = g;
     sa.n_tiles = (int32_t)p.n_tiles;

@@ -191,14 +191,14 @@ __device__ __forceinline__ bool cursor_next(const StreamArgs& a, const int32_t* 
 // Block scales of one stage, widened to fp32, 16 per lane: slot (r, j) = (i / 64, i % 64) for
 // i = lane + 32 t.  Slots past the chunk or past N read nothing (0).
 template <int FMT, int SDT>
-__device__ __forceinline__ void producer_fetch_scales(const StreamArgs& a, const StageCursor& cur,
+__device__ __forceinline__ void producer_fetch_scales(const StreamArgs& a, int eid, int tile, int c,
                                                       int scales_per_chunk, int lane, float* v) {
     const int64_t scale_blk = (FMT == GNF4B_FMT_NF4) ? 64 : 32;
-    const int64_t boff = (int64_t)cur.c * a.chunk_bytes;
+    const int64_t boff = (int64_t)c * a.chunk_bytes;
     const int cbytes = (int)min((int64_t)a.chunk_bytes, a.g.K / 2 - boff);
     const int nsc = cbytes * 2 / (int)scale_blk;
-    const int n0 = cur.it.tile * kSTileN;
-    const int64_t base = (int64_t)cur.it.eid * a.g.s_se + (int64_t)cur.c * scales_per_chunk;
+    const int n0 = tile * kSTileN;
+    const int64_t base = (int64_t)eid * a.g.s_se + (int64_t)c * scales_per_chunk;
 #pragma unroll
     for (int t = 0; t < 16; ++t) {
         const int i = lane + 32 * t;
@@ -210,18 +210,18 @@ __device__ __forceinline__ void producer_fetch_scales(const StreamArgs& a, const
 // Warm L2 (and the TLB) with the block scales of one stage: lanes 0..15 each touch one of
 // the at most two 128-byte lines of one of the eight rows.
 template <int FMT, int SDT>
-__device__ __forceinline__ void producer_prefetch_scales(const StreamArgs& a, const StageCursor& cur,
+__device__ __forceinline__ void producer_prefetch_scales(const StreamArgs& a, int eid, int tile, int c,
                                                          int scales_per_chunk, int lane) {
     if (lane >= 16) return;
     const int64_t scale_blk = (FMT == GNF4B_FMT_NF4) ? 64 : 32;
     const int elt = (SDT == GNF4B_S_F32) ? 4 : (SDT == GNF4B_S_BF16 ? 2 : 1);
-    const int64_t boff = (int64_t)cur.c * a.chunk_bytes;
+    const int64_t boff = (int64_t)c * a.chunk_bytes;
     const int cbytes = (int)min((int64_t)a.chunk_bytes, a.g.K / 2 - boff);
     const int nsc = cbytes * 2 / (int)scale_blk;
-    const int n = cur.it.tile * kSTileN + (lane >> 1);
+    const int n = tile * kSTileN + (lane >> 1);
     if (n >= a.g.N) return;
     const uintptr_t first = reinterpret_cast<uintptr_t>(a.g.S) +
-        (uintptr_t)(((int64_t)cur.it.eid * a.g.s_se + (int64_t)n * a.g.s_sn + (int64_t)cur.c * scales_per_chunk) * elt);
+        (uintptr_t)(((int64_t)eid * a.g.s_se + (int64_t)n * a.g.s_sn + (int64_t)c * scales_per_chunk) * elt);
     const uintptr_t last = first + (uintptr_t)(nsc * elt) - 1;
     const uintptr_t line = (first & ~(uintptr_t)127) + (uintptr_t)(lane & 1) * 128;
     if (line <= last) asm volatile("prefetch.global.L2 [%0];" ::"l"(line));
@@ -285,6 +285,99 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_gemm_kernel(const StreamA
     const int scales_per_chunk = a.chunk_bytes * 2 / (int)scale_blk;
     const int64_t row_bytes = a.g.K / 2;
 
+    if (warp >= kSConsumerWarps && AU > 0) {
+        // ------------------------------------------------------------ producers, decode form
+        // Every item takes exactly n_chunks ring stages whether its group is empty or not, so
+        // stage q of this CTA is (item_lo + q / n_chunks, q % n_chunks) in closed form and a
+        // producer warp reaches its stages q = pw, pw + 4, ... without walking the ones between.
+        // A four-deep register queue of stage descriptors lets a warp prefetch the scales of a
+        // stage into L2 three of its turns ahead, load them one turn ahead and publish them now.
+        const uint32_t pw = (uint32_t)(warp - kSConsumerWarps);
+        const uint32_t nc = (uint32_t)a.n_chunks;
+        const uint32_t ns = (uint32_t)(item_hi - item_lo) * nc;
+        struct DStage { int32_t eid, tile, c; bool valid; };
+        // generator state: next stage index to describe and the (group, tile) of its item
+        uint32_t gq = pw;
+        uint32_t g_item = gq / nc;                       // item index relative to item_lo
+        int32_t gg, gtile;
+        {
+            const uint32_t it0 = (uint32_t)item_lo + g_item;
+            gg = (int32_t)(it0 / (uint32_t)a.n_tiles);
+            gtile = (int32_t)(it0 - (uint32_t)gg * (uint32_t)a.n_tiles);
+        }
+        auto gen = [&]() -> DStage {
+            DStage d;
+            d.valid = false; d.eid = 0; d.tile = gtile; d.c = (int32_t)(gq - g_item * nc);
+            if (gq < ns) {
+                int32_t row0, end;
+                if (gg < a.g_cache) { row0 = s_grp[gg]; end = s_grp[gg + 1]; d.eid = s_grp[a.g_cache + 1 + gg]; }
+                else { row0 = __ldg(a.g.off + gg); end = __ldg(a.g.off + gg + 1); d.eid = __ldg(a.g.eids + gg); }
+                d.valid = end > row0 && row0 >= 0 && end <= a.g.T && d.eid >= 0 && d.eid < a.g.E;
+                if (d.valid) producer_prefetch_scales<FMT, SDT>(a, d.eid, d.tile, d.c, scales_per_chunk, lane);
+            }
+            gq += kSProducerWarps;
+            const uint32_t ni = gq / nc;
+            gtile += (int32_t)(ni - g_item);
+            g_item = ni;
+            while (gtile >= a.n_tiles) { gtile -= a.n_tiles; ++gg; }
+            return d;
+        };
+        DStage f0 = gen(), f1 = gen(), f2 = gen(), f3 = gen();
+        float v_cur[16], v_nxt[16];
+#pragma unroll
+        for (int t = 0; t < 16; ++t) { v_cur[t] = 0.f; v_nxt[t] = 0.f; }
+        if (f0.valid) producer_fetch_scales<FMT, SDT>(a, f0.eid, f0.tile, f0.c, scales_per_chunk, lane, v_cur);
+        bool poisoned = false;
+        for (uint32_t q = pw; q < ns; q += kSProducerWarps) {
+            const uint32_t stage = q % kSStages, phase = (q / kSStages) & 1;
+            if (!poisoned && !mbar_wait_bounded(empty_bar + stage, phase ^ 1, abort_flag)) poisoned = true;
+            uint8_t* st = ring + stage * kSStageBytes;
+            if (!poisoned) {
+                if (f0.valid && a.w_align == 16) {
+                    const int n0 = f0.tile * kSTileN;
+                    const int n_valid = min(kSTileN, (int)(a.g.N - n0));
+                    const int64_t boff = (int64_t)f0.c * kSRowPitch;
+                    const int cbytes = (int)min((int64_t)kSRowPitch, row_bytes - boff);
+                    if (lane == 0) mbar_arrive_expect_tx(full_bar + stage, (uint32_t)(n_valid * cbytes));
+                    __syncwarp();
+                    if (lane < n_valid)
+                        bulk_g2s(st + lane * kSRowPitch,
+                                 a.g.W + (int64_t)f0.eid * a.g.w_se + (int64_t)(n0 + lane) * a.g.w_sn + boff,
+                                 (uint32_t)cbytes, full_bar + stage);
+                } else {
+                    if (f0.valid) {
+                        const int n0 = f0.tile * kSTileN;
+                        const int n_valid = min(kSTileN, (int)(a.g.N - n0));
+                        const int64_t boff = (int64_t)f0.c * kSRowPitch;
+                        const int cbytes = (int)min((int64_t)kSRowPitch, row_bytes - boff);
+                        for (int r = 0; r < n_valid; ++r) {
+                            const uint8_t* src = a.g.W + (int64_t)f0.eid * a.g.w_se + (int64_t)(n0 + r) * a.g.w_sn + boff;
+                            if (a.w_align == 8) plain_copy_row<8>(st + r * kSRowPitch, src, cbytes, lane);
+                            else if (a.w_align == 4) plain_copy_row<4>(st + r * kSRowPitch, src, cbytes, lane);
+                            else plain_copy_row<1>(st + r * kSRowPitch, src, cbytes, lane);
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(full_bar + stage);
+                }
+            }
+            if (f1.valid) producer_fetch_scales<FMT, SDT>(a, f1.eid, f1.tile, f1.c, scales_per_chunk, lane, v_nxt);
+            if (!poisoned) {
+                float* st_sc = reinterpret_cast<float*>(st + kSTileN * kSRowPitch);
+                if (f0.valid) {
+#pragma unroll
+                    for (int t = 0; t < 16; ++t) st_sc[lane + 32 * t] = v_cur[t];
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full_bar + stage);
+            }
+            f0 = f1; f1 = f2; f2 = f3; f3 = gen();
+#pragma unroll
+            for (int t = 0; t < 16; ++t) v_cur[t] = v_nxt[t];
+        }
+        if (poisoned && lane == 0 && a.g.status) atomicOr(a.g.status, GNF4B_ST_TIMEOUT);
+        return;
+    }
     if (warp >= kSConsumerWarps) {
         // ------------------------------------------------------------ producers
         // Stage q of this CTA belongs to producer warp q % 4.  Per stage a warp (1) issues the
@@ -299,12 +392,12 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_gemm_kernel(const StreamA
         bool have = cursor_next(a, s_grp, cur, item_lo, item_hi);
         for (uint32_t i = 0; have && i < pw; ++i, ++q) have = cursor_next(a, s_grp, cur, item_lo, item_hi);
         float v_cur[16], v_nxt[16];
-        if (have) producer_fetch_scales<FMT, SDT>(a, cur, scales_per_chunk, lane, v_cur);
+        if (have) producer_fetch_scales<FMT, SDT>(a, cur.it.eid, cur.it.tile, cur.c, scales_per_chunk, lane, v_cur);
         StageCursor far = cur;
         bool have_far = have;
         for (int d = 0; d < kFar; ++d) {
             for (int i = 0; have_far && i < kSProducerWarps; ++i) have_far = cursor_next(a, s_grp, far, item_lo, item_hi);
-            if (have_far) producer_prefetch_scales<FMT, SDT>(a, far, scales_per_chunk, lane);
+            if (have_far) producer_prefetch_scales<FMT, SDT>(a, far.it.eid, far.it.tile, far.c, scales_per_chunk, lane);
         }
         bool poisoned = false;
         while (have) {
@@ -337,9 +430,9 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_gemm_kernel(const StreamA
             StageCursor nxt = cur;
             bool have_nxt = true;
             for (int i = 0; have_nxt && i < kSProducerWarps; ++i) have_nxt = cursor_next(a, s_grp, nxt, item_lo, item_hi);
-            if (have_nxt) producer_fetch_scales<FMT, SDT>(a, nxt, scales_per_chunk, lane, v_nxt);
+            if (have_nxt) producer_fetch_scales<FMT, SDT>(a, nxt.it.eid, nxt.it.tile, nxt.c, scales_per_chunk, lane, v_nxt);
             for (int i = 0; have_far && i < kSProducerWarps; ++i) have_far = cursor_next(a, s_grp, far, item_lo, item_hi);
-            if (have_far) producer_prefetch_scales<FMT, SDT>(a, far, scales_per_chunk, lane);
+            if (have_far) producer_prefetch_scales<FMT, SDT>(a, far.it.eid, far.it.tile, far.c, scales_per_chunk, lane);
             if (!poisoned) {
                 // scale slot (r, j) of the stage lives at st_sc[r * 64 + j]; a lane owns slots
                 // lane, lane + 32, ... of the 8 x 64 grid
@@ -390,10 +483,9 @@ __global__ void __launch_bounds__(kSThreads, 1) stream_gemm_kernel(const StreamA
         for (int64_t item = item_lo; item < item_hi; ++item) {
             if (item > item_lo) walker_step(a, walker);
             const StreamItem it = walker_item(a, s_grp, walker);
-            if (!it.valid) continue;
             const int n = it.tile * kSTileN + warp;
-            const bool active = n < a.g.N;
-            if (reg_g != it.g) {
+            const bool active = it.valid && n < a.g.N;      // empty groups still take their stages
+            if (active && reg_g != it.g) {
                 const uint8_t* xrow = reinterpret_cast<const uint8_t*>(a.g.x) + (int64_t)it.row0 * a.g.K * 2;
 #pragma unroll
                 for (int q = 0; q < AU; ++q) {

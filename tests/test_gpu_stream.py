@@ -375,3 +375,27 @@ def test_offsets_beyond_2gib():
         w = dequant_ref(B[e], A[e], N, K).double()
         ref = (a[i].double() @ w.t()).cpu().numpy()[None]
         assert rel_fro(out[i:i + 1], ref) <= REL_FRO_TOL, e
+
+
+@pytest.mark.parametrize("fmt,N,K", [("nf4", 1536, 2048), ("nf4", 2048, 768), ("nf4", 512, 2880 // 64 * 64),
+                                     ("mxfp4", 2880, 2880), ("mxfp4", 64, 96)])
+def test_decode_kernel_equals_generic_streaming_kernel_bitwise(fmt, N, K):
+    """Host-known one-row groups take the batch-1 decode kernel; the same call with only
+    device-side offsets takes the generic streaming kernel.  Same summation order, same bits.
+    Includes an empty group and a repeated expert."""
+    gen = torch.Generator().manual_seed(K + N)
+    E = 6
+    if fmt == "nf4":
+        W, S = synth.nf4_stack(E, N, K, gen, device=DEV, fast=True)
+        fn = gemm_4bit_grouped
+    else:
+        W, S = synth.mxfp4_stack(E, N, K, gen, device=DEV, fast=True)
+        fn = mxfp4_grouped.gemm_mxfp4_grouped
+    sizes, ids = [1, 1, 0, 1, 1], [4, 0, 2, 4, 5]
+    a = torch.randn(sum(sizes), K, generator=gen).to(torch.bfloat16).to(DEV)
+    dec = fn(a, W, S, sizes, ids)
+    off = torch.tensor([0, 1, 2, 2, 3, 4], dtype=torch.int32, device=DEV)
+    gen_out = fn(a, W, S, None, torch.tensor(ids, dtype=torch.int32, device=DEV), group_offsets=off, path=_gnf4b.PATH_STREAM)
+    assert torch.equal(dec, gen_out)
+    assert rel_fro(dec, oracle_fwd64(fmt, a, W, S, sizes, ids)) <= REL_FRO_TOL
+    assert nf4_grouped.last_status(DEV) == 0
