@@ -29,6 +29,7 @@ S_F32, S_BF16, S_E8M0 = 0, 1, 2
 PATH_AUTO, PATH_STREAM, PATH_TENSOR = 0, 1, 2
 SPLITK_SHIFT = 8
 ST_BAD_EXPERT, ST_BAD_OFFSETS, ST_TIMEOUT = 1, 2, 4
+NOALLOC_SCRATCH_BYTES = 8 << 20
 
 _lib = None
 _lock = threading.Lock()
@@ -75,6 +76,10 @@ def _declare(lib):
     lib.gnf4b_gemm_grouped.argtypes = [
         C.c_int, C.c_int, vp, C.c_int, i64, vp, i64, i64, vp, C.c_int, i64, i64,
         vp, vp, i32, i32, i64, i64, i32, vp, vp, sz, vp, u32, vp]
+    lib.gnf4b_gemm_grouped_noalloc.restype = C.c_int
+    lib.gnf4b_gemm_grouped_noalloc.argtypes = [
+        C.c_int, C.c_int, vp, C.c_int, i64, vp, i64, i64, vp, C.c_int, i64, i64,
+        vp, vp, i32, i32, i64, i64, i32, vp, vp, u32, vp]
     lib.gnf4b_workspace_bytes.restype = sz
     lib.gnf4b_workspace_bytes.argtypes = [C.c_int, C.c_int, i64, i32, i64, i64, i32, u32]
     lib.gnf4b_plan_split_k.restype = C.c_int
@@ -90,6 +95,7 @@ def _declare(lib):
 
 #: every symbol include/gnf4b.h declares
 EXPORTS = ("gnf4b_abi_version", "gnf4b_strerror", "gnf4b_last_cuda_error", "gnf4b_gemm_grouped",
+           "gnf4b_gemm_grouped_noalloc",
            "gnf4b_workspace_bytes", "gnf4b_plan_split_k", "gnf4b_build_offsets", "gnf4b_dequant",
            "gnf4b_device_info")
 

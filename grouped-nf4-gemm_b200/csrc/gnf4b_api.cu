@@ -14,6 +14,10 @@
 
 namespace gnf4b {
 
+// Scratch of gnf4b_gemm_grouped_noalloc.  In host code this name is only a stand-in for the
+// device array; its device address comes from cudaGetSymbolAddress (noalloc_scratch below).
+static __device__ __align__(256) unsigned char g_noalloc_scratch[GNF4B_NOALLOC_SCRATCH_BYTES];
+
 static thread_local char g_cuda_err[256] = "";
 
 static int cuda_fail(cudaError_t e, const char* what) {
@@ -41,6 +45,25 @@ static int device_info(DevInfo* out) {
         e = cudaDeviceGetAttribute(&cache[dev].smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
         if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute(shared memory)");
         cache[dev].ok = true;
+    }
+    *out = cache[dev];
+    return GNF4B_OK;
+}
+
+// Device address of g_noalloc_scratch on the current device, looked up once per device.
+static int noalloc_scratch(void** out) {
+    static std::mutex mu;
+    static void* cache[64] = {nullptr};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    if (dev < 0 || dev >= 64) return GNF4B_EINVAL;
+    std::lock_guard<std::mutex> lk(mu);
+    if (!cache[dev]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess || !p) return cuda_fail(e, "cudaGetSymbolAddress(noalloc scratch)");
+        cache[dev] = p;
     }
     *out = cache[dev];
     return GNF4B_OK;
@@ -381,6 +404,36 @@ int gnf4b_gemm_grouped(int fmt, int op, const void* x, int x_dtype, int64_t T, c
         e = launch_stream_au<GNF4B_FMT_MXFP4, GNF4B_S_E8M0>(sa, p.au, grid, smem, st);
     if (e != cudaSuccess) return cuda_fail(e, "stream kernel launch");
     return GNF4B_OK;
+}
+
+int gnf4b_gemm_grouped_noalloc(int fmt, int op, const void* x, int x_dtype, int64_t T, const uint8_t* W,
+                               int64_t w_stride_e, int64_t w_stride_n, const void* S, int s_dtype,
+                               int64_t s_stride_e, int64_t s_stride_n, const int32_t* group_offsets,
+                               const int32_t* expert_ids, int32_t G, int32_t E, int64_t N, int64_t K,
+                               int32_t max_rows, void* out, int32_t* status_word, uint32_t flags,
+                               void* cuda_stream) {
+    int rc = check_shape(fmt, op, x_dtype, s_dtype, T, G, E, N, K);
+    if (rc) return rc;
+    if (T == 0 || G == 0) return GNF4B_OK;
+    DevInfo di;
+    rc = device_info(&di);
+    if (rc) return rc;
+    Plan p;
+    rc = make_plan(fmt, op, T, G, N, K, max_rows, flags, di, &p);
+    if (rc) return rc;
+    const size_t need = p.counters_bytes + p.ws_bytes;
+    if (need > (size_t)GNF4B_NOALLOC_SCRATCH_BYTES) return GNF4B_ETOOBIG;
+    void* scratch = nullptr;
+    rc = noalloc_scratch(&scratch);
+    if (rc) return rc;
+    if (p.counters_bytes) {
+        // the arrival counters must start at zero whatever an earlier call left behind
+        cudaError_t e = cudaMemsetAsync(scratch, 0, p.counters_bytes, reinterpret_cast<cudaStream_t>(cuda_stream));
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(noalloc scratch)");
+    }
+    return gnf4b_gemm_grouped(fmt, op, x, x_dtype, T, W, w_stride_e, w_stride_n, S, s_dtype, s_stride_e, s_stride_n,
+                              group_offsets, expert_ids, G, E, N, K, max_rows, out, scratch,
+                              (size_t)GNF4B_NOALLOC_SCRATCH_BYTES, status_word, flags, cuda_stream);
 }
 
 int gnf4b_build_offsets(const int32_t* sizes, int32_t G, int32_t* group_offsets, void* cuda_stream) {

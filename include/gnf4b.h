@@ -95,7 +95,41 @@ int gnf4b_gemm_grouped(int fmt, int op,
                        void* out, void* workspace, size_t workspace_bytes,
                        int32_t* status_word, uint32_t flags, void* cuda_stream);
 
-/* Scratch the call above needs for the same arguments (0 when none).  Replaces the
+/* Largest scratch gnf4b_gemm_grouped_noalloc can serve (bytes of the built-in device array). */
+#define GNF4B_NOALLOC_SCRATCH_BYTES (8u << 20)
+
+/* The same grouped GEMM for callers that cannot allocate device memory.  No counterpart in
+ * the reference project: there the split-K scratch is always a fresh torch allocation.
+ *
+ * Who needs it: code that runs where cudaMalloc is off limits -- inside a region that must
+ * not touch the allocator (a serving loop with a frozen memory plan, a plugin hosted by a
+ * runtime that owns all device memory and hands out none, a signal-safe or real-time path
+ * where an allocation's latency or failure is unacceptable).  Those callers still pass
+ * their inputs and the output buffer; only the scratch comes from the library: a
+ * file-scope device array of GNF4B_NOALLOC_SCRATCH_BYTES that every GPU loading this
+ * library holds until the process exits.
+ *
+ * Arguments are those of gnf4b_gemm_grouped without workspace / workspace_bytes.
+ *   - Returns GNF4B_ETOOBIG when the split-K scratch of this problem
+ *     (gnf4b_workspace_bytes) exceeds GNF4B_NOALLOC_SCRATCH_BYTES; nothing is launched.
+ *   - Calls no cudaMalloc / cudaFree and no allocating library routine.
+ *   - The first call on each device looks the array's device address up
+ *     (cudaGetSymbolAddress, with that device current); make that first call outside any
+ *     CUDA stream capture.
+ *   - All calls share the one array and it keeps what the last call left: the part that
+ *     must start at zero (the arrival counters) is cleared on `cuda_stream` before every
+ *     launch.  Two calls whose kernels overlap on the GPU (different streams, no ordering
+ *     between them) race on it; order them.
+ */
+int gnf4b_gemm_grouped_noalloc(int fmt, int op,
+                               const void* x, int x_dtype, int64_t T,
+                               const uint8_t* W, int64_t w_stride_e, int64_t w_stride_n,
+                               const void* S, int s_dtype, int64_t s_stride_e, int64_t s_stride_n,
+                               const int32_t* group_offsets, const int32_t* expert_ids,
+                               int32_t G, int32_t E, int64_t N, int64_t K, int32_t max_rows,
+                               void* out, int32_t* status_word, uint32_t flags, void* cuda_stream);
+
+/* Scratch gnf4b_gemm_grouped needs for the same arguments (0 when none).  Replaces the
  * `ws = torch.empty(sk, T, N)` split-K buffer of kernel/nf4_grouped.py:784. */
 size_t gnf4b_workspace_bytes(int fmt, int op, int64_t T, int32_t G, int64_t N, int64_t K,
                              int32_t max_rows, uint32_t flags);
