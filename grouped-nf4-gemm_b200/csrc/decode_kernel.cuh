@@ -8,12 +8,13 @@
 // (TMA engine) issued by a single producer lane -- no per-row copies, no register-staged
 // scale loads -- and the stage index is a closed-form function of the item index.
 //
-//   warp 8       producer: one lane walks this CTA's contiguous item range and issues, per
+//   warp 16      producer: two lanes walk this CTA's contiguous item range and issue, per
 //                item, cp.async.bulk(weights) + cp.async.bulk(raw scales) on full[stage]
-//   warps 0..7   consumers: warp w owns rows w, w + 8, ... of the stage; a lane owns the
+//   warps 0..15  consumers: warp w owns rows w, w + 16, ... of the stage; a lane owns the
 //                16-byte units lane, lane + 32, ... of a row, decodes through the
 //                conflict-free byte-pair table, FMAs against the activation row it keeps in
-//                registers, applies the block scale once per unit, warp-shuffle reduces.
+//                registers as bf16 pairs, applies the block scale once per unit, warp-shuffle
+//                reduces.  Sixteen warps because the loop is latency-bound, not issue-bound.
 //
 // Summation order per output element is the same as in stream_kernel.cuh, so both kernels
 // give bit-identical results.
@@ -24,7 +25,7 @@
 
 namespace gnf4b {
 
-constexpr int kDConsumerWarps = 8;
+constexpr int kDConsumerWarps = 16;
 constexpr int kDThreads = (kDConsumerWarps + 1) * 32;
 constexpr int kDMaxStages = 8;
 
@@ -46,28 +47,35 @@ __host__ __device__ inline size_t decode_smem_bytes(int slot_bytes, int stages, 
     return (size_t)kSTableBytes + (size_t)stages * slot_bytes + 256 + (size_t)(2 * g_cache + 1) * 4;
 }
 
-// Two weight rows at once against the same activation registers: two independent sets of
-// FMA chains and twice the table lookups in flight per lane.  Each row is summed exactly as
-// unit_dot_regs sums it.
-__device__ __forceinline__ void unit_dot_regs2(const uint4 wa, const uint4 wb, const float* a32, uint32_t tab_lane,
-                                               float* ra, float* rb) {
-    const uint32_t xa[4] = {wa.x, wa.y, wa.z, wa.w};
-    const uint32_t xb[4] = {wb.x, wb.y, wb.z, wb.w};
-    float pa[4] = {0.f, 0.f, 0.f, 0.f}, pb[4] = {0.f, 0.f, 0.f, 0.f};
+// One unit (16 packed bytes = 32 elements) against the activation row kept in registers as
+// 16 bf16 pairs (widened on use: a bf16 is the top half of its fp32).  Same four partial
+// sums and the same order as unit_dot_regs of the streaming kernel, so the bits agree.
+__device__ __forceinline__ float2 ld_table(uint32_t addr) {
+    // the pair table is written once before the consumers' barrier and never again, so this
+    // load may be scheduled freely (no volatile, no memory clobber)
+    float2 v;
+    asm("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+    return v;
+}
+
+__device__ __forceinline__ float unit_dot_bf16(const uint4 wv, const uint32_t* a16, uint32_t tab_lane) {
+    const uint32_t words[4] = {wv.x, wv.y, wv.z, wv.w};
+    float2 p[16];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) p[i * 4 + b] = ld_table(tab_lane + prmt(words[i], 0u, 0x4404u | (b << 4)));
+    float part[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
-            const float2 p = ld_shared_f32x2(tab_lane + prmt(xa[i], 0u, 0x4404u | (b << 4)));
-            const float2 q = ld_shared_f32x2(tab_lane + prmt(xb[i], 0u, 0x4404u | (b << 4)));
-            pa[b] = fmaf(p.x, a32[i * 8 + b * 2], pa[b]);
-            pb[b] = fmaf(q.x, a32[i * 8 + b * 2], pb[b]);
-            pa[b] = fmaf(p.y, a32[i * 8 + b * 2 + 1], pa[b]);
-            pb[b] = fmaf(q.y, a32[i * 8 + b * 2 + 1], pb[b]);
+            const uint32_t ab = a16[i * 4 + b];
+            part[b] = fmaf(p[i * 4 + b].x, __uint_as_float(ab << 16), part[b]);
+            part[b] = fmaf(p[i * 4 + b].y, __uint_as_float(ab & 0xffff0000u), part[b]);
         }
     }
-    *ra = (pa[0] + pa[1]) + (pa[2] + pa[3]);
-    *rb = (pb[0] + pb[1]) + (pb[2] + pb[3]);
+    return (part[0] + part[1]) + (part[2] + part[3]);
 }
 
 template <int SDT>
@@ -187,46 +195,45 @@ __global__ void __launch_bounds__(kDThreads, 1) decode_gemv_kernel(const DecodeA
     DGroup grp;
     grp.valid = false;
     grp.row0 = 0;
-    float a_reg[AU * 32];
+    uint32_t a16[AU * 16];         // the group's activation row, bf16 pairs, units lane, lane + 32, ...
 
-    // The first group's activation row is requested before the table is built, so its
-    // global-memory latency overlaps the table construction.
-    auto load_a = [&](const DGroup& gr, uint4 (&raw)[AU * 4]) {
+    auto load_a = [&](const DGroup& gr) {
         const uint8_t* xrow = reinterpret_cast<const uint8_t*>(a.g.x) + (int64_t)gr.row0 * a.g.K * 2;
 #pragma unroll
         for (int q = 0; q < AU; ++q) {
             const int U = lane + 32 * q;
 #pragma unroll
-            for (int v = 0; v < 4; ++v)
-                raw[q * 4 + v] = (gr.valid && U < n_units)
-                                     ? __ldg(reinterpret_cast<const uint4*>(xrow + (int64_t)U * 64 + v * 16))
-                                     : make_uint4(0, 0, 0, 0);
+            for (int v = 0; v < 4; ++v) {
+                const uint4 raw = (gr.valid && U < n_units)
+                                      ? __ldg(reinterpret_cast<const uint4*>(xrow + (int64_t)U * 64 + v * 16))
+                                      : make_uint4(0, 0, 0, 0);
+                a16[q * 16 + v * 4 + 0] = raw.x;
+                a16[q * 16 + v * 4 + 1] = raw.y;
+                a16[q * 16 + v * 4 + 2] = raw.z;
+                a16[q * 16 + v * 4 + 3] = raw.w;
+            }
         }
     };
-    auto cvt_a = [&](const uint4 (&raw)[AU * 4]) {
-#pragma unroll
-        for (int i = 0; i < AU * 4; ++i) cvt8(raw[i], a.g.x_dtype, &a_reg[i * 8]);
-    };
+    // The first group's activation row is requested before the table is built, so its
+    // global-memory latency overlaps the table construction.
+    if (item_lo < item_hi) {
+        grp = decode_group(a, s_grp, g);
+        cur_g = g;
+    }
+    load_a(grp);
     {
-        uint4 raw[AU * 4];
-        if (item_lo < item_hi) {
-            grp = decode_group(a, s_grp, g);
-            cur_g = g;
-        }
-        load_a(grp, raw);
         // pair table: tab[byte][slot], 32 slots of float2 per byte, all holding the same pair,
         // so a lane reading slot == its lane id never conflicts with another lane.  A half
         // warp writes one byte's 256-byte row per step with 16-byte stores.
         const int half = lane >> 4, hl = lane & 15;
 #pragma unroll 4
-        for (int j = 0; j < 32; j += 2) {
-            const int b = warp * 32 + j + half;
+        for (int j = 0; j < 256 / kDConsumerWarps; j += 2) {
+            const int b = warp * (256 / kDConsumerWarps) + j + half;
             const float2 p = byte_pair<FMT>(b);
             asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(smem_u32(tab_raw) + b * 256 + hl * 16),
                          "f"(p.x), "f"(p.y), "f"(p.x), "f"(p.y)
                          : "memory");
         }
-        cvt_a(raw);
     }
     named_bar_sync(1, kDConsumerWarps * 32);
 
@@ -239,49 +246,29 @@ __global__ void __launch_bounds__(kDThreads, 1) decode_gemv_kernel(const DecodeA
         if (cur_g != g) {
             grp = decode_group(a, s_grp, g);
             cur_g = g;
-            uint4 raw[AU * 4];
-            load_a(grp, raw);
-            cvt_a(raw);
+            load_a(grp);
         }
         if (!poisoned && !mbar_wait_bounded(full_bar + stage, phase, abort_flag)) poisoned = true;
         if (!poisoned && grp.valid) {
             const uint32_t st = smem_u32(ring + (size_t)stage * a.slot_bytes);
             const int n0 = tile * R;
             const int rows = min(R, (int)(a.g.N - n0));
-            // rows of the stage are taken two at a time: (r, r + 8)
-            for (int r = warp; r < rows; r += 2 * kDConsumerWarps) {
-                const bool two = r + kDConsumerWarps < rows;
-                const int rb = two ? r + kDConsumerWarps : r;
-                const uint32_t wrow_a = st + (uint32_t)(r * a.row_bytes);
-                const uint32_t wrow_b = st + (uint32_t)(rb * a.row_bytes);
-                const uint32_t srow_a = st + (uint32_t)(R * a.row_bytes + r * a.scale_row_bytes);
-                const uint32_t srow_b = st + (uint32_t)(R * a.row_bytes + rb * a.scale_row_bytes);
-                float acc_a = 0.f, acc_b = 0.f;
+            for (int r = warp; r < rows; r += kDConsumerWarps) {
+                const uint32_t wrow = st + (uint32_t)(r * a.row_bytes);
+                const uint32_t srow = st + (uint32_t)(R * a.row_bytes + r * a.scale_row_bytes);
+                float acc = 0.f;
 #pragma unroll
                 for (int q = 0; q < AU; ++q) {
                     const int u = lane + 32 * q;
                     if (u < n_units) {
-                        const uint4 wa = ld_shared_u32x4(wrow_a + u * 16);
-                        const uint4 wb = ld_shared_u32x4(wrow_b + u * 16);
-                        const int si = (FMT == GNF4B_FMT_NF4) ? (u >> 1) : u;
-                        const float sa = ld_shared_scale<SDT>(srow_a, si);
-                        const float sb = ld_shared_scale<SDT>(srow_b, si);
-                        float da, db;
-                        unit_dot_regs2(wa, wb, &a_reg[q * 32], tab_lane, &da, &db);
-                        acc_a += da * sa;
-                        acc_b += db * sb;
+                        const uint4 wv = ld_shared_u32x4(wrow + u * 16);
+                        const float sc = ld_shared_scale<SDT>(srow, (FMT == GNF4B_FMT_NF4) ? (u >> 1) : u);
+                        acc += unit_dot_bf16(wv, &a16[q * 16], tab_lane) * sc;
                     }
                 }
 #pragma unroll
-                for (int o = 16; o > 0; o >>= 1) {
-                    acc_a += __shfl_xor_sync(0xffffffffu, acc_a, o);
-                    acc_b += __shfl_xor_sync(0xffffffffu, acc_b, o);
-                }
-                if (lane == 0) {
-                    uint16_t* dst = out_bf + (int64_t)grp.row0 * a.g.N + n0;
-                    dst[r] = f32_to_bf16_bits(acc_a);
-                    if (two) dst[rb] = f32_to_bf16_bits(acc_b);
-                }
+                for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                if (lane == 0) out_bf[(int64_t)grp.row0 * a.g.N + n0 + r] = f32_to_bf16_bits(acc);
             }
         }
         __syncwarp();

@@ -162,13 +162,30 @@ static int make_plan(int fmt, int op, int64_t T, int32_t G, int64_t N, int64_t K
     return GNF4B_OK;
 }
 
+// cudaFuncSetAttribute is per device and not free; raise a kernel's dynamic shared-memory
+// limit only when a launch needs more than was already granted on this device.
+template <typename F>
+static cudaError_t ensure_smem(F kfn, size_t smem, int* granted /*[64], zero-initialised*/) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    dev &= 63;
+    if ((int)smem > granted[dev]) {
+        e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        granted[dev] = (int)smem;
+    }
+    return cudaSuccess;
+}
+
 // ------------------------------------------------------------------ launches
 template <int FMT, int SDT>
 static cudaError_t launch_stream_au(const StreamArgs& sa, int au, int grid, size_t smem, cudaStream_t st) {
 #define GNF4B_LAUNCH_AU(AUV)                                                                          \
     do {                                                                                              \
         auto kfn = stream_gemm_kernel<FMT, SDT, AUV>;                                                 \
-        cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        static int granted[64];                                                                       \
+        cudaError_t e = ensure_smem(kfn, smem, granted);                                              \
         if (e != cudaSuccess) return e;                                                               \
         kfn<<<grid, kSThreads, smem, st>>>(sa);                                                       \
         return cudaGetLastError();                                                                    \
@@ -184,7 +201,8 @@ static cudaError_t launch_decode_au(const DecodeArgs& da, int au, int grid, size
 #define GNF4B_LAUNCH_D(AUV)                                                                           \
     do {                                                                                              \
         auto kfn = decode_gemv_kernel<FMT, SDT, AUV>;                                                 \
-        cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        static int granted[64];                                                                       \
+        cudaError_t e = ensure_smem(kfn, smem, granted);                                              \
         if (e != cudaSuccess) return e;                                                               \
         kfn<<<grid, kDThreads, smem, st>>>(da);                                                       \
         return cudaGetLastError();                                                                    \
@@ -350,12 +368,13 @@ int gnf4b_gemm_grouped(int fmt, int op, const void* x, int x_dtype, int64_t T, c
         const bool contiguous = w_stride_n == row_bytes && s_stride_n == K / blk &&
                                 (((uintptr_t)W | (uint64_t)w_stride_e) & 15) == 0 &&
                                 (((uintptr_t)S | (uint64_t)(s_stride_e * elt)) & 15) == 0 && ((8 * srow) & 15) == 0;
-        if (max_rows == 1 && p.split_k == 1 && K <= 3072 && (N % 8) == 0 && contiguous && G <= T) {
+        if (max_rows == 1 && p.split_k == 1 && K <= 3072 && (N % 8) == 0 && contiguous &&
+            x_dtype == GNF4B_X_BF16) {
             DecodeArgs da;
             da.g = g;
-            // rows per stage: 16 (two per consumer warp, processed together), more for short rows
-            const int m = (int)std::max<int64_t>(2, std::min<int64_t>(4, 16384 / (8 * row_bytes)));
-            da.rows_per_stage = 8 * m;
+            // rows per stage: one per consumer warp, more for short rows
+            const int m = (int)std::max<int64_t>(1, std::min<int64_t>(4, 16384 / (kDConsumerWarps * row_bytes)));
+            da.rows_per_stage = kDConsumerWarps * m;
             da.tiles_per_group = (int32_t)ceil_div(N, da.rows_per_stage);
             da.row_bytes = (int32_t)row_bytes;
             da.scale_row_bytes = (int32_t)srow;

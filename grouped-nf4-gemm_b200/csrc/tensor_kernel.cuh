@@ -1,13 +1,13 @@
 // tcgen05 / TMEM grouped GEMM for prefill-sized groups, forward and dgrad.
 //
-// Persistent, warp-specialised, one CTA per SM (448 threads):
+// Persistent, warp-specialised, one CTA per SM (704 threads):
 //   warp 0      TMA producer: activation tiles [128 rows x 64 contraction] per stage via
 //               cp.async.bulk.tensor (128-byte swizzle), counted on full_a[stage]
 //   warp 1      MMA issuer: one lane issues tcgen05.mma (M=128, N=128, K=16, bf16 x bf16,
 //               fp32 accumulate in TMEM); tcgen05.commit frees the stage / publishes the tile
 //   warps 2-5   epilogue: tcgen05.ld of the accumulator (one TMEM lane quarter per warp),
 //               one bf16 rounding, masked stores for ragged rows / columns
-//   warps 6-13  weight decode: packed nibbles + block scales straight from global memory
+//   warps 6-21  weight decode: packed nibbles + block scales straight from global memory
 //               (prefetched two stages ahead) -> bf16 tiles written into shared memory in the
 //               UMMA canonical 128-byte-swizzled layout.  MXFP4 decodes exactly to one bf16
 //               tile.  NF4 writes hi = bf16(w) and lo = bf16(w - hi) with w = fp32(LUT*absmax)
@@ -37,7 +37,7 @@ constexpr int kTBM = 128;             // rows per row tile (UMMA M)
 constexpr int kTBC = 128;             // output columns per item (UMMA N)
 constexpr int kTBR = 64;              // contraction elements per stage
 constexpr int kTMT = 2;               // row tiles per item
-constexpr int kTDecodeWarps = 8;
+constexpr int kTDecodeWarps = 16;
 constexpr int kTThreads = (2 + 4 + kTDecodeWarps) * 32;
 constexpr int kTATile = kTBM * kTBR * 2;        // 16 KiB
 constexpr int kTBTile = kTBC * kTBR * 2;        // 16 KiB
@@ -199,42 +199,47 @@ __device__ __forceinline__ bool next_item(const TensorArgs& a, ItemCursor& cur, 
     return false;
 }
 
-// 16 packed bytes (32 elements) of one weight row.  valid = false -> zeros (code 7 of NF4
-// is 0.0 but a ZERO BYTE is not, so padding is produced after decode, never before).
-__device__ __forceinline__ uint4 load_packed16(const uint8_t* p, int w_align) {
-    if (w_align >= 16) return __ldg(reinterpret_cast<const uint4*>(p));
-    uint4 v;
+// 8 packed bytes (16 elements) of one weight row.
+__device__ __forceinline__ uint2 load_packed8(const uint8_t* p, int w_align) {
+    if (w_align >= 8) return __ldg(reinterpret_cast<const uint2*>(p));
+    uint2 v;
     if (w_align >= 4) {
         const uint32_t* q = reinterpret_cast<const uint32_t*>(p);
-        v.x = __ldg(q); v.y = __ldg(q + 1); v.z = __ldg(q + 2); v.w = __ldg(q + 3);
+        v.x = __ldg(q);
+        v.y = __ldg(q + 1);
     } else {
-        uint32_t w[4];
+        uint32_t w[2];
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
+        for (int i = 0; i < 2; ++i)
             w[i] = (uint32_t)__ldg(p + 4 * i) | ((uint32_t)__ldg(p + 4 * i + 1) << 8) |
                    ((uint32_t)__ldg(p + 4 * i + 2) << 16) | ((uint32_t)__ldg(p + 4 * i + 3) << 24);
-        v = make_uint4(w[0], w[1], w[2], w[3]);
+        v = make_uint2(w[0], w[1]);
     }
     return v;
 }
 
-// Decode 32 elements and store them as four 16-byte chunks (8 bf16 each) of a swizzled
-// 128-byte row.  row_addr = shared address of the row, chunk0 = first chunk index (0 or 4),
-// r7 = row & 7 (the swizzle key).  lo_delta = byte distance from the hi tile to the lo tile.
+// Decode 16 elements and store them as two 16-byte chunks (8 bf16 each) of a swizzled
+// 128-byte row.  row_addr = shared address of the row, chunk0 = first chunk index, r7 =
+// row & 7 (the swizzle key), lo_delta = byte distance from the hi tile to the lo tile.
+// Padding (rows past N, columns past K) arrives with scale 0 and decodes to zeros; it must
+// not be produced from zero BYTES, which are code 0 = -1.0 in NF4.
+//   NF4 table: lut[code][lane] fp32 (one copy of the 16-entry codebook per lane).
+//   MXFP4 table: tab[byte][lane] bf16x2 of the doubled e2m1 pair.
 template <int FMT>
-__device__ __forceinline__ void decode_store32(const uint4 pk, float scale, bool valid, uint32_t tab_lane,
-                                               uint32_t row_addr, int chunk0, int r7, uint32_t lo_delta) {
-    const uint32_t w[4] = {pk.x, pk.y, pk.z, pk.w};
+__device__ __forceinline__ void decode_store16(const uint2 pk, float scale, uint32_t tab_lane, uint32_t row_addr,
+                                               int chunk0, int r7, uint32_t lo_delta) {
+    const uint32_t w[2] = {pk.x, pk.y};
     if (FMT == GNF4B_FMT_NF4) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < 2; ++i) {
             uint32_t hi[4], lo[4];
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
-                const uint32_t off = (b == 0) ? ((w[i] << 7) & 0x7f80u) : ((w[i] >> (8 * b - 7)) & 0x7f80u);
-                const float2 p = ld_shared_f32x2(tab_lane + off);
-                const float w0 = valid ? p.x * scale : 0.f;
-                const float w1 = valid ? p.y * scale : 0.f;
+                // even element = high nibble of byte b, odd element = low nibble; offset = code * 128
+                const uint32_t off_e = (b == 0) ? ((w[i] << 3) & 0x780u) : ((w[i] >> (8 * b - 3)) & 0x780u);
+                const uint32_t off_o = (b == 0) ? ((w[i] << 7) & 0x780u) : ((w[i] >> (8 * b - 7)) & 0x780u);
+                const float w0 = ld_shared_f32(tab_lane + off_e) * scale;
+                const float w1 = ld_shared_f32(tab_lane + off_o) * scale;
                 hi[b] = pack_bf16x2(w1, w0);
                 const float r0 = w0 - __uint_as_float(hi[b] << 16);
                 const float r1 = w1 - __uint_as_float(hi[b] & 0xffff0000u);
@@ -245,12 +250,12 @@ __device__ __forceinline__ void decode_store32(const uint4 pk, float scale, bool
             st_shared_v4(addr + lo_delta, lo[0], lo[1], lo[2], lo[3]);
         }
     } else {
-        // scale = 2^(e-128) as a bf16 pair; the table holds the doubled e2m1 values, so the
-        // bf16 product is exactly value * 2^(e-127)
+        // scale = 2^(e-128) as a bf16 pair (0 for padding); the table holds the doubled e2m1
+        // values, so the bf16 product is exactly value * 2^(e-127)
         const uint32_t s16 = __float_as_uint(scale) >> 16;
-        const uint32_t s2 = valid ? (s16 | (s16 << 16)) : 0u;
+        const uint32_t s2 = s16 | (s16 << 16);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < 2; ++i) {
             uint32_t v[4];
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
@@ -298,12 +303,11 @@ tensor_gemm_kernel(const TensorArgs a, const __grid_constant__ CUtensorMap x_map
         tmem_alloc(tmem_slot, kTTmemCols);
         tmem_relinquish();
     }
-    // decode table: [byte][slot]; NF4: 16 slots of float2 (LUT pair), MXFP4: 32 slots of
-    // bf16x2 (doubled e2m1 pair).  Every slot of a byte holds the same entry; a lane reads
-    // its own slot, so lookups never conflict.
+    // decode table, one copy per lane so lookups never conflict: NF4 lut[code][lane] fp32,
+    // MXFP4 tab[byte][lane] bf16x2 (doubled e2m1 pair).
     if (FMT == GNF4B_FMT_NF4) {
-        float2* tab = reinterpret_cast<float2*>(tab_raw);
-        for (int i = threadIdx.x; i < 256 * 16; i += kTThreads) tab[i] = byte_pair<FMT>(i >> 4);
+        float* tab = reinterpret_cast<float*>(tab_raw);
+        for (int i = threadIdx.x; i < 16 * 32; i += kTThreads) tab[i] = kNf4Lut[i >> 5];
     } else {
         uint32_t* tab = reinterpret_cast<uint32_t*>(tab_raw);
         for (int i = threadIdx.x; i < 256 * 32; i += kTThreads) {
@@ -434,16 +438,19 @@ tensor_gemm_kernel(const TensorArgs a, const __grid_constant__ CUtensorMap x_map
         }
     } else {
         // ------------------------------------------------------------ weight decode
-        const int dt = threadIdx.x - 6 * 32;       // 0..255
-        // forward: row = dt/2 of 128, half dt%2 -> chunks 4*(dt%2)..  (32 bytes per row per stage)
-        // dgrad:   row = dt/4 of 64, quarter dt%4 -> block (dt%4)/2, chunks 4*((dt%4)%2).. (64 bytes per row)
-        const int trow = (OP == GNF4B_OP_FWD) ? (dt >> 1) : (dt >> 2);
-        const int part = (OP == GNF4B_OP_FWD) ? (dt & 1) : (dt & 3);
-        const int chunk0 = (part & 1) * 4;
-        const uint32_t tile_off = (OP == GNF4B_OP_FWD) ? (uint32_t)(trow * 128)
-                                                       : (uint32_t)((part >> 1) * 8192 + trow * 128);
+        const int dt = threadIdx.x - 6 * 32;       // 0..511, 16 elements (8 packed bytes) each
+        // forward: stage tile = 128 weight rows x 64 k.  row = dt / 4, k offset = (dt % 4) * 16.
+        // dgrad:   stage tile = 64 weight rows x 128 k, stored as two 64-column blocks of 8 KiB.
+        //          block = dt / 256, row = (dt % 256) / 4, k offset = block * 64 + (dt % 4) * 16.
+        // Either way a quarter warp covers two rows x four 32-byte pieces, whose swizzled
+        // 16-byte chunks fall into eight different bank groups.
+        const int blk = (OP == GNF4B_OP_FWD) ? 0 : (dt >> 8);
+        const int trow = (OP == GNF4B_OP_FWD) ? (dt >> 2) : ((dt & 255) >> 2);
+        const int koff = blk * 64 + (dt & 3) * 16;
+        const int chunk0 = (dt & 3) * 2;
+        const uint32_t tile_off = (uint32_t)(blk * 8192 + trow * 128);
         const int r7 = trow & 7;
-        const uint32_t tab_lane = smem_u32(tab_raw) + ((FMT == GNF4B_FMT_NF4) ? (lane & 15) * 8 : lane * 4);
+        const uint32_t tab_lane = smem_u32(tab_raw) + lane * 4;
         ItemCursor cur;
         TItem it;
         uint32_t stage = 0, phase = 0;
@@ -451,26 +458,24 @@ tensor_gemm_kernel(const TensorArgs a, const __grid_constant__ CUtensorMap x_map
         for (int64_t id = blockIdx.x; ok && next_item(a, cur, id, &it); id += gridDim.x) {
             const uint8_t* w_e = a.g.W + (int64_t)it.eid * a.g.w_se;
             const int64_t s_e = (int64_t)it.eid * a.g.s_se;
-            // Element coordinates of this thread's 32 elements in stage rb:
-            //   forward: n = c0 + trow,        k = rb*64 + part*32
-            //   dgrad:   n = rb*64 + trow,     k = c0 + part*32
-            auto fetch = [&](int rb, uint4* pk, float* sc) -> bool {
+            // Element coordinates of this thread's 16 elements in stage rb:
+            //   forward: n = c0 + trow,        k = rb*64 + koff
+            //   dgrad:   n = rb*64 + trow,     k = c0 + koff
+            auto fetch = [&](int rb, uint2* pk, float* sc) {
                 const int64_t n = (OP == GNF4B_OP_FWD) ? (int64_t)it.c0 + trow : (int64_t)rb * kTBR + trow;
-                const int64_t k = (OP == GNF4B_OP_FWD) ? (int64_t)rb * kTBR + part * 32 : (int64_t)it.c0 + part * 32;
-                const bool valid = rb < a.r_blocks && n < a.g.N && k < a.g.K;
-                if (valid) {
-                    *pk = load_packed16(w_e + n * a.g.w_sn + (k >> 1), a.w_align);
+                const int64_t k = (OP == GNF4B_OP_FWD) ? (int64_t)rb * kTBR + koff : (int64_t)it.c0 + koff;
+                if (rb < a.r_blocks && n < a.g.N && k < a.g.K) {
+                    *pk = load_packed8(w_e + n * a.g.w_sn + (k >> 1), a.w_align);
                     *sc = load_scale<SDT>(a.g.S, s_e + n * a.g.s_sn + k / scale_blk);
                 } else {
-                    *pk = make_uint4(0, 0, 0, 0);
-                    *sc = 0.f;
+                    *pk = make_uint2(0, 0);
+                    *sc = 0.f;                 // padding decodes to zeros
                 }
-                return valid;
             };
-            uint4 pk0, pk1;
+            uint2 pk0, pk1;
             float sc0, sc1;
-            bool v0 = fetch(0, &pk0, &sc0);
-            bool v1 = fetch(1, &pk1, &sc1);
+            fetch(0, &pk0, &sc0);
+            fetch(1, &pk1, &sc1);
             for (int rb = 0; rb < a.r_blocks && ok; rb += 2) {
 #pragma unroll
                 for (int u = 0; u < 2; ++u) {
@@ -480,11 +485,11 @@ tensor_gemm_kernel(const TensorArgs a, const __grid_constant__ CUtensorMap x_map
                             const uint32_t row_addr =
                                 smem_u32(smem + (size_t)stage * kStageBytes) + kTMT * kTATile + tile_off;
                             if (u == 0) {
-                                decode_store32<FMT>(pk0, sc0, v0, tab_lane, row_addr, chunk0, r7, kLoDelta);
-                                v0 = fetch(rb + 2, &pk0, &sc0);
+                                decode_store16<FMT>(pk0, sc0, tab_lane, row_addr, chunk0, r7, kLoDelta);
+                                fetch(rb + 2, &pk0, &sc0);
                             } else {
-                                decode_store32<FMT>(pk1, sc1, v1, tab_lane, row_addr, chunk0, r7, kLoDelta);
-                                v1 = fetch(rb + 3, &pk1, &sc1);
+                                decode_store16<FMT>(pk1, sc1, tab_lane, row_addr, chunk0, r7, kLoDelta);
+                                fetch(rb + 3, &pk1, &sc1);
                             }
                             fence_proxy_async();
                             __syncwarp();
@@ -531,8 +536,15 @@ static EncodeTiledFn encode_tiled_fn() {
 template <int FMT, int SDT, int OP>
 static int launch_tensor_t(const TensorArgs& ta, const CUtensorMap& map, int sm_count, size_t smem, cudaStream_t st) {
     auto kfn = tensor_gemm_kernel<FMT, SDT, OP>;
-    if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-        return GNF4B_ECUDA;
+    static int granted[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return GNF4B_ECUDA;
+    dev &= 63;
+    if ((int)smem > granted[dev]) {
+        if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return GNF4B_ECUDA;
+        granted[dev] = (int)smem;
+    }
     kfn<<<sm_count, kTThreads, smem, st>>>(ta, map);
     return cudaPeekAtLastError() == cudaSuccess ? GNF4B_OK : GNF4B_ECUDA;
 }

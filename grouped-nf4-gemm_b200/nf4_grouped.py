@@ -75,6 +75,7 @@ class _PinnedIndexArena:
         self.off = 0
         self._retired: list = []
         self._ring = torch.empty(self.RING_SLOTS * self.RING_SLOT_INTS, dtype=torch.int32, pin_memory=True)
+        self._ring_np = self._ring.numpy()          # same memory; list -> pinned bytes without a torch op
         self._ring_evt = [None] * self.RING_SLOTS
         self._ring_next = 0
 
@@ -127,7 +128,8 @@ class _PinnedIndexArena:
         evt = self._ring_evt[i]
         if evt is not None:
             evt.synchronize()
-        return self._ring[i * self.RING_SLOT_INTS: i * self.RING_SLOT_INTS + n], i
+        lo = i * self.RING_SLOT_INTS
+        return self._ring[lo: lo + n], i
 
     def staged(self, slot: int):
         if self._ring_evt[slot] is None:
@@ -169,17 +171,18 @@ def to_device_i32(seqs, device):
         packed = torch.tensor(_flat_ints(seqs), dtype=torch.int32, device=dev)
     else:
         ar = _arena(dev)
-        vals = torch.tensor(_flat_ints(seqs), dtype=torch.int32)
+        flat = _flat_ints(seqs)
         if ar._capturing():
             host, _ = ar.take(total)
-            host.copy_(vals)
+            host.copy_(torch.tensor(flat, dtype=torch.int32))
             packed = host.to(dev, non_blocking=True)
         else:
             host, slot = ar.stage(total)
             if host is None:
-                packed = vals.to(dev)
+                packed = torch.tensor(flat, dtype=torch.int32).to(dev)
             else:
-                host.copy_(vals)
+                lo = slot * ar.RING_SLOT_INTS
+                ar._ring_np[lo: lo + total] = flat
                 packed = host.to(dev, non_blocking=True)
                 ar.staged(slot)
     out, o = [], 0
@@ -384,7 +387,8 @@ def _launch(fmt, op, x, W, S, sizes, expert_ids, n_out, *, split_k=None, path=_g
         raise TypeError(f"packed weights must be uint8, got {W.dtype}")
     if W.device != dev or S.device != dev:
         raise ValueError("activations, packed weights and scales must live on the same device")
-    x = x.contiguous()
+    if not x.is_contiguous():
+        x = x.contiguous()
     if x.data_ptr() % 16:
         x = x.clone()
     if W.stride(2) != 1:
@@ -404,7 +408,11 @@ def _launch(fmt, op, x, W, S, sizes, expert_ids, n_out, *, split_k=None, path=_g
     if T == 0:
         return out
     lib = _gnf4b.load()
-    with torch.cuda.device(dev):
+    prev = -1
+    if dev.index is not None and dev.index != torch.cuda.current_device():
+        prev = torch.cuda.current_device()          # the C library launches on the current device
+        torch.cuda.set_device(dev)
+    try:
         off_t, ids_t, G, max_rows = _group_tables(sizes, expert_ids, T, E, dev, group_offsets, max_rows)
         if G == 0:
             return out
@@ -418,7 +426,11 @@ def _launch(fmt, op, x, W, S, sizes, expert_ids, n_out, *, split_k=None, path=_g
             S.data_ptr(), sdt, S.stride(0), S.stride(1), off_t.data_ptr(), ids_t.data_ptr(),
             G, E, N, K, max_rows, out.data_ptr(), ws.data_ptr() if ws is not None else None,
             need, _status_word(dev).data_ptr(), flags, torch.cuda.current_stream(dev).cuda_stream)
-    _gnf4b.check(rc, "gnf4b_gemm_grouped")
+    finally:
+        if prev >= 0:
+            torch.cuda.set_device(prev)
+    if rc:
+        _gnf4b.check(rc, "gnf4b_gemm_grouped")
     return out
 
 

@@ -1,0 +1,82 @@
+"""Expert-parallel layer on real GPUs (needs >= 2): two NCCL ranks must reproduce the
+single-GPU layer on the same seeds.  Rows are computed by the same kernels whatever the
+sharding, but the planner may pick a different kernel for a rank's smaller groups, so the
+comparison is at bf16 resolution, plus a check against the fp64 oracle on rank 0."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _problem():
+    import synth
+    E, H, I, k, M = 16, 256, 128, 4, 96
+    gen = torch.Generator().manual_seed(31)
+    gu = synth.nf4_stack(E, 2 * I, H, gen, scale=0.05)
+    dn = synth.nf4_stack(E, H, I, gen, scale=0.05)
+    return E, H, I, k, M, gu, dn
+
+
+def _tokens(rank, E, H, k, M):
+    import synth
+    gen = torch.Generator().manual_seed(500 + rank)
+    logits = torch.randn(M, E, generator=gen)
+    x = torch.randn(M, H, generator=gen).to(torch.bfloat16)
+    idx, w = synth.route_topk(logits, k)
+    return x, idx, w
+
+
+def _worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world)
+    try:
+        import ep_moe
+        import nf4_grouped
+        dev = torch.device("cuda", rank)
+        E, H, I, k, M, gu, dn = _problem()
+        el = E // world
+        sh = lambda t: (t[0][rank * el:(rank + 1) * el].to(dev), t[1][rank * el:(rank + 1) * el].to(dev))  # noqa: E731
+        layer = ep_moe.EPGroupedMoE(E, sh(gu), sh(dn), fmt="nf4")
+        x, idx, w = _tokens(rank, E, H, k, M)
+        y = layer.forward(x.to(dev), idx.to(dev), w.to(dev))
+        torch.cuda.synchronize()
+        q.put((rank, y.float().cpu().numpy(), nf4_grouped.last_status(dev)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpu_layer_matches_single_gpu_layer():
+    import ep_moe
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = {}
+    for _ in range(world):
+        r, y, status = q.get(timeout=300)
+        got[r] = y
+        assert status == 0
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    E, H, I, k, M, gu, dn = _problem()
+    dev = torch.device("cuda", 0)
+    single = ep_moe.EPGroupedMoE(E, (gu[0].to(dev), gu[1].to(dev)), (dn[0].to(dev), dn[1].to(dev)), fmt="nf4")
+    for r in range(world):
+        x, idx, w = _tokens(r, E, H, k, M)
+        want = single.forward(x.to(dev), idx.to(dev), w.to(dev)).float().cpu().numpy()
+        scale = np.abs(want).max()
+        assert np.abs(got[r] - want).max() <= 2 * 2 ** -8 * scale, r

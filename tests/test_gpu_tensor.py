@@ -49,10 +49,13 @@ def _clean():
 ])
 def test_prefill_nf4_vs_oracle(N, K, sizes, ids):
     B, A = make_stack(8, N, K, seed=N + K, device=DEV)
-    a = torch.randn(sum(sizes), K, device=DEV, dtype=torch.bfloat16)
+    gen = torch.Generator().manual_seed(N * 7 + K)
+    a = torch.randn(sum(sizes), K, generator=gen).to(torch.bfloat16).to(DEV)
     out = gemm_4bit_grouped(a, B, A, sizes, ids, path=T)
     ref = oracle_fwd64("nf4", a, B, A, sizes, ids)
-    assert rel_fro(out, ref) <= REL_FRO_TOL, rel_fro(out, ref)
+    # a handful of outputs cannot average the bf16 rounding error down: bound them by one half ulp
+    tol = REL_FRO_TOL if out.numel() >= 4096 else 2 ** -8
+    assert rel_fro(out, ref) <= tol, rel_fro(out, ref)
     # the planner's own choice and the streaming kernel agree with it at bf16 resolution
     auto = gemm_4bit_grouped(a, B, A, sizes, ids)
     st = gemm_4bit_grouped(a, B, A, sizes, ids, path=S)
