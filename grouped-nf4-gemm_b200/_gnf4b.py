@@ -86,6 +86,8 @@ def _declare(lib):
     lib.gnf4b_plan_split_k.argtypes = [C.c_int, C.c_int, i64, i32, i64, i64, i32, u32]
     lib.gnf4b_build_offsets.restype = C.c_int
     lib.gnf4b_build_offsets.argtypes = [vp, i32, vp, vp]
+    lib.gnf4b_upload_i32.restype = C.c_int
+    lib.gnf4b_upload_i32.argtypes = [vp, vp, i64, vp]
     lib.gnf4b_dequant.restype = C.c_int
     lib.gnf4b_dequant.argtypes = [C.c_int, vp, i64, i64, vp, C.c_int, i64, i64, i32, i64, i64, vp, vp]
     lib.gnf4b_device_info.restype = C.c_int
@@ -96,7 +98,7 @@ def _declare(lib):
 #: every symbol include/gnf4b.h declares
 EXPORTS = ("gnf4b_abi_version", "gnf4b_strerror", "gnf4b_last_cuda_error", "gnf4b_gemm_grouped",
            "gnf4b_gemm_grouped_noalloc",
-           "gnf4b_workspace_bytes", "gnf4b_plan_split_k", "gnf4b_build_offsets", "gnf4b_dequant",
+           "gnf4b_workspace_bytes", "gnf4b_plan_split_k", "gnf4b_build_offsets", "gnf4b_upload_i32", "gnf4b_dequant",
            "gnf4b_device_info")
 
 

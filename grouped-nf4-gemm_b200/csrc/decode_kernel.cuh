@@ -97,16 +97,12 @@ struct DGroup {
 };
 
 __device__ __forceinline__ DGroup decode_group(const DecodeArgs& a, const int32_t* s_grp, int g) {
-    int32_t row0, end, eid;
-    if (g < a.g_cache) {
-        row0 = s_grp[g];
-        end = s_grp[g + 1];
-        eid = s_grp[a.g_cache + 1 + g];
-    } else {
-        row0 = __ldg(a.g.off + g);
-        end = __ldg(a.g.off + g + 1);
-        eid = __ldg(a.g.eids + g);
-    }
+    // a group changes once per N / R items, so its three ints come straight from global
+    // memory (L1-cached) instead of a shared-memory copy that every thread would wait for
+    (void)s_grp;
+    const int32_t row0 = __ldg(a.g.off + g);
+    const int32_t end = __ldg(a.g.off + g + 1);
+    const int32_t eid = __ldg(a.g.eids + g);
     DGroup d;
     d.row0 = row0;
     d.eid = eid;
@@ -140,8 +136,6 @@ __global__ void __launch_bounds__(kDThreads, 1) decode_gemv_kernel(const DecodeA
         *abort_flag = 0;
         fence_barrier_init();
     }
-    for (int i = threadIdx.x; i < 2 * a.g_cache + 1; i += kDThreads)
-        s_grp[i] = (i <= a.g_cache) ? __ldg(a.g.off + i) : __ldg(a.g.eids + (i - a.g_cache - 1));
     __syncthreads();
 
     const int bid = (int)blockIdx.x;

@@ -463,6 +463,15 @@ int gnf4b_build_offsets(const int32_t* sizes, int32_t G, int32_t* group_offsets,
     return GNF4B_OK;
 }
 
+int gnf4b_upload_i32(const int32_t* host_src, int32_t* device_dst, int64_t n, void* cuda_stream) {
+    if (n < 0 || (n > 0 && (!host_src || !device_dst))) return GNF4B_EINVAL;
+    if (n == 0) return GNF4B_OK;
+    cudaError_t e = cudaMemcpyAsync(device_dst, host_src, (size_t)n * 4, cudaMemcpyHostToDevice,
+                                    reinterpret_cast<cudaStream_t>(cuda_stream));
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(group tables)");
+    return GNF4B_OK;
+}
+
 int gnf4b_dequant(int fmt, const uint8_t* W, int64_t w_stride_e, int64_t w_stride_n, const void* S,
                   int s_dtype, int64_t s_stride_e, int64_t s_stride_n, int32_t E, int64_t N, int64_t K,
                   float* out_f32, void* cuda_stream) {

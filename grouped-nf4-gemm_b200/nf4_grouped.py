@@ -147,6 +147,58 @@ def _arena(device) -> _PinnedIndexArena:
     return _ARENAS[key]
 
 
+class _IndexRing:
+    """Per (device, stream) staging for the group tables of eager calls: a pinned host ring
+    and a device ring of the same shape.  A call writes its ints into the next host slot
+    (numpy view, no torch op), issues ONE asynchronous copy to the matching device slot on
+    the call's stream and hands the kernel the device slot's address.  Slots are recycled
+    in blocks of eight; a block is reused only after the event recorded behind its last
+    copy has completed, and copies and kernels of one stream are ordered, so neither side
+    of a slot is overwritten while something still reads it."""
+
+    SLOTS, SLOT_INTS, BLOCK = 64, 4096, 8
+
+    def __init__(self, dev):
+        self.host = torch.empty(self.SLOTS * self.SLOT_INTS, dtype=torch.int32, pin_memory=True)
+        self.np = self.host.numpy()
+        self.dev = torch.empty(self.SLOTS * self.SLOT_INTS, dtype=torch.int32, device=dev)
+        self.host_ptr, self.dev_ptr = self.host.data_ptr(), self.dev.data_ptr()
+        self.events = [None] * (self.SLOTS // self.BLOCK)
+        self.next = 0
+
+    def upload(self, flat, lib, stream_ptr):
+        """-> device address of the uploaded ints, or 0 when they do not fit a slot."""
+        n = len(flat)
+        if n > self.SLOT_INTS:
+            return 0
+        i = self.next
+        self.next = (i + 1) % self.SLOTS
+        blk = i // self.BLOCK
+        if i % self.BLOCK == 0 and self.events[blk] is not None:
+            self.events[blk].synchronize()
+        lo = i * self.SLOT_INTS
+        self.np[lo: lo + n] = flat
+        rc = lib.gnf4b_upload_i32(self.host_ptr + lo * 4, self.dev_ptr + lo * 4, n, stream_ptr)
+        if rc:
+            _gnf4b.check(rc, "gnf4b_upload_i32")
+        if i % self.BLOCK == self.BLOCK - 1:
+            if self.events[blk] is None:
+                self.events[blk] = torch.cuda.Event()
+            self.events[blk].record()
+        return self.dev_ptr + lo * 4
+
+
+_RINGS: dict = {}
+
+
+def _index_ring(dev, stream_ptr):
+    key = (dev.index, stream_ptr)
+    r = _RINGS.get(key)
+    if r is None:
+        r = _RINGS[key] = _IndexRing(dev)
+    return r
+
+
 def _flat_ints(seqs):
     flat = []
     for s in seqs:
@@ -317,9 +369,10 @@ def last_status(device) -> int:
     return v
 
 
-def _group_tables(sizes, expert_ids, T: int, E: int, dev, group_offsets=None, max_rows=None):
-    """-> (group_offsets[G+1] dev, expert_ids[G] dev, G, max_rows).  Host inputs are checked
-    and travel in one transfer; device inputs are used where they are, with no host read."""
+def _group_tables(sizes, expert_ids, T: int, E: int, dev, group_offsets=None, max_rows=None, stream_ptr=0):
+    """-> (group_offsets[G+1] dev, expert_ids[G] dev, G, max_rows); the first two are tensors,
+    or plain device addresses on the eager host-list fast path.  Host inputs are checked and
+    travel in one transfer; device inputs are used where they are, with no host read."""
     ids_dev = torch.is_tensor(expert_ids) and expert_ids.is_cuda
     if group_offsets is not None:
         # caller-built device prefix sum: nothing to transfer, nothing to read back
@@ -355,6 +408,14 @@ def _group_tables(sizes, expert_ids, T: int, E: int, dev, group_offsets=None, ma
         if expert_ids.numel() != G:
             raise ValueError(f"sizes has {G} groups but expert_ids has {expert_ids.numel()}")
     if not sz_dev and not ids_dev:
+        capturing = False
+        try:
+            capturing = torch.cuda.is_current_stream_capturing()
+        except Exception:
+            pass
+        base = 0 if capturing else _index_ring(dev, stream_ptr).upload(offs + ids, _gnf4b.load(), stream_ptr)
+        if base:
+            return base, base + 4 * (G + 1), G, max_rows
         off_t, ids_t = to_device_i32((offs, ids), dev)
     elif not sz_dev:
         off_t = to_device_i32((offs,), dev)[0]
@@ -413,9 +474,12 @@ def _launch(fmt, op, x, W, S, sizes, expert_ids, n_out, *, split_k=None, path=_g
         prev = torch.cuda.current_device()          # the C library launches on the current device
         torch.cuda.set_device(dev)
     try:
-        off_t, ids_t, G, max_rows = _group_tables(sizes, expert_ids, T, E, dev, group_offsets, max_rows)
+        stream_ptr = torch.cuda.current_stream(dev).cuda_stream
+        off_t, ids_t, G, max_rows = _group_tables(sizes, expert_ids, T, E, dev, group_offsets, max_rows, stream_ptr)
         if G == 0:
             return out
+        off_p = off_t if isinstance(off_t, int) else off_t.data_ptr()
+        ids_p = ids_t if isinstance(ids_t, int) else ids_t.data_ptr()
         flags = path
         if split_k is not None:
             flags |= max(1, int(split_k)) << _gnf4b.SPLITK_SHIFT
@@ -423,9 +487,9 @@ def _launch(fmt, op, x, W, S, sizes, expert_ids, n_out, *, split_k=None, path=_g
         ws = torch.zeros(need, dtype=torch.uint8, device=dev) if need else None
         rc = lib.gnf4b_gemm_grouped(
             fmt, op, x.data_ptr(), xdt, T, W.data_ptr(), W.stride(0), W.stride(1),
-            S.data_ptr(), sdt, S.stride(0), S.stride(1), off_t.data_ptr(), ids_t.data_ptr(),
+            S.data_ptr(), sdt, S.stride(0), S.stride(1), off_p, ids_p,
             G, E, N, K, max_rows, out.data_ptr(), ws.data_ptr() if ws is not None else None,
-            need, _status_word(dev).data_ptr(), flags, torch.cuda.current_stream(dev).cuda_stream)
+            need, _status_word(dev).data_ptr(), flags, stream_ptr)
     finally:
         if prev >= 0:
             torch.cuda.set_device(prev)

@@ -145,6 +145,11 @@ int gnf4b_plan_split_k(int fmt, int op, int64_t T, int32_t G, int64_t N, int64_t
 int gnf4b_build_offsets(const int32_t* sizes, int32_t G, int32_t* group_offsets,
                         void* cuda_stream);
 
+/* Copy n int32 from (pinned) host memory to device memory on the stream, asynchronously:
+ * one cudaMemcpyAsync.  This is how the small group tables travel; it replaces the
+ * pageable / pinned-arena transfers of to_device_i32 (kernel/nf4_grouped.py:229-331). */
+int gnf4b_upload_i32(const int32_t* host_src, int32_t* device_dst, int64_t n, void* cuda_stream);
+
 /* Element decode of a whole stack with the SAME device decode routines the GEMM kernels
  * use: out_f32 [E, N, K] contiguous.  Counterpart of dequant_ref
  * (kernel/nf4_grouped.py:910-929) and dequant_mxfp4 (kernel/mxfp4_pack_ref.py:46-70);
