@@ -131,12 +131,18 @@ def make_steps(shape, tokens, n_steps, seed, zipf=None):
     return steps
 
 
-def build_layers(shape, n_layers, device, seed):
+def build_layers(shape, n_layers, device, seed, random_bytes=False):
     gen = torch.Generator().manual_seed(seed)
     layers = []
     for _ in range(n_layers):
         (n1, k1), (n2, k2) = shape.gate_up, shape.down
-        if shape.fmt == "nf4":
+        if shape.fmt == "nf4" and random_bytes:
+            # profiling aid: uniform random codes and absmax in [0.01, 0.06] instead of quantised
+            # N(0, 0.02) weights -- the kernels' timing does not depend on the values
+            mk = lambda n, k: (torch.randint(0, 256, (shape.experts, n, k // 2), dtype=torch.uint8, device=device),  # noqa: E731
+                               torch.rand(shape.experts, n, k // 64, device=device) * 0.05 + 0.01)
+            gu, dn = mk(n1, k1), mk(n2, k2)
+        elif shape.fmt == "nf4":
             gu = synth.nf4_stack(shape.experts, n1, k1, gen, device=device, fast=True)
             dn = synth.nf4_stack(shape.experts, n2, k2, gen, device=device, fast=True)
         else:
@@ -227,7 +233,7 @@ def run_gpu(args, shape, rank, world):
     torch.cuda.set_device(dev)
     fn = grouped(shape)
     K, W = args.steps, args.warmup
-    layers = build_layers(shape, args.layers, dev, seed=1234 + rank)
+    layers = build_layers(shape, args.layers, dev, seed=1234 + rank, random_bytes=args.random_bytes)
     steps = make_steps(shape, args.tokens, K + W, seed=99 + rank)
     dsteps = []
     for s in steps:
@@ -374,6 +380,8 @@ def main():
     ap.add_argument("--layers", type=int, default=16)
     ap.add_argument("--repeats", type=int, default=7)
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--random-bytes", action="store_true",
+                    help="NF4 stacks from uniform random bytes (few set-up kernels; for profiler captures)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
