@@ -11,6 +11,7 @@
 #include "stream_kernel.cuh"
 #include "decode_kernel.cuh"
 #include "tensor_kernel.cuh"
+#include "tensor_fwd_kernel.cuh"
 
 namespace gnf4b {
 
@@ -341,8 +342,13 @@ int gnf4b_gemm_grouped(int fmt, int op, const void* x, int x_dtype, int64_t T, c
     g.T = T; g.N = N; g.K = K; g.G = G; g.E = E; g.x_dtype = x_dtype; g.split_k = 1;
 
     if (p.path == GNF4B_PATH_TENSOR) {
-        rc = launch_tensor(fmt, op, s_dtype, g, max_rows, di.sm_count, di.smem_optin,
-                           align_class(W, w_stride_e, w_stride_n), st);
+        // forward: weight tile in tensor memory; dgrad (and GNF4B_FLAG_SMEM_OPERANDS): both operands
+        // in shared memory
+        if (op == GNF4B_OP_FWD && !(flags & GNF4B_FLAG_SMEM_OPERANDS))
+            rc = launch_tensor_fwd(fmt, s_dtype, g, di.sm_count, di.smem_optin, align_class(W, w_stride_e, w_stride_n), st);
+        else
+            rc = launch_tensor(fmt, op, s_dtype, g, max_rows, di.sm_count, di.smem_optin,
+                               align_class(W, w_stride_e, w_stride_n), st);
         if (rc == GNF4B_ECUDA) return cuda_fail(cudaGetLastError(), "tensor kernel launch");
         // A forward the tensor kernel declines (e.g. fp16 activations) still has a CUDA
         // kernel that takes it when the caller left the choice to the planner.

@@ -1,0 +1,431 @@
+// tcgen05 / TMEM grouped GEMM, forward only, weight tile resident in TENSOR MEMORY.
+//
+// The first tensor kernel (tensor_kernel.cuh) keeps both MMA operands in shared memory and is
+// bound by shared-memory bandwidth: per k-step the MMAs read their operands, the decode warps
+// read codebook entries and write hi/lo tiles, TMA writes activations -- all through the same
+// 128 B/clk.  Here the decoded weights never touch shared memory:
+//
+//   out^T[n, t] = sum_k W[n, k] * x[t, k]      (accumulator lane = weight row n, column = token t)
+//
+//   operand A = decoded weight tile [128 n x 16 k] bf16 in TMEM, written by the decode warps with
+//               tcgen05.st straight from registers (hi and, for NF4, lo = bf16(w - hi))
+//   operand B = activation tile [<=256 tokens x 16 k] bf16, K-major, 128-byte swizzled, in
+//               shared memory by TMA -- the only MMA operand read from shared memory
+//   D         = fp32 [128 lanes x <=256 columns] in TMEM
+//
+// Roles (704 threads, one CTA per SM, persistent):
+//   warp 0      TMA producer of activation tiles (two 128-row boxes per stage)
+//   warp 1      MMA issuer (one lane): per stage 4 k-steps x (hi [, lo]) tcgen05.mma with A in TMEM
+//   warps 2-5   epilogue: tcgen05.ld, neighbour lanes exchange one value so each writes a
+//               bf16 pair, stores are 64-byte coalesced along n (the output is transposed back here)
+//   warps 6-21  decode, two groups of 8 warps that take alternate stages: thread = (weight row,
+//               32 k): 16 packed bytes + one block scale from global memory (prefetched one own
+//               stage = two pipeline stages ahead, across item boundaries), one table lookup per
+//               byte, tcgen05.st of 16 columns (hi) + 16 columns (lo)
+//
+// TMEM budget (512 columns): 256 accumulator columns + 4 stages x 64 columns of A (hi 32 + lo 32).
+// Work item = (group, balanced chunk of <= 256 rows, 128-column tile of N), column tile fastest.
+#pragma once
+
+#include "tensor_kernel.cuh"
+
+namespace gnf4b {
+
+constexpr int kFStages = 4;
+constexpr int kFTok = 256;                     // tokens per item (UMMA N)
+constexpr int kFXTile = kFTok * kTBR * 2;      // 32 KiB of activations per stage
+constexpr int kFAcols = 64;                    // TMEM columns of A per stage (hi 32 + lo 32)
+constexpr int kFThreads = (2 + 4 + 16) * 32;
+
+// Lookup tables, one copy per lane so that no two lanes share a bank:
+//   NF4   tab[byte][lane] float2 = codebook values of the byte's two elements (64 KiB)
+//   MXFP4 tab[byte][lane] bf16x2 = doubled e2m1 values of the byte's two elements (32 KiB)
+__host__ __device__ inline size_t tensor_fwd_table_bytes(int fmt) { return fmt == GNF4B_FMT_NF4 ? 65536 : 32768; }
+__host__ __device__ inline size_t tensor_fwd_smem_bytes(int fmt) {
+    return (size_t)kFStages * kFXTile + tensor_fwd_table_bytes(fmt) + 1024 + 1024;
+}
+
+__device__ __forceinline__ void tc_mma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                               uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* r) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, "
+                 "%13, %14, %15, %16};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+struct FItem {
+    int32_t row0;      // first row of the chunk
+    int32_t tokens;    // rows in the chunk (1..256)
+    int32_t eid;
+    int32_t c0;        // first output column (weight row) of the tile
+};
+
+struct FCursor {
+    int32_t g = 0;
+    int64_t base = 0;
+    int32_t row0 = 0, rows = 0, eid = 0, chunks = 0, chunk_rows = 0;
+    bool loaded = false;
+};
+
+// Item id -> (group, balanced row chunk, column tile); column tile fastest.
+__device__ __forceinline__ bool next_fitem(const TensorArgs& a, FCursor& cur, int64_t id, FItem* it) {
+    while (cur.g < a.g.G) {
+        if (!cur.loaded) {
+            cur.row0 = __ldg(a.g.off + cur.g);
+            cur.rows = __ldg(a.g.off + cur.g + 1) - cur.row0;
+            cur.eid = __ldg(a.g.eids + cur.g);
+            const bool bad_e = cur.eid < 0 || cur.eid >= a.g.E;
+            const bool bad_o = cur.rows < 0 || cur.row0 < 0 || (int64_t)cur.row0 + cur.rows > a.g.T;
+            if ((bad_e || bad_o) && cur.rows != 0 && a.g.status && threadIdx.x == 0 && blockIdx.x == 0)
+                atomicOr(a.g.status, bad_e ? GNF4B_ST_BAD_EXPERT : GNF4B_ST_BAD_OFFSETS);
+            cur.chunks = (bad_e || bad_o || cur.rows <= 0) ? 0 : (cur.rows + kFTok - 1) / kFTok;
+            // equal chunks, a multiple of 16 rows each (the MMA's N granularity)
+            cur.chunk_rows = cur.chunks ? (((cur.rows + cur.chunks - 1) / cur.chunks + 15) & ~15) : 0;
+            cur.loaded = true;
+        }
+        const int64_t n_items = (int64_t)cur.chunks * a.c_tiles;
+        if (id < cur.base + n_items) {
+            const int32_t local = (int32_t)(id - cur.base);
+            const int32_t mc = local / a.c_tiles;
+            const int32_t ct = local - mc * a.c_tiles;
+            it->row0 = cur.row0 + mc * cur.chunk_rows;
+            it->tokens = min(cur.chunk_rows, cur.row0 + cur.rows - it->row0);
+            it->eid = cur.eid;
+            it->c0 = ct * kTBC;
+            return true;
+        }
+        cur.base += n_items;
+        cur.g++;
+        cur.loaded = false;
+    }
+    return false;
+}
+
+// 16 packed bytes (32 elements) of one weight row.
+__device__ __forceinline__ uint4 load_packed16(const uint8_t* p, int w_align) {
+    if (w_align >= 16) return __ldg(reinterpret_cast<const uint4*>(p));
+    const uint2 lo = load_packed8(p, w_align), hi = load_packed8(p + 8, w_align);
+    return make_uint4(lo.x, lo.y, hi.x, hi.y);
+}
+
+// Decode the 8 elements of one packed word into 4 bf16x2 words of hi (and lo for NF4): per byte
+// one table read, NF4 then scales in fp32 and splits hi = bf16(w), lo = bf16(w - hi); MXFP4
+// multiplies the exact bf16 pair by the power-of-two scale (exact).  Same arithmetic as
+// decode_store16 of tensor_kernel.cuh.
+template <int FMT>
+__device__ __forceinline__ void decode8_regs(const uint32_t w, float scale, uint32_t s2, uint32_t tab_lane,
+                                             uint32_t* hi, uint32_t* lo) {
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        const uint32_t byte = (b == 0) ? (w & 0xffu) : (b == 3) ? (w >> 24) : prmt(w, 0u, 0x4440u | b);
+        if (FMT == GNF4B_FMT_NF4) {
+            const float2 p = ld_shared_f32x2(tab_lane + (byte << 8));
+            const float w0 = p.x * scale, w1 = p.y * scale;
+            const uint32_t h = pack_bf16x2(w1, w0);
+            hi[b] = h;
+            lo[b] = pack_bf16x2(w1 - __uint_as_float(h & 0xffff0000u), w0 - __uint_as_float(h << 16));
+        } else {
+            hi[b] = mul_bf16x2(ld_shared_u32(tab_lane + (byte << 7)), s2);
+        }
+    }
+}
+
+template <int FMT, int SDT>
+__global__ void __launch_bounds__(kFThreads, 1)
+tensor_fwd_kernel(const TensorArgs a, const __grid_constant__ CUtensorMap x_map) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* tab_raw = smem + (size_t)kFStages * kFXTile;
+    uint64_t* full_x = reinterpret_cast<uint64_t*>(tab_raw + tensor_fwd_table_bytes(FMT));
+    uint64_t* full_w = full_x + kFStages;
+    uint64_t* empty = full_w + kFStages;
+    uint64_t* acc_full = empty + kFStages;
+    uint64_t* acc_empty = acc_full + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kFStages; ++s) {
+            mbar_init(full_x + s, 1);
+            mbar_init(full_w + s, 8);
+            mbar_init(empty + s, 1);
+        }
+        mbar_init(acc_full, 1);
+        mbar_init(acc_empty, 4);
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, kTTmemCols);
+        tmem_relinquish();
+    }
+    if (FMT == GNF4B_FMT_NF4) {
+        float2* tab = reinterpret_cast<float2*>(tab_raw);
+        for (int i = threadIdx.x; i < 256 * 32; i += kFThreads) tab[i] = byte_pair<FMT>(i >> 5);
+    } else {
+        uint32_t* tab = reinterpret_cast<uint32_t*>(tab_raw);
+        for (int i = threadIdx.x; i < 256 * 32; i += kFThreads) {
+            const float2 p = byte_pair<FMT>(i >> 5);
+            tab[i] = pack_bf16x2(p.y, p.x);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_a0 = tmem_base + kFTok;          // A stages start after the 256 accumulator columns
+    const int64_t scale_blk = (FMT == GNF4B_FMT_NF4) ? 64 : 32;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            FCursor cur;
+            FItem it;
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (int64_t id = blockIdx.x; ok && next_fitem(a, cur, id, &it); id += gridDim.x) {
+                const int boxes = it.tokens > kTBM ? 2 : 1;
+                for (int rb = 0; rb < a.r_blocks && ok; ++rb) {
+                    ok = mbar_wait_bounded(empty + stage, phase ^ 1, abort_flag);
+                    if (!ok) break;
+                    uint8_t* st = smem + (size_t)stage * kFXTile;
+                    mbar_arrive_expect_tx(full_x + stage, (uint32_t)(boxes * kTATile));
+                    for (int b = 0; b < boxes; ++b)
+                        tma_load_2d(st + b * kTATile, &x_map, rb * kTBR, it.row0 + b * kTBM, full_x + stage);
+                    if (++stage == kFStages) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            FCursor cur;
+            FItem it;
+            uint32_t stage = 0, phase = 0, acc_phase = 0;
+            bool ok = true;
+            for (int64_t id = blockIdx.x; ok && next_fitem(a, cur, id, &it); id += gridDim.x) {
+                const uint32_t n_umma = (uint32_t)((it.tokens + 15) & ~15);
+                // kind::f16: fp32 accumulate, bf16 x bf16, both K-major, M = 128, N = n_umma
+                const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((n_umma >> 3) << 17) | ((kTBM >> 4) << 24);
+                ok = mbar_wait_bounded(acc_empty, acc_phase ^ 1, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                for (int rb = 0; rb < a.r_blocks && ok; ++rb) {
+                    ok = mbar_wait_bounded(full_x + stage, phase, abort_flag) &&
+                         mbar_wait_bounded(full_w + stage, phase, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t xs = smem_u32(smem + (size_t)stage * kFXTile);
+                    const uint32_t a_hi = tmem_a0 + stage * kFAcols;
+#pragma unroll
+                    for (int j = 0; j < kTBR / 16; ++j) {
+                        const uint64_t db = umma_desc(xs + j * 32, 16, 1024);
+                        tc_mma_bf16_ts(tmem_base, a_hi + j * 8, db, idesc, (rb > 0 || j > 0) ? 1u : 0u);
+                        if (FMT == GNF4B_FMT_NF4) tc_mma_bf16_ts(tmem_base, a_hi + 32 + j * 8, db, idesc, 1u);
+                    }
+                    tc_commit(empty + stage);
+                    if (++stage == kFStages) { stage = 0; phase ^= 1; }
+                }
+                if (ok) tc_commit(acc_full);
+                acc_phase ^= 1;
+            }
+        }
+    } else if (warp < 6) {
+        // ------------------------------------------------------------ epilogue
+        const int q = warp & 3;
+        FCursor cur;
+        FItem it;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        uint16_t* out = reinterpret_cast<uint16_t*>(a.g.out);
+        const bool pair_ok = (a.C % 2) == 0;
+        for (int64_t id = blockIdx.x; ok && next_fitem(a, cur, id, &it); id += gridDim.x) {
+            ok = mbar_wait_bounded(acc_full, acc_phase, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            const int64_t n = (int64_t)it.c0 + q * 32 + lane;          // this lane's output column
+            const int chunks = (it.tokens + 31) >> 5;
+            for (int c = 0; c < chunks; ++c) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
+                tmem_ld_wait();
+                if (c == chunks - 1) {
+                    // every accumulator value this warp needs is in registers: free the buffer
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(acc_empty);
+                }
+                const int t0 = c * 32;
+                if (pair_ok) {
+                    // lanes 2i and 2i+1 swap one value: the even lane stores (n, n+1) of token j,
+                    // the odd lane (n-1, n) of token j+1 -- 4-byte stores, 64 bytes per half warp
+                    const int odd = lane & 1;
+                    const int left = (n - odd < a.C) ? it.tokens - t0 - odd : 0;     // store while j < left
+                    uint16_t* p = out + (int64_t)(it.row0 + t0 + odd) * a.C + (n - odd);
+                    const int64_t step = 2 * a.C;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2) {
+                        const float mine0 = __uint_as_float(r[j]), mine1 = __uint_as_float(r[j + 1]);
+                        const float got = __shfl_xor_sync(0xffffffffu, odd ? mine0 : mine1, 1);
+                        if (j < left)
+                            *reinterpret_cast<uint32_t*>(p) = odd ? pack_bf16x2(mine1, got) : pack_bf16x2(got, mine0);
+                        p += step;
+                    }
+                } else {
+                    const int left = (n < a.C) ? it.tokens - t0 : 0;
+                    uint16_t* p = out + (int64_t)(it.row0 + t0) * a.C + n;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        if (j < left) *p = f32_to_bf16_bits(__uint_as_float(r[j]));
+                        p += a.C;
+                    }
+                }
+            }
+            acc_phase ^= 1;
+        }
+    } else {
+        // ------------------------------------------------------------ weight decode -> TMEM
+        const int dw = warp - 6;
+        const int grp = dw >> 3;                   // this group takes pipeline stages grp, grp + 2, ...
+        const int hf = (dw >> 2) & 1;              // which 32 k of the stage's 64
+        const int q = warp & 3;                    // TMEM lane quarter this warp may write
+        const int n_local = q * 32 + lane;
+        const uint32_t tab_lane = smem_u32(tab_raw) + lane * (FMT == GNF4B_FMT_NF4 ? 8 : 4);
+        const uint32_t col0 = tmem_a0 + ((uint32_t)(q * 32) << 16) + hf * 16;
+        // the fetch cursor runs one own stage ahead of the stage being decoded and crosses items
+        FCursor cur;
+        FItem it;
+        int64_t id = blockIdx.x;
+        bool have = next_fitem(a, cur, id, &it);
+        int rb = grp;
+        uint4 pk_n = make_uint4(0, 0, 0, 0);
+        float sc_n = 0.f;
+        auto settle = [&]() {                      // bring (it, rb) to the next existing stage
+            while (have && rb >= a.r_blocks) {
+                rb -= a.r_blocks;
+                id += gridDim.x;
+                have = next_fitem(a, cur, id, &it);
+            }
+        };
+        auto fetch = [&]() {
+            const int64_t n = (int64_t)it.c0 + n_local;
+            const int64_t k = (int64_t)rb * kTBR + hf * 32;
+            if (n < a.g.N && k < a.g.K) {
+                pk_n = load_packed16(a.g.W + (int64_t)it.eid * a.g.w_se + n * a.g.w_sn + (k >> 1), a.w_align);
+                sc_n = load_scale<SDT>(a.g.S, (int64_t)it.eid * a.g.s_se + n * a.g.s_sn + k / scale_blk);
+            } else {
+                pk_n = make_uint4(0, 0, 0, 0);
+                sc_n = 0.f;                        // padding decodes to zeros
+            }
+        };
+        settle();
+        if (have) fetch();
+        uint32_t stage = grp, phase = 0;
+        bool ok = true;
+        while (have && ok) {
+            const uint4 pk = pk_n;
+            const float sc = sc_n;
+            rb += 2;
+            settle();
+            if (have) fetch();
+            const bool more = have;
+            ok = mbar_wait_bounded(empty + stage, phase ^ 1, abort_flag);
+            if (ok) {
+                const uint32_t s16 = __float_as_uint(sc) >> 16;
+                const uint32_t s2 = s16 | (s16 << 16);
+                const uint32_t col = col0 + stage * kFAcols;
+                const uint32_t w4[4] = {pk.x, pk.y, pk.z, pk.w};
+                uint32_t hi[16], lo[16];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) decode8_regs<FMT>(w4[i], sc, s2, tab_lane, hi + 4 * i, lo + 4 * i);
+                tmem_st16(col, hi);
+                if (FMT == GNF4B_FMT_NF4) tmem_st16(col + 32, lo);
+                tmem_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full_w + stage);
+                stage += 2;
+                if (stage >= kFStages) { stage -= kFStages; phase ^= 1; }
+            }
+            have = more;
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTTmemCols);
+    }
+    if (threadIdx.x == 0 && *abort_flag && a.g.status) atomicOr(a.g.status, GNF4B_ST_TIMEOUT);
+}
+
+template <int FMT, int SDT>
+static int launch_tensor_fwd_t(const TensorArgs& ta, const CUtensorMap& map, int sm_count, size_t smem, cudaStream_t st) {
+    auto kfn = tensor_fwd_kernel<FMT, SDT>;
+    static int granted[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return GNF4B_ECUDA;
+    dev &= 63;
+    if ((int)smem > granted[dev]) {
+        if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return GNF4B_ECUDA;
+        granted[dev] = (int)smem;
+    }
+    kfn<<<sm_count, kFThreads, smem, st>>>(ta, map);
+    return cudaPeekAtLastError() == cudaSuccess ? GNF4B_OK : GNF4B_ECUDA;
+}
+
+// Forward with the weight tile in tensor memory.  Same preconditions as launch_tensor.
+static int launch_tensor_fwd(int fmt, int s_dtype, const GemmArgs& g, int sm_count, int smem_optin, int w_align,
+                             cudaStream_t st) {
+    if (g.x_dtype != GNF4B_X_BF16) return GNF4B_EUNSUPPORTED;
+    TensorArgs ta;
+    ta.g = g;
+    ta.C = g.N;
+    ta.R = g.K;
+    if ((ta.R * 2) % 16) return GNF4B_EUNSUPPORTED;
+    ta.c_tiles = (int32_t)((ta.C + kTBC - 1) / kTBC);
+    ta.r_blocks = (int32_t)((ta.R + kTBR - 1) / kTBR);
+    ta.w_align = w_align;
+    ta.stages = kFStages;
+    const size_t smem = tensor_fwd_smem_bytes(fmt);
+    if (smem > (size_t)smem_optin) return GNF4B_EUNSUPPORTED;
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return GNF4B_EUNSUPPORTED;
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {(cuuint64_t)ta.R, (cuuint64_t)g.T};
+    const cuuint64_t strides[1] = {(cuuint64_t)ta.R * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kTBR, (cuuint32_t)kTBM};
+    const cuuint32_t estr[2] = {1, 1};
+    if (enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(g.x), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return GNF4B_EUNSUPPORTED;
+    if (fmt == GNF4B_FMT_NF4 && s_dtype == GNF4B_S_F32)
+        return launch_tensor_fwd_t<GNF4B_FMT_NF4, GNF4B_S_F32>(ta, map, sm_count, smem, st);
+    if (fmt == GNF4B_FMT_NF4) return launch_tensor_fwd_t<GNF4B_FMT_NF4, GNF4B_S_BF16>(ta, map, sm_count, smem, st);
+    return launch_tensor_fwd_t<GNF4B_FMT_MXFP4, GNF4B_S_E8M0>(ta, map, sm_count, smem, st);
+}
+
+}  // namespace gnf4b

@@ -65,6 +65,32 @@ def test_prefill_nf4_vs_oracle(N, K, sizes, ids):
     _clean()
 
 
+@pytest.mark.parametrize("fmt", ["nf4", "mxfp4"])
+@pytest.mark.parametrize("sizes", [[256], [257, 16, 15], [700, 0, 1, 90], [31, 33]])
+def test_both_forward_tensor_kernels_agree(fmt, sizes):
+    """Forward runs on the kernel that keeps decoded weights in tensor memory; the first tensor kernel
+    (both operands in shared memory) stays reachable as an ablation and serves dgrad.  Same products in the
+    same k order: the two must agree to bf16 resolution, and both with the oracle.  Chunk boundaries
+    (256 rows, multiples of 16) and ragged last column tiles are the cases here."""
+    N, K = 200, 320
+    ids = list(range(len(sizes)))
+    gen = torch.Generator().manual_seed(len(sizes) * 31 + sizes[0])
+    a = torch.randn(sum(sizes), K, generator=gen).to(torch.bfloat16).to(DEV)
+    if fmt == "nf4":
+        W, Sc = make_stack(4, N, K, seed=5, device=DEV)
+        call = gemm_4bit_grouped
+    else:
+        W, Sc = _mx_stack(4, N, K, seed=5)
+        call = mxfp4_grouped.gemm_mxfp4_grouped
+    new = call(a, W, Sc, sizes, ids, path=T)
+    old = call(a, W, Sc, sizes, ids, path=T | _gnf4b.FLAG_SMEM_OPERANDS)
+    ref = oracle_fwd64(fmt, a, W, Sc, sizes, ids)
+    assert rel_fro(new, ref) <= REL_FRO_TOL and rel_fro(old, ref) <= REL_FRO_TOL
+    lim = 2 ** -8 * float(np.abs(ref).max())
+    assert (new.float() - old.float()).abs().max().item() <= lim
+    _clean()
+
+
 CENSUS = [("olmoe_gu", 2048, 2048, 8), ("qwen_gu", 1536, 2048, 8), ("qwen_dn", 2048, 768, 8),
           ("gemma_dn", 2816, 704, 8), ("gptoss_gu", 5760, 2880, 4), ("gptoss_dn", 2880, 2880, 4)]
 
