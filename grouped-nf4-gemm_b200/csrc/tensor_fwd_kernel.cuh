@@ -13,12 +13,15 @@
 //               shared memory by TMA -- the only MMA operand read from shared memory
 //   D         = fp32 [128 lanes x <=256 columns] in TMEM
 //
-// Roles (704 threads, one CTA per SM, persistent):
+// Roles (832 threads, one CTA per SM, persistent):
 //   warp 0      TMA producer of activation tiles (two 128-row boxes per stage)
 //   warp 1      MMA issuer (one lane): per stage 4 k-steps x (hi [, lo]) tcgen05.mma with A in TMEM
-//   warps 2-5   epilogue: tcgen05.ld, neighbour lanes exchange one value so each writes a
-//               bf16 pair, stores are 64-byte coalesced along n (the output is transposed back here)
-//   warps 6-21  decode, two groups of 8 warps that take alternate stages: thread = (weight row,
+//   warps 2-9   epilogue, two per TMEM lane quarter taking alternate 32-token chunks: tcgen05.ld,
+//               neighbour lanes exchange one value so each writes a bf16 pair, stores are 64-byte
+//               coalesced along n (the output is transposed back here).  One warp needs ~700 cycles
+//               per chunk (it is bound by its own instruction latency), the tensor pipe idles
+//               until the last chunk is in registers: hence two warps per quarter
+//   warps 10-25 decode, two groups of 8 warps that take alternate stages: thread = (weight row,
 //               32 k): 16 packed bytes + one block scale from global memory (prefetched one own
 //               stage = two pipeline stages ahead, across item boundaries), one table lookup per
 //               byte, tcgen05.st of 16 columns (hi) + 16 columns (lo)
@@ -35,14 +38,17 @@ constexpr int kFStages = 4;
 constexpr int kFTok = 256;                     // tokens per item (UMMA N)
 constexpr int kFXTile = kFTok * kTBR * 2;      // 32 KiB of activations per stage
 constexpr int kFAcols = 64;                    // TMEM columns of A per stage (hi 32 + lo 32)
-constexpr int kFThreads = (2 + 4 + 16) * 32;
+constexpr int kFEpiWarps = 8;                  // two per TMEM lane quarter, alternate 32-token chunks
+constexpr int kFDecWarp0 = 2 + kFEpiWarps;     // first decode warp
+constexpr int kFThreads = (2 + kFEpiWarps + 16) * 32;
+constexpr int kFGroupBytes = 512 * 16 + 513 * 8 + 16 * 8 + 8;   // FGroup[512], base[513], warp totals[16]
 
 // Lookup tables, one copy per lane so that no two lanes share a bank:
 //   NF4   tab[byte][lane] float2 = codebook values of the byte's two elements (64 KiB)
 //   MXFP4 tab[byte][lane] bf16x2 = doubled e2m1 values of the byte's two elements (32 KiB)
 __host__ __device__ inline size_t tensor_fwd_table_bytes(int fmt) { return fmt == GNF4B_FMT_NF4 ? 65536 : 32768; }
 __host__ __device__ inline size_t tensor_fwd_smem_bytes(int fmt) {
-    return (size_t)kFStages * kFXTile + tensor_fwd_table_bytes(fmt) + 1024 + 1024;
+    return (size_t)kFStages * kFXTile + tensor_fwd_table_bytes(fmt) + kFGroupBytes + 1024 + 1024;
 }
 
 __device__ __forceinline__ void tc_mma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
@@ -74,45 +80,70 @@ struct FItem {
     int32_t c0;        // first output column (weight row) of the tile
 };
 
+// The group table lives in shared memory: every role walks the item list, and the MMA issuer does
+// so between two items with the tensor pipe idle -- a walk through global memory (three dependent
+// loads per group, a dozen groups per step) cost it thousands of cycles per item.
+constexpr int kFMaxGroups = 512;
+struct FGroup {
+    int32_t row0, rows, eid, chunk_rows;
+};
+struct FTable {
+    const FGroup* grp;       // [G]
+    const int64_t* base;     // [G + 1] items before group g
+};
 struct FCursor {
     int32_t g = 0;
-    int64_t base = 0;
-    int32_t row0 = 0, rows = 0, eid = 0, chunks = 0, chunk_rows = 0;
-    bool loaded = false;
 };
 
 // Item id -> (group, balanced row chunk, column tile); column tile fastest.
-__device__ __forceinline__ bool next_fitem(const TensorArgs& a, FCursor& cur, int64_t id, FItem* it) {
-    while (cur.g < a.g.G) {
-        if (!cur.loaded) {
-            cur.row0 = __ldg(a.g.off + cur.g);
-            cur.rows = __ldg(a.g.off + cur.g + 1) - cur.row0;
-            cur.eid = __ldg(a.g.eids + cur.g);
-            const bool bad_e = cur.eid < 0 || cur.eid >= a.g.E;
-            const bool bad_o = cur.rows < 0 || cur.row0 < 0 || (int64_t)cur.row0 + cur.rows > a.g.T;
-            if ((bad_e || bad_o) && cur.rows != 0 && a.g.status && threadIdx.x == 0 && blockIdx.x == 0)
-                atomicOr(a.g.status, bad_e ? GNF4B_ST_BAD_EXPERT : GNF4B_ST_BAD_OFFSETS);
-            cur.chunks = (bad_e || bad_o || cur.rows <= 0) ? 0 : (cur.rows + kFTok - 1) / kFTok;
-            // equal chunks, a multiple of 16 rows each (the MMA's N granularity)
-            cur.chunk_rows = cur.chunks ? (((cur.rows + cur.chunks - 1) / cur.chunks + 15) & ~15) : 0;
-            cur.loaded = true;
-        }
-        const int64_t n_items = (int64_t)cur.chunks * a.c_tiles;
-        if (id < cur.base + n_items) {
-            const int32_t local = (int32_t)(id - cur.base);
-            const int32_t mc = local / a.c_tiles;
-            const int32_t ct = local - mc * a.c_tiles;
-            it->row0 = cur.row0 + mc * cur.chunk_rows;
-            it->tokens = min(cur.chunk_rows, cur.row0 + cur.rows - it->row0);
-            it->eid = cur.eid;
-            it->c0 = ct * kTBC;
-            return true;
-        }
-        cur.base += n_items;
-        cur.g++;
-        cur.loaded = false;
+__device__ __forceinline__ bool next_fitem(const TensorArgs& a, const FTable& tb, FCursor& cur, int64_t id, FItem* it) {
+    while (cur.g < a.g.G && id >= tb.base[cur.g + 1]) cur.g++;
+    if (cur.g >= a.g.G) return false;
+    const FGroup gr = tb.grp[cur.g];
+    const int32_t local = (int32_t)(id - tb.base[cur.g]);
+    const int32_t mc = local / a.c_tiles;
+    const int32_t ct = local - mc * a.c_tiles;
+    it->row0 = gr.row0 + mc * gr.chunk_rows;
+    it->tokens = min(gr.chunk_rows, gr.row0 + gr.rows - it->row0);
+    it->eid = gr.eid;
+    it->c0 = ct * kTBC;
+    return true;
+}
+
+// Build the table: one thread per group, then a block-wide inclusive scan of the item counts.
+// Groups with a bad expert id or bad offsets are flagged in the status word and get no items.
+__device__ __forceinline__ void build_ftable(const TensorArgs& a, FGroup* grp, int64_t* base, int64_t* warp_tot) {
+    const int t = threadIdx.x, lane = t & 31, w = t >> 5;
+    int64_t items = 0;
+    if (t < a.g.G) {
+        FGroup gr;
+        gr.row0 = __ldg(a.g.off + t);
+        gr.rows = __ldg(a.g.off + t + 1) - gr.row0;
+        gr.eid = __ldg(a.g.eids + t);
+        const bool bad_e = gr.eid < 0 || gr.eid >= a.g.E;
+        const bool bad_o = gr.rows < 0 || gr.row0 < 0 || (int64_t)gr.row0 + gr.rows > a.g.T;
+        if ((bad_e || bad_o) && gr.rows != 0 && a.g.status && blockIdx.x == 0)
+            atomicOr(a.g.status, bad_e ? GNF4B_ST_BAD_EXPERT : GNF4B_ST_BAD_OFFSETS);
+        const int32_t chunks = (bad_e || bad_o || gr.rows <= 0) ? 0 : (gr.rows + kFTok - 1) / kFTok;
+        // equal chunks, a multiple of 16 rows each (the MMA's N granularity)
+        gr.chunk_rows = chunks ? (((gr.rows + chunks - 1) / chunks + 15) & ~15) : 0;
+        grp[t] = gr;
+        items = (int64_t)chunks * a.c_tiles;
     }
-    return false;
+    int64_t incl = items;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int64_t up = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += up;
+    }
+    if (lane == 31 && w < kFMaxGroups / 32) warp_tot[w] = incl;
+    __syncthreads();
+    if (t < a.g.G) {
+        int64_t before = 0;
+        for (int v = 0; v < w; ++v) before += warp_tot[v];
+        base[t + 1] = before + incl;
+    }
+    if (t == 0) base[0] = 0;
 }
 
 // 16 packed bytes (32 elements) of one weight row.
@@ -150,7 +181,11 @@ tensor_fwd_kernel(const TensorArgs a, const __grid_constant__ CUtensorMap x_map)
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* tab_raw = smem + (size_t)kFStages * kFXTile;
-    uint64_t* full_x = reinterpret_cast<uint64_t*>(tab_raw + tensor_fwd_table_bytes(FMT));
+    uint8_t* grp_raw = tab_raw + tensor_fwd_table_bytes(FMT);
+    FGroup* s_grp = reinterpret_cast<FGroup*>(grp_raw);
+    int64_t* s_base = reinterpret_cast<int64_t*>(grp_raw + kFMaxGroups * 16);
+    int64_t* s_wtot = s_base + kFMaxGroups + 1;
+    uint64_t* full_x = reinterpret_cast<uint64_t*>(grp_raw + kFGroupBytes);
     uint64_t* full_w = full_x + kFStages;
     uint64_t* empty = full_w + kFStages;
     uint64_t* acc_full = empty + kFStages;
@@ -168,7 +203,7 @@ tensor_fwd_kernel(const TensorArgs a, const __grid_constant__ CUtensorMap x_map)
             mbar_init(empty + s, 1);
         }
         mbar_init(acc_full, 1);
-        mbar_init(acc_empty, 4);
+        mbar_init(acc_empty, kFEpiWarps);
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -186,6 +221,8 @@ tensor_fwd_kernel(const TensorArgs a, const __grid_constant__ CUtensorMap x_map)
             tab[i] = pack_bf16x2(p.y, p.x);
         }
     }
+    build_ftable(a, s_grp, s_base, s_wtot);
+    const FTable tb{s_grp, s_base};
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -200,7 +237,7 @@ tensor_fwd_kernel(const TensorArgs a, const __grid_constant__ CUtensorMap x_map)
             FItem it;
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            for (int64_t id = blockIdx.x; ok && next_fitem(a, cur, id, &it); id += gridDim.x) {
+            for (int64_t id = blockIdx.x; ok && next_fitem(a, tb, cur, id, &it); id += gridDim.x) {
                 const int boxes = it.tokens > kTBM ? 2 : 1;
                 for (int rb = 0; rb < a.r_blocks && ok; ++rb) {
                     ok = mbar_wait_bounded(empty + stage, phase ^ 1, abort_flag);
@@ -220,7 +257,7 @@ tensor_fwd_kernel(const TensorArgs a, const __grid_constant__ CUtensorMap x_map)
             FItem it;
             uint32_t stage = 0, phase = 0, acc_phase = 0;
             bool ok = true;
-            for (int64_t id = blockIdx.x; ok && next_fitem(a, cur, id, &it); id += gridDim.x) {
+            for (int64_t id = blockIdx.x; ok && next_fitem(a, tb, cur, id, &it); id += gridDim.x) {
                 const uint32_t n_umma = (uint32_t)((it.tokens + 15) & ~15);
                 // kind::f16: fp32 accumulate, bf16 x bf16, both K-major, M = 128, N = n_umma
                 const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((n_umma >> 3) << 17) | ((kTBM >> 4) << 24);
@@ -247,27 +284,33 @@ tensor_fwd_kernel(const TensorArgs a, const __grid_constant__ CUtensorMap x_map)
                 acc_phase ^= 1;
             }
         }
-    } else if (warp < 6) {
+    } else if (warp < kFDecWarp0) {
         // ------------------------------------------------------------ epilogue
         const int q = warp & 3;
+        const int e = (warp - 2) >> 2;              // takes chunks e, e + 2, ...
         FCursor cur;
         FItem it;
         uint32_t acc_phase = 0;
         bool ok = true;
         uint16_t* out = reinterpret_cast<uint16_t*>(a.g.out);
         const bool pair_ok = (a.C % 2) == 0;
-        for (int64_t id = blockIdx.x; ok && next_fitem(a, cur, id, &it); id += gridDim.x) {
+        for (int64_t id = blockIdx.x; ok && next_fitem(a, tb, cur, id, &it); id += gridDim.x) {
             ok = mbar_wait_bounded(acc_full, acc_phase, abort_flag);
             if (!ok) break;
             tc_fence_after();
             const int64_t n = (int64_t)it.c0 + q * 32 + lane;          // this lane's output column
             const int chunks = (it.tokens + 31) >> 5;
-            for (int c = 0; c < chunks; ++c) {
+            if (e >= chunks) {                           // nothing to drain for this warp
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(acc_empty);
+            }
+            for (int c = e; c < chunks; c += 2) {
                 uint32_t r[32];
                 tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
                 tmem_ld_wait();
-                if (c == chunks - 1) {
-                    // every accumulator value this warp needs is in registers: free the buffer
+                if (c + 2 >= chunks) {
+                    // every accumulator value this warp needs is in registers: hand the buffer back
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(acc_empty);
@@ -280,12 +323,16 @@ tensor_fwd_kernel(const TensorArgs a, const __grid_constant__ CUtensorMap x_map)
                     const int left = (n - odd < a.C) ? it.tokens - t0 - odd : 0;     // store while j < left
                     uint16_t* p = out + (int64_t)(it.row0 + t0 + odd) * a.C + (n - odd);
                     const int64_t step = 2 * a.C;
+                    uint32_t v[16];
 #pragma unroll
                     for (int j = 0; j < 32; j += 2) {
                         const float mine0 = __uint_as_float(r[j]), mine1 = __uint_as_float(r[j + 1]);
                         const float got = __shfl_xor_sync(0xffffffffu, odd ? mine0 : mine1, 1);
-                        if (j < left)
-                            *reinterpret_cast<uint32_t*>(p) = odd ? pack_bf16x2(mine1, got) : pack_bf16x2(got, mine0);
+                        v[j >> 1] = odd ? pack_bf16x2(mine1, got) : pack_bf16x2(got, mine0);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2) {
+                        if (j < left) *reinterpret_cast<uint32_t*>(p) = v[j >> 1];
                         p += step;
                     }
                 } else {
@@ -302,7 +349,7 @@ tensor_fwd_kernel(const TensorArgs a, const __grid_constant__ CUtensorMap x_map)
         }
     } else {
         // ------------------------------------------------------------ weight decode -> TMEM
-        const int dw = warp - 6;
+        const int dw = warp - kFDecWarp0;
         const int grp = dw >> 3;                   // this group takes pipeline stages grp, grp + 2, ...
         const int hf = (dw >> 2) & 1;              // which 32 k of the stage's 64
         const int q = warp & 3;                    // TMEM lane quarter this warp may write
@@ -313,7 +360,7 @@ tensor_fwd_kernel(const TensorArgs a, const __grid_constant__ CUtensorMap x_map)
         FCursor cur;
         FItem it;
         int64_t id = blockIdx.x;
-        bool have = next_fitem(a, cur, id, &it);
+        bool have = next_fitem(a, tb, cur, id, &it);
         int rb = grp;
         uint4 pk_n = make_uint4(0, 0, 0, 0);
         float sc_n = 0.f;
@@ -321,7 +368,7 @@ tensor_fwd_kernel(const TensorArgs a, const __grid_constant__ CUtensorMap x_map)
             while (have && rb >= a.r_blocks) {
                 rb -= a.r_blocks;
                 id += gridDim.x;
-                have = next_fitem(a, cur, id, &it);
+                have = next_fitem(a, tb, cur, id, &it);
             }
         };
         auto fetch = [&]() {
@@ -352,11 +399,14 @@ tensor_fwd_kernel(const TensorArgs a, const __grid_constant__ CUtensorMap x_map)
                 const uint32_t s2 = s16 | (s16 << 16);
                 const uint32_t col = col0 + stage * kFAcols;
                 const uint32_t w4[4] = {pk.x, pk.y, pk.z, pk.w};
-                uint32_t hi[16], lo[16];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) decode8_regs<FMT>(w4[i], sc, s2, tab_lane, hi + 4 * i, lo + 4 * i);
-                tmem_st16(col, hi);
-                if (FMT == GNF4B_FMT_NF4) tmem_st16(col + 32, lo);
+                for (int h = 0; h < 2; ++h) {
+                    uint32_t hi[8], lo[8];
+                    decode8_regs<FMT>(w4[2 * h], sc, s2, tab_lane, hi, lo);
+                    decode8_regs<FMT>(w4[2 * h + 1], sc, s2, tab_lane, hi + 4, lo + 4);
+                    tmem_st8(col + h * 8, hi);
+                    if (FMT == GNF4B_FMT_NF4) tmem_st8(col + 32 + h * 8, lo);
+                }
                 tmem_st_wait();
                 tc_fence_before();
                 __syncwarp();
@@ -404,7 +454,7 @@ static int launch_tensor_fwd(int fmt, int s_dtype, const GemmArgs& g, int sm_cou
     ta.g = g;
     ta.C = g.N;
     ta.R = g.K;
-    if ((ta.R * 2) % 16) return GNF4B_EUNSUPPORTED;
+    if ((ta.R * 2) % 16 || g.G > kFMaxGroups) return GNF4B_EUNSUPPORTED;
     ta.c_tiles = (int32_t)((ta.C + kTBC - 1) / kTBC);
     ta.r_blocks = (int32_t)((ta.R + kTBR - 1) / kTBR);
     ta.w_align = w_align;

@@ -91,6 +91,20 @@ def test_both_forward_tensor_kernels_agree(fmt, sizes):
     _clean()
 
 
+def test_more_groups_than_the_forward_kernels_group_table():
+    """The forward kernel keeps its group table in shared memory (512 groups); a call with more groups
+    runs on the first tensor kernel instead -- same answer, no error."""
+    G, N, K = 600, 128, 128
+    gen = torch.Generator().manual_seed(600)
+    sizes = [int(v) for v in torch.randint(0, 4, (G,), generator=gen)]
+    ids = [int(v) for v in torch.randint(0, 8, (G,), generator=gen)]
+    B, A = make_stack(8, N, K, seed=21, device=DEV)
+    a = torch.randn(sum(sizes), K, generator=gen).to(torch.bfloat16).to(DEV)
+    out = gemm_4bit_grouped(a, B, A, sizes, ids, path=T)
+    assert rel_fro(out, oracle_fwd64("nf4", a, B, A, sizes, ids)) <= REL_FRO_TOL
+    _clean()
+
+
 CENSUS = [("olmoe_gu", 2048, 2048, 8), ("qwen_gu", 1536, 2048, 8), ("qwen_dn", 2048, 768, 8),
           ("gemma_dn", 2816, 704, 8), ("gptoss_gu", 5760, 2880, 4), ("gptoss_dn", 2880, 2880, 4)]
 
