@@ -28,6 +28,7 @@ X_BF16, X_FP16 = 0, 1
 S_F32, S_BF16, S_E8M0 = 0, 1, 2
 PATH_AUTO, PATH_STREAM, PATH_TENSOR = 0, 1, 2
 SPLITK_SHIFT = 8
+FLAG_CTA_PAIR = 0x20000           # forward tensor kernel as CTA pairs (cta_group::2) instead of single CTAs
 FLAG_SMEM_OPERANDS = 0x10000      # ablation: forward on the kernel with both MMA operands in shared memory
 ST_BAD_EXPERT, ST_BAD_OFFSETS, ST_TIMEOUT = 1, 2, 4
 NOALLOC_SCRATCH_BYTES = 8 << 20

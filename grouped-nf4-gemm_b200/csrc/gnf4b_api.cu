@@ -346,7 +346,8 @@ int gnf4b_gemm_grouped(int fmt, int op, const void* x, int x_dtype, int64_t T, c
         // in shared memory
         rc = GNF4B_EUNSUPPORTED;
         if (op == GNF4B_OP_FWD && !(flags & GNF4B_FLAG_SMEM_OPERANDS))
-            rc = launch_tensor_fwd(fmt, s_dtype, g, di.sm_count, di.smem_optin, align_class(W, w_stride_e, w_stride_n), st);
+            rc = launch_tensor_fwd(fmt, s_dtype, g, di.sm_count, di.smem_optin, align_class(W, w_stride_e, w_stride_n),
+                                   (flags & GNF4B_FLAG_CTA_PAIR) != 0, st);
         if (rc == GNF4B_EUNSUPPORTED)      // dgrad, the ablation flag, or more groups than its table holds
             rc = launch_tensor(fmt, op, s_dtype, g, max_rows, di.sm_count, di.smem_optin,
                                align_class(W, w_stride_e, w_stride_n), st);

@@ -34,7 +34,8 @@
 
 namespace gnf4b {
 
-constexpr int kFStages = 4;
+constexpr int kFStages = 4;                     // tensor-memory slots of decoded weights
+constexpr int kFRing = 8;                       // barrier ring
 constexpr int kFTok = 256;                     // tokens per item (UMMA N)
 constexpr int kFXTile = kFTok * kTBR * 2;      // 32 KiB of activations per stage
 constexpr int kFAcols = 64;                    // TMEM columns of A per stage (hi 32 + lo 32)
@@ -73,6 +74,73 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// ---- CTA-pair (cta_group::2) helpers.  A pair is a cluster of two CTAs on the two SMs of a TPC.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// shared::cluster address of the same shared-memory location in the CTA of rank `rank`
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+// Arrive on a barrier of the peer CTA.  Relaxed on purpose: a release at cluster scope costs a
+// cluster-wide fence per arrival (measured: 25 % of the kernel's time), and nothing here publishes
+// ordinary memory.  What the arrival announces is complete before it is issued -- tensor-memory
+// stores behind tcgen05.wait::st and tcgen05.fence::before_thread_sync, accumulator reads behind
+// tcgen05.wait::ld, a landed TMA copy observed on the local barrier -- and the waiter acquires at
+// cluster scope and fences tcgen05 after it.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// bounded like mbar_wait_bounded; acquires at cluster scope (the arrival came from the peer CTA)
+__device__ __forceinline__ bool mbar_wait_bounded_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while (true) {
+        if (mbar_try_wait_cluster(bar, parity)) return true;
+        if ((++spins & 255u) == 0) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > kWaitLimitCycles) {
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// tcgen05.mma over the CTA pair: M = 256 (128 rows of A and D in each CTA's tensor memory),
+// each CTA supplies half of B's rows from its own shared memory at the same offset
+__device__ __forceinline__ void tc_mma_bf16_ts2(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                                uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// arrive on a barrier (shared::cluster address, this CTA's or the peer's) when every MMA issued so far is done
+__device__ __forceinline__ void tc_commit2(uint32_t cluster_addr) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr)
+                 : "memory");
+}
+
 struct FItem {
     int32_t row0;      // first row of the chunk
     int32_t tokens;    // rows in the chunk (1..256)
@@ -96,23 +164,27 @@ struct FCursor {
 };
 
 // Item id -> (group, balanced row chunk, column tile); column tile fastest.
-__device__ __forceinline__ bool next_fitem(const TensorArgs& a, const FTable& tb, FCursor& cur, int64_t id, FItem* it) {
+// `tiles` = column tiles (CG = 1) or column-tile pairs (CG = 2) per row chunk; `tile_mul`, `tile_add`
+// turn the item's tile index into this CTA's 128-column tile.
+__device__ __forceinline__ bool next_fitem(const TensorArgs& a, const FTable& tb, FCursor& cur, int64_t id, FItem* it,
+                                           int32_t tiles, int32_t tile_mul, int32_t tile_add) {
     while (cur.g < a.g.G && id >= tb.base[cur.g + 1]) cur.g++;
     if (cur.g >= a.g.G) return false;
     const FGroup gr = tb.grp[cur.g];
     const int32_t local = (int32_t)(id - tb.base[cur.g]);
-    const int32_t mc = local / a.c_tiles;
-    const int32_t ct = local - mc * a.c_tiles;
+    const int32_t mc = local / tiles;
+    const int32_t ct = local - mc * tiles;
     it->row0 = gr.row0 + mc * gr.chunk_rows;
     it->tokens = min(gr.chunk_rows, gr.row0 + gr.rows - it->row0);
     it->eid = gr.eid;
-    it->c0 = ct * kTBC;
+    it->c0 = (ct * tile_mul + tile_add) * kTBC;
     return true;
 }
 
 // Build the table: one thread per group, then a block-wide inclusive scan of the item counts.
 // Groups with a bad expert id or bad offsets are flagged in the status word and get no items.
-__device__ __forceinline__ void build_ftable(const TensorArgs& a, FGroup* grp, int64_t* base, int64_t* warp_tot) {
+__device__ __forceinline__ void build_ftable(const TensorArgs& a, FGroup* grp, int64_t* base, int64_t* warp_tot,
+                                             int32_t tiles) {
     const int t = threadIdx.x, lane = t & 31, w = t >> 5;
     int64_t items = 0;
     if (t < a.g.G) {
@@ -128,7 +200,7 @@ __device__ __forceinline__ void build_ftable(const TensorArgs& a, FGroup* grp, i
         // equal chunks, a multiple of 16 rows each (the MMA's N granularity)
         gr.chunk_rows = chunks ? (((gr.rows + chunks - 1) / chunks + 15) & ~15) : 0;
         grp[t] = gr;
-        items = (int64_t)chunks * a.c_tiles;
+        items = (int64_t)chunks * tiles;
     }
     int64_t incl = items;
 #pragma unroll
@@ -175,7 +247,7 @@ __device__ __forceinline__ void decode8_regs(const uint32_t w, float scale, uint
     }
 }
 
-template <int FMT, int SDT>
+template <int FMT, int SDT, int CG>
 __global__ void __launch_bounds__(kFThreads, 1)
 tensor_fwd_kernel(const TensorArgs a, const __grid_constant__ CUtensorMap x_map) {
     extern __shared__ uint8_t smem_raw[];
@@ -185,25 +257,43 @@ tensor_fwd_kernel(const TensorArgs a, const __grid_constant__ CUtensorMap x_map)
     FGroup* s_grp = reinterpret_cast<FGroup*>(grp_raw);
     int64_t* s_base = reinterpret_cast<int64_t*>(grp_raw + kFMaxGroups * 16);
     int64_t* s_wtot = s_base + kFMaxGroups + 1;
-    uint64_t* full_x = reinterpret_cast<uint64_t*>(grp_raw + kFGroupBytes);
-    uint64_t* full_w = full_x + kFStages;
-    uint64_t* empty = full_w + kFStages;
-    uint64_t* acc_full = empty + kFStages;
+    // full[s]: the stage's activations (TMA transaction bytes + the producer's arrival) and its decoded
+    // weights (one arrival per decode warp of the group) are in place
+    // One barrier ring of kFRing slots serves both pipelines; stage number seq uses slot seq % kFRing,
+    // tensor-memory slot seq % kFStages for its decoded weights and shared-memory slot seq % XS for
+    // its activations (XS = 4 tiles of 32 KiB, or 8 half tiles of 16 KiB in a CTA pair).
+    //   full[slot]  activations landed (TMA bytes + the producer's arrival) and weights decoded
+    //               (one arrival per decode warp); in a pair only the leader's is used and the
+    //               peer's warps arrive on it remotely
+    //   done[slot]  the stage's MMAs have completed: its two slots may be refilled
+    //   x_local[slot]  peer CTA only: its own TMA landed (the relay forwards this to the leader)
+    uint64_t* full = reinterpret_cast<uint64_t*>(grp_raw + kFGroupBytes);
+    uint64_t* done = full + kFRing;
+    uint64_t* x_local = done + kFRing;
+    uint64_t* acc_full = x_local + kFRing;
     uint64_t* acc_empty = acc_full + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    // CG = 2: the two CTAs of a cluster share every item -- same row chunk, neighbouring column
+    // tiles; rank 0 (the leader) issues the MMAs for both
+    const uint32_t rank = (CG == 2) ? cluster_ctarank() : 0u;
+    const int64_t worker = (CG == 2) ? (blockIdx.x >> 1) : blockIdx.x;
+    const int64_t workers = (CG == 2) ? (gridDim.x >> 1) : gridDim.x;
+    const int32_t tiles = (CG == 2) ? (a.c_tiles + 1) / 2 : a.c_tiles;
+    constexpr uint32_t XS = (CG == 2) ? 8 : 4;                  // activation slots
+    constexpr uint32_t kXBytes = (CG == 2) ? kTATile : kFXTile; // bytes per activation slot
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kFStages; ++s) {
-            mbar_init(full_x + s, 1);
-            mbar_init(full_w + s, 8);
-            mbar_init(empty + s, 1);
+        for (int s = 0; s < kFRing; ++s) {
+            mbar_init(full + s, CG == 2 ? 2 * (1 + 8) : 1 + 8);
+            mbar_init(done + s, 1);
+            mbar_init(x_local + s, 1);
         }
         mbar_init(acc_full, 1);
-        mbar_init(acc_empty, kFEpiWarps);
+        mbar_init(acc_empty, kFEpiWarps * CG);
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -221,10 +311,11 @@ tensor_fwd_kernel(const TensorArgs a, const __grid_constant__ CUtensorMap x_map)
             tab[i] = pack_bf16x2(p.y, p.x);
         }
     }
-    build_ftable(a, s_grp, s_base, s_wtot);
+    build_ftable(a, s_grp, s_base, s_wtot, tiles);
     const FTable tb{s_grp, s_base};
     tc_fence_before();
-    __syncthreads();
+    if (CG == 2) cluster_sync_all();      // the peer's barriers exist before anything arrives on them
+    else __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_a0 = tmem_base + kFTok;          // A stages start after the 256 accumulator columns
@@ -235,53 +326,123 @@ tensor_fwd_kernel(const TensorArgs a, const __grid_constant__ CUtensorMap x_map)
         if (lane == 0) {
             FCursor cur;
             FItem it;
-            uint32_t stage = 0, phase = 0;
+            uint32_t seq = 0;
             bool ok = true;
-            for (int64_t id = blockIdx.x; ok && next_fitem(a, tb, cur, id, &it); id += gridDim.x) {
-                const int boxes = it.tokens > kTBM ? 2 : 1;
-                for (int rb = 0; rb < a.r_blocks && ok; ++rb) {
-                    ok = mbar_wait_bounded(empty + stage, phase ^ 1, abort_flag);
-                    if (!ok) break;
-                    uint8_t* st = smem + (size_t)stage * kFXTile;
-                    mbar_arrive_expect_tx(full_x + stage, (uint32_t)(boxes * kTATile));
+            for (int64_t id = worker; ok && next_fitem(a, tb, cur, id, &it, tiles, CG, (int32_t)rank); id += workers) {
+                // CG = 1: the whole chunk, two 128-row boxes when it has more than 128 rows.
+                // CG = 2: this CTA's half of the MMA's N = round_up(tokens, 16) rows, one box.
+                const int boxes = (CG == 1 && it.tokens > kTBM) ? 2 : 1;
+                const int row_first = it.row0 + (CG == 2 ? (int)rank * (((it.tokens + 15) & ~15) >> 1) : 0);
+                for (int rb = 0; rb < a.r_blocks && ok; ++rb, ++seq) {
+                    if (seq >= XS) {             // the slot's previous stage has been multiplied
+                        ok = mbar_wait_bounded(done + ((seq - XS) & (kFRing - 1)), ((seq - XS) / kFRing) & 1, abort_flag);
+                        if (!ok) break;
+                    }
+                    uint8_t* st = smem + (size_t)(seq % XS) * kXBytes;
+                    uint64_t* bar = ((CG == 2 && rank == 1) ? x_local : full) + (seq & (kFRing - 1));
+                    mbar_arrive_expect_tx(bar, (uint32_t)(boxes * kTATile));
                     for (int b = 0; b < boxes; ++b)
-                        tma_load_2d(st + b * kTATile, &x_map, rb * kTBR, it.row0 + b * kTBM, full_x + stage);
-                    if (++stage == kFStages) { stage = 0; phase ^= 1; }
+                        tma_load_2d(st + b * kTATile, &x_map, rb * kTBR, row_first + b * kTBM, bar);
                 }
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        if (lane == 0 && rank == 0) {
             FCursor cur;
             FItem it;
-            uint32_t stage = 0, phase = 0, acc_phase = 0;
+            uint32_t seq = 0, acc_phase = 0;
             bool ok = true;
-            for (int64_t id = blockIdx.x; ok && next_fitem(a, tb, cur, id, &it); id += gridDim.x) {
+            const uint32_t peer_done = (CG == 2) ? map_to_cta(smem_u32(done), 1) : 0u;
+            const uint32_t peer_acc_full = (CG == 2) ? map_to_cta(smem_u32(acc_full), 1) : 0u;
+            auto wait_full = [&](uint32_t q_) {
+                uint64_t* bar = full + (q_ & (kFRing - 1));
+                const uint32_t par = (q_ / kFRing) & 1;
+                return (CG == 2) ? mbar_wait_bounded_cluster(bar, par, abort_flag) : mbar_wait_bounded(bar, par, abort_flag);
+            };
+            for (int64_t id = worker; ok && next_fitem(a, tb, cur, id, &it, tiles, CG, (int32_t)rank); id += workers) {
                 const uint32_t n_umma = (uint32_t)((it.tokens + 15) & ~15);
-                // kind::f16: fp32 accumulate, bf16 x bf16, both K-major, M = 128, N = n_umma
-                const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((n_umma >> 3) << 17) | ((kTBM >> 4) << 24);
-                ok = mbar_wait_bounded(acc_empty, acc_phase ^ 1, abort_flag);
+                // kind::f16: fp32 accumulate, bf16 x bf16, both K-major, M = 128 per CTA, N = n_umma
+                const uint32_t idesc =
+                    (1u << 4) | (1u << 7) | (1u << 10) | ((n_umma >> 3) << 17) | (((uint32_t)(kTBM * CG) >> 4) << 24);
+                ok = (CG == 2) ? mbar_wait_bounded_cluster(acc_empty, acc_phase ^ 1, abort_flag)
+                               : mbar_wait_bounded(acc_empty, acc_phase ^ 1, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
-                for (int rb = 0; rb < a.r_blocks && ok; ++rb) {
-                    ok = mbar_wait_bounded(full_x + stage, phase, abort_flag) &&
-                         mbar_wait_bounded(full_w + stage, phase, abort_flag);
-                    if (!ok) break;
-                    tc_fence_after();
-                    const uint32_t xs = smem_u32(smem + (size_t)stage * kFXTile);
-                    const uint32_t a_hi = tmem_a0 + stage * kFAcols;
+                // Between the last MMA of a stage and the first of the next this thread does nothing but
+                // address arithmetic: the tensor pipe keeps only a short queue, so every cycle spent
+                // there on a barrier, a fence or a commit is a cycle the pipe idles.  Hence the wait
+                // (and fence) for stage s + 1 sits before the last k-step of stage s, and the commit
+                // of stage s after the first k-step of stage s + 1 (it then also covers that k-step,
+                // which frees the slots of stage s one MMA later -- harmless).
+                bool primed = false, pending = false;
+                uint32_t pending_slot = 0;
+                auto commit_done = [&](uint32_t slot) {
+                    if (CG == 2) {
+                        tc_commit2(smem_u32(done + slot));
+                        tc_commit2(peer_done + slot * 8);
+                    } else {
+                        tc_commit(done + slot);
+                    }
+                };
+                for (int rb = 0; rb < a.r_blocks && ok; ++rb, ++seq) {
+                    if (!primed) {
+                        ok = wait_full(seq);
+                        if (!ok) break;
+                        tc_fence_after();
+                    }
+                    primed = false;
+                    const uint32_t xs = smem_u32(smem + (size_t)(seq % XS) * kXBytes);
+                    const uint32_t a_hi = tmem_a0 + (seq & (kFStages - 1)) * kFAcols;
 #pragma unroll
                     for (int j = 0; j < kTBR / 16; ++j) {
+                        if (j == kTBR / 16 - 1 && rb + 1 < a.r_blocks) {
+                            ok = wait_full(seq + 1);
+                            tc_fence_after();
+                            primed = true;
+                        }
                         const uint64_t db = umma_desc(xs + j * 32, 16, 1024);
-                        tc_mma_bf16_ts(tmem_base, a_hi + j * 8, db, idesc, (rb > 0 || j > 0) ? 1u : 0u);
-                        if (FMT == GNF4B_FMT_NF4) tc_mma_bf16_ts(tmem_base, a_hi + 32 + j * 8, db, idesc, 1u);
+                        const uint32_t acc = (rb > 0 || j > 0) ? 1u : 0u;
+                        if (CG == 2) {
+                            tc_mma_bf16_ts2(tmem_base, a_hi + j * 8, db, idesc, acc);
+                            if (FMT == GNF4B_FMT_NF4) tc_mma_bf16_ts2(tmem_base, a_hi + 32 + j * 8, db, idesc, 1u);
+                        } else {
+                            tc_mma_bf16_ts(tmem_base, a_hi + j * 8, db, idesc, acc);
+                            if (FMT == GNF4B_FMT_NF4) tc_mma_bf16_ts(tmem_base, a_hi + 32 + j * 8, db, idesc, 1u);
+                        }
+                        if (j == 0 && pending) {
+                            commit_done(pending_slot);
+                            pending = false;
+                        }
                     }
-                    tc_commit(empty + stage);
-                    if (++stage == kFStages) { stage = 0; phase ^= 1; }
+                    pending = true;
+                    pending_slot = seq & (kFRing - 1);
                 }
-                if (ok) tc_commit(acc_full);
+                if (pending) commit_done(pending_slot);
+                if (ok) {
+                    if (CG == 2) {
+                        tc_commit2(smem_u32(acc_full));
+                        tc_commit2(peer_acc_full);
+                    } else {
+                        tc_commit(acc_full);
+                    }
+                }
                 acc_phase ^= 1;
+            }
+        } else if (lane == 0 && CG == 2) {
+            // -------------------------------------------------------- relay (rank 1): forward "my
+            // activations have landed" to the leader's full barrier
+            FCursor cur;
+            FItem it;
+            uint32_t seq = 0;
+            bool ok = true;
+            const uint32_t leader_full = map_to_cta(smem_u32(full), 0);
+            for (int64_t id = worker; ok && next_fitem(a, tb, cur, id, &it, tiles, CG, (int32_t)rank); id += workers) {
+                for (int rb = 0; rb < a.r_blocks && ok; ++rb, ++seq) {
+                    ok = mbar_wait_bounded(x_local + (seq & (kFRing - 1)), (seq / kFRing) & 1, abort_flag);
+                    if (!ok) break;
+                    mbar_arrive_cluster(leader_full + (seq & (kFRing - 1)) * 8);
+                }
             }
         }
     } else if (warp < kFDecWarp0) {
@@ -293,28 +454,28 @@ tensor_fwd_kernel(const TensorArgs a, const __grid_constant__ CUtensorMap x_map)
         uint32_t acc_phase = 0;
         bool ok = true;
         uint16_t* out = reinterpret_cast<uint16_t*>(a.g.out);
+        const uint32_t leader_acc_empty = (CG == 2) ? map_to_cta(smem_u32(acc_empty), 0) : 0u;
+        auto release_acc = [&]() {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                if (CG == 2) mbar_arrive_cluster(leader_acc_empty);
+                else mbar_arrive(acc_empty);
+            }
+        };
         const bool pair_ok = (a.C % 2) == 0;
-        for (int64_t id = blockIdx.x; ok && next_fitem(a, tb, cur, id, &it); id += gridDim.x) {
+        for (int64_t id = worker; ok && next_fitem(a, tb, cur, id, &it, tiles, CG, (int32_t)rank); id += workers) {
             ok = mbar_wait_bounded(acc_full, acc_phase, abort_flag);
             if (!ok) break;
             tc_fence_after();
             const int64_t n = (int64_t)it.c0 + q * 32 + lane;          // this lane's output column
             const int chunks = (it.tokens + 31) >> 5;
-            if (e >= chunks) {                           // nothing to drain for this warp
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(acc_empty);
-            }
+            if (e >= chunks) release_acc();              // nothing to drain for this warp
             for (int c = e; c < chunks; c += 2) {
                 uint32_t r[32];
                 tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
                 tmem_ld_wait();
-                if (c + 2 >= chunks) {
-                    // every accumulator value this warp needs is in registers: hand the buffer back
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(acc_empty);
-                }
+                if (c + 2 >= chunks) release_acc();      // all this warp needs is in registers
                 const int t0 = c * 32;
                 if (pair_ok) {
                     // lanes 2i and 2i+1 swap one value: the even lane stores (n, n+1) of token j,
@@ -359,16 +520,16 @@ tensor_fwd_kernel(const TensorArgs a, const __grid_constant__ CUtensorMap x_map)
         // the fetch cursor runs one own stage ahead of the stage being decoded and crosses items
         FCursor cur;
         FItem it;
-        int64_t id = blockIdx.x;
-        bool have = next_fitem(a, tb, cur, id, &it);
+        int64_t id = worker;
+        bool have = next_fitem(a, tb, cur, id, &it, tiles, CG, (int32_t)rank);
         int rb = grp;
         uint4 pk_n = make_uint4(0, 0, 0, 0);
         float sc_n = 0.f;
         auto settle = [&]() {                      // bring (it, rb) to the next existing stage
             while (have && rb >= a.r_blocks) {
                 rb -= a.r_blocks;
-                id += gridDim.x;
-                have = next_fitem(a, tb, cur, id, &it);
+                id += workers;
+                have = next_fitem(a, tb, cur, id, &it, tiles, CG, (int32_t)rank);
             }
         };
         auto fetch = [&]() {
@@ -384,8 +545,9 @@ tensor_fwd_kernel(const TensorArgs a, const __grid_constant__ CUtensorMap x_map)
         };
         settle();
         if (have) fetch();
-        uint32_t stage = grp, phase = 0;
+        uint32_t seq = grp;
         bool ok = true;
+        const uint32_t leader_full = (CG == 2) ? map_to_cta(smem_u32(full), 0) : 0u;
         while (have && ok) {
             const uint4 pk = pk_n;
             const float sc = sc_n;
@@ -393,11 +555,12 @@ tensor_fwd_kernel(const TensorArgs a, const __grid_constant__ CUtensorMap x_map)
             settle();
             if (have) fetch();
             const bool more = have;
-            ok = mbar_wait_bounded(empty + stage, phase ^ 1, abort_flag);
+            if (seq >= kFStages)             // the tensor-memory slot's previous stage has been multiplied
+                ok = mbar_wait_bounded(done + ((seq - kFStages) & (kFRing - 1)), ((seq - kFStages) / kFRing) & 1, abort_flag);
             if (ok) {
                 const uint32_t s16 = __float_as_uint(sc) >> 16;
                 const uint32_t s2 = s16 | (s16 << 16);
-                const uint32_t col = col0 + stage * kFAcols;
+                const uint32_t col = col0 + (seq & (kFStages - 1)) * kFAcols;
                 const uint32_t w4[4] = {pk.x, pk.y, pk.z, pk.w};
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
@@ -410,9 +573,11 @@ tensor_fwd_kernel(const TensorArgs a, const __grid_constant__ CUtensorMap x_map)
                 tmem_st_wait();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(full_w + stage);
-                stage += 2;
-                if (stage >= kFStages) { stage -= kFStages; phase ^= 1; }
+                if (lane == 0) {
+                    if (CG == 2) mbar_arrive_cluster(leader_full + (seq & (kFRing - 1)) * 8);
+                    else mbar_arrive(full + (seq & (kFRing - 1)));
+                }
+                seq += 2;
             }
             have = more;
         }
@@ -421,7 +586,9 @@ tensor_fwd_kernel(const TensorArgs a, const __grid_constant__ CUtensorMap x_map)
     // ---------------------------------------------------------------- teardown
     __syncwarp();
     tc_fence_before();
-    __syncthreads();
+    // CG = 2: neither CTA may free its tensor memory or leave while the pair's MMAs can still read it
+    if (CG == 2) cluster_sync_all();
+    else __syncthreads();
     if (warp == 1) {
         __syncwarp();
         tc_fence_after();
@@ -430,9 +597,9 @@ tensor_fwd_kernel(const TensorArgs a, const __grid_constant__ CUtensorMap x_map)
     if (threadIdx.x == 0 && *abort_flag && a.g.status) atomicOr(a.g.status, GNF4B_ST_TIMEOUT);
 }
 
-template <int FMT, int SDT>
+template <int FMT, int SDT, int CG>
 static int launch_tensor_fwd_t(const TensorArgs& ta, const CUtensorMap& map, int sm_count, size_t smem, cudaStream_t st) {
-    auto kfn = tensor_fwd_kernel<FMT, SDT>;
+    auto kfn = tensor_fwd_kernel<FMT, SDT, CG>;
     static int granted[64];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return GNF4B_ECUDA;
@@ -442,13 +609,36 @@ static int launch_tensor_fwd_t(const TensorArgs& ta, const CUtensorMap& map, int
             return GNF4B_ECUDA;
         granted[dev] = (int)smem;
     }
-    kfn<<<sm_count, kFThreads, smem, st>>>(ta, map);
-    return cudaPeekAtLastError() == cudaSuccess ? GNF4B_OK : GNF4B_ECUDA;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(CG == 2 ? (sm_count & ~1) : sm_count));
+    cfg.blockDim = dim3(kFThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CG;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, kfn, ta, map) != cudaSuccess) return GNF4B_ECUDA;
+    return GNF4B_OK;
+}
+
+template <int CG>
+static int launch_tensor_fwd_cg(int fmt, int s_dtype, const TensorArgs& ta, const CUtensorMap& map, int sm_count,
+                                size_t smem, cudaStream_t st) {
+    if (fmt == GNF4B_FMT_NF4 && s_dtype == GNF4B_S_F32)
+        return launch_tensor_fwd_t<GNF4B_FMT_NF4, GNF4B_S_F32, CG>(ta, map, sm_count, smem, st);
+    if (fmt == GNF4B_FMT_NF4)
+        return launch_tensor_fwd_t<GNF4B_FMT_NF4, GNF4B_S_BF16, CG>(ta, map, sm_count, smem, st);
+    return launch_tensor_fwd_t<GNF4B_FMT_MXFP4, GNF4B_S_E8M0, CG>(ta, map, sm_count, smem, st);
 }
 
 // Forward with the weight tile in tensor memory.  Same preconditions as launch_tensor.
+// `pair` = run as CTA pairs (cta_group::2 MMAs, each CTA loads half of the activation tile).
 static int launch_tensor_fwd(int fmt, int s_dtype, const GemmArgs& g, int sm_count, int smem_optin, int w_align,
-                             cudaStream_t st) {
+                             bool pair, cudaStream_t st) {
     if (g.x_dtype != GNF4B_X_BF16) return GNF4B_EUNSUPPORTED;
     TensorArgs ta;
     ta.g = g;
@@ -472,10 +662,8 @@ static int launch_tensor_fwd(int fmt, int s_dtype, const GemmArgs& g, int sm_cou
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return GNF4B_EUNSUPPORTED;
-    if (fmt == GNF4B_FMT_NF4 && s_dtype == GNF4B_S_F32)
-        return launch_tensor_fwd_t<GNF4B_FMT_NF4, GNF4B_S_F32>(ta, map, sm_count, smem, st);
-    if (fmt == GNF4B_FMT_NF4) return launch_tensor_fwd_t<GNF4B_FMT_NF4, GNF4B_S_BF16>(ta, map, sm_count, smem, st);
-    return launch_tensor_fwd_t<GNF4B_FMT_MXFP4, GNF4B_S_E8M0>(ta, map, sm_count, smem, st);
+    if (pair && sm_count >= 2) return launch_tensor_fwd_cg<2>(fmt, s_dtype, ta, map, sm_count, smem, st);
+    return launch_tensor_fwd_cg<1>(fmt, s_dtype, ta, map, sm_count, smem, st);
 }
 
 }  // namespace gnf4b

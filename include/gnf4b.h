@@ -44,6 +44,8 @@ extern "C" {
 #define GNF4B_PATH_MASK    3u
 #define GNF4B_SPLITK_SHIFT 8    /* bits 8..15: forced split-K factor, 0 = planner     */
 #define GNF4B_SPLITK_MASK  0xff00u
+#define GNF4B_FLAG_CTA_PAIR      0x20000u /* forward tensor kernel as CTA pairs (cta_group::2 MMAs, each CTA
+                                            loads half of the activation tile); default: single CTAs */
 #define GNF4B_FLAG_SMEM_OPERANDS 0x10000u /* ablation: forward on the first tensor kernel (both MMA
                                             operands in shared memory) instead of weights in TMEM */
 

@@ -70,7 +70,8 @@ def test_prefill_nf4_vs_oracle(N, K, sizes, ids):
 def test_both_forward_tensor_kernels_agree(fmt, sizes):
     """Forward runs on the kernel that keeps decoded weights in tensor memory; the first tensor kernel
     (both operands in shared memory) stays reachable as an ablation and serves dgrad.  Same products in the
-    same k order: the two must agree to bf16 resolution, and both with the oracle.  Chunk boundaries
+    same k order: the two must agree to bf16 resolution, and both with the oracle; the CTA-pair form
+    of the forward kernel (cta_group::2, optional) must give the single-CTA bits.  Chunk boundaries
     (256 rows, multiples of 16) and ragged last column tiles are the cases here."""
     N, K = 200, 320
     ids = list(range(len(sizes)))
@@ -84,10 +85,13 @@ def test_both_forward_tensor_kernels_agree(fmt, sizes):
         call = mxfp4_grouped.gemm_mxfp4_grouped
     new = call(a, W, Sc, sizes, ids, path=T)
     old = call(a, W, Sc, sizes, ids, path=T | _gnf4b.FLAG_SMEM_OPERANDS)
+    pair = call(a, W, Sc, sizes, ids, path=T | _gnf4b.FLAG_CTA_PAIR)
     ref = oracle_fwd64(fmt, a, W, Sc, sizes, ids)
     assert rel_fro(new, ref) <= REL_FRO_TOL and rel_fro(old, ref) <= REL_FRO_TOL
     lim = 2 ** -8 * float(np.abs(ref).max())
     assert (new.float() - old.float()).abs().max().item() <= lim
+    # CTA pairs issue the same MMAs in the same order on the same operands: identical bits
+    assert torch.equal(pair, new)
     _clean()
 
 
