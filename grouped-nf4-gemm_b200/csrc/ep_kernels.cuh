@@ -1,0 +1,87 @@
+// Row-wise helpers of the expert-parallel layer: the two elementwise passes that sit between the
+// grouped GEMMs and the exchanges.  Both are HBM-bound (read once, write once, 16-byte accesses)
+// and deterministic.
+#pragma once
+
+#include "common.cuh"
+
+namespace gnf4b {
+
+__device__ __forceinline__ float silu_f32(float x) { return x / (1.0f + expf(-x)); }
+
+// out[r, c] = bf16( silu(gate[r, c]) * up[r, c] ), gate = gu[:, :h], up = gu[:, h:], fp32 math.
+// VEC = 8 (h % 8 == 0, 16-byte aligned rows) or 1.
+template <int VEC>
+__global__ void silu_glu_kernel(const uint16_t* __restrict__ gu, int64_t rows, int64_t h, uint16_t* __restrict__ out) {
+    const int64_t per_row = h / VEC;
+    const int64_t total = rows * per_row;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / per_row, c = (i - r * per_row) * VEC;
+        const uint16_t* g = gu + r * 2 * h + c;
+        if (VEC == 8) {
+            const uint4 gv = __ldg(reinterpret_cast<const uint4*>(g));
+            const uint4 uv = __ldg(reinterpret_cast<const uint4*>(g + h));
+            const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
+            uint32_t ow[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float g0 = __uint_as_float(gw[j] << 16), g1 = __uint_as_float(gw[j] & 0xffff0000u);
+                const float u0 = __uint_as_float(uw[j] << 16), u1 = __uint_as_float(uw[j] & 0xffff0000u);
+                ow[j] = (uint32_t)f32_to_bf16_bits(__fmul_rn(silu_f32(g0), u0)) |
+                        ((uint32_t)f32_to_bf16_bits(__fmul_rn(silu_f32(g1), u1)) << 16);
+            }
+            *reinterpret_cast<uint4*>(out + r * h + c) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+        } else {
+            const float gf = bf16_bits_to_float(g[0]), uf = bf16_bits_to_float(g[h]);
+            out[r * h + c] = f32_to_bf16_bits(__fmul_rn(silu_f32(gf), uf));
+        }
+    }
+}
+
+// out[m, :] = bf16( sum_j w[m, j] * rows[pos[m, j], :] ), j = 0..k-1 in order, fp32, multiply and add
+// rounded separately (no fused multiply-add) so that a plain loop of tensor operations gives the same bits.
+// One thread = 8 consecutive columns of one token (VEC = 8) or one column (VEC = 1).
+template <int VEC>
+__global__ void combine_rows_kernel(const uint16_t* __restrict__ rows, const int64_t* __restrict__ pos,
+                                    const float* __restrict__ w, int32_t k, int64_t M, int64_t H, int64_t P,
+                                    uint16_t* __restrict__ out, int32_t* status) {
+    const int64_t per_row = H / VEC;
+    const int64_t total = M * per_row;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t m = i / per_row, c = (i - m * per_row) * VEC;
+        float acc[VEC];
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) acc[v] = 0.f;
+        for (int j = 0; j < k; ++j) {
+            const int64_t p = __ldg(pos + m * k + j);
+            if (p < 0 || p >= P) {                     // never dereferenced
+                if (status) atomicOr(status, GNF4B_ST_BAD_OFFSETS);
+                continue;
+            }
+            const float wj = __ldg(w + m * k + j);
+            const uint16_t* src = rows + p * H + c;
+            if (VEC == 8) {
+                const uint4 rv = __ldg(reinterpret_cast<const uint4*>(src));
+                const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    acc[2 * q] = __fadd_rn(acc[2 * q], __fmul_rn(__uint_as_float(rw[q] << 16), wj));
+                    acc[2 * q + 1] = __fadd_rn(acc[2 * q + 1], __fmul_rn(__uint_as_float(rw[q] & 0xffff0000u), wj));
+                }
+            } else {
+                acc[0] = __fadd_rn(acc[0], __fmul_rn(bf16_bits_to_float(src[0]), wj));
+            }
+        }
+        if (VEC == 8) {
+            uint32_t ow[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+                ow[q] = (uint32_t)f32_to_bf16_bits(acc[2 * q]) | ((uint32_t)f32_to_bf16_bits(acc[2 * q + 1]) << 16);
+            *reinterpret_cast<uint4*>(out + m * H + c) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+        } else {
+            out[m * H + c] = f32_to_bf16_bits(acc[0]);
+        }
+    }
+}
+
+}  // namespace gnf4b

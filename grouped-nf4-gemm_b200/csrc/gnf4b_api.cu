@@ -12,6 +12,7 @@
 #include "decode_kernel.cuh"
 #include "tensor_kernel.cuh"
 #include "tensor_fwd_kernel.cuh"
+#include "ep_kernels.cuh"
 
 namespace gnf4b {
 
@@ -478,6 +479,40 @@ int gnf4b_upload_i32(const int32_t* host_src, int32_t* device_dst, int64_t n, vo
                                     reinterpret_cast<cudaStream_t>(cuda_stream));
     if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(group tables)");
     return GNF4B_OK;
+}
+
+int gnf4b_silu_glu(const void* gate_up, int64_t rows, int64_t h, void* out, void* cuda_stream) {
+    if (rows < 0 || h <= 0 || (rows > 0 && (!gate_up || !out))) return GNF4B_EINVAL;
+    if (rows == 0) return GNF4B_OK;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(cuda_stream);
+    const bool vec = (h % 8) == 0 && ((reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+    const int64_t work = rows * (vec ? h / 8 : h);
+    const int grid = (int)std::min<int64_t>(ceil_div(work, 256), 148 * 16);
+    if (vec)
+        silu_glu_kernel<8><<<grid, 256, 0, st>>>(static_cast<const uint16_t*>(gate_up), rows, h, static_cast<uint16_t*>(out));
+    else
+        silu_glu_kernel<1><<<grid, 256, 0, st>>>(static_cast<const uint16_t*>(gate_up), rows, h, static_cast<uint16_t*>(out));
+    cudaError_t e = cudaPeekAtLastError();
+    return e == cudaSuccess ? GNF4B_OK : cuda_fail(e, "silu_glu launch");
+}
+
+int gnf4b_combine_rows(const void* rows, int64_t P, const int64_t* pos, const float* weights, int32_t k, int64_t M,
+                       int64_t H, void* out, int32_t* status_word, void* cuda_stream) {
+    if (P < 0 || M < 0 || H <= 0 || k <= 0) return GNF4B_EINVAL;
+    if (M > 0 && (!pos || !weights || !out || (P > 0 && !rows))) return GNF4B_EINVAL;
+    if (M == 0) return GNF4B_OK;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(cuda_stream);
+    const bool vec = (H % 8) == 0 && ((reinterpret_cast<uintptr_t>(rows) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+    const int64_t work = M * (vec ? H / 8 : H);
+    const int grid = (int)std::min<int64_t>(ceil_div(work, 256), 148 * 16);
+    if (vec)
+        combine_rows_kernel<8><<<grid, 256, 0, st>>>(static_cast<const uint16_t*>(rows), pos, weights, k, M, H, P,
+                                                     static_cast<uint16_t*>(out), status_word);
+    else
+        combine_rows_kernel<1><<<grid, 256, 0, st>>>(static_cast<const uint16_t*>(rows), pos, weights, k, M, H, P,
+                                                     static_cast<uint16_t*>(out), status_word);
+    cudaError_t e = cudaPeekAtLastError();
+    return e == cudaSuccess ? GNF4B_OK : cuda_fail(e, "combine_rows launch");
 }
 
 int gnf4b_dequant(int fmt, const uint8_t* W, int64_t w_stride_e, int64_t w_stride_n, const void* S,

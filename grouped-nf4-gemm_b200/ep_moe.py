@@ -31,9 +31,43 @@ import torch.distributed as dist
 
 def silu_glu(gu: torch.Tensor) -> torch.Tensor:
     """silu(gate) * up with gate = first half, up = second half of the gate_up output
-    (the split of the reference's offload decode, bench/phase3/offload_decode_235b.py:232-233)."""
+    (the split of the reference's offload decode, bench/phase3/offload_decode_235b.py:232-233).
+    fp32 math, one bf16 rounding.  On a GPU this is one kernel of the library (gnf4b_silu_glu)."""
     h = gu.shape[1] // 2
-    return (torch.nn.functional.silu(gu[:, :h].float()) * gu[:, h:].float()).to(gu.dtype)
+    if gu.is_cuda and gu.dtype == torch.bfloat16 and gu.is_contiguous():
+        import _gnf4b
+        out = torch.empty(gu.shape[0], h, dtype=gu.dtype, device=gu.device)
+        with torch.cuda.device(gu.device):
+            rc = _gnf4b.load().gnf4b_silu_glu(gu.data_ptr(), gu.shape[0], h, out.data_ptr(),
+                                              torch.cuda.current_stream(gu.device).cuda_stream)
+        _gnf4b.check(rc, "gnf4b_silu_glu")
+        return out
+    g, u = gu[:, :h].float(), gu[:, h:].float()
+    return (g / (1.0 + torch.exp(-g)) * u).to(gu.dtype)
+
+
+def combine_rows(rows: torch.Tensor, pos: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+    """out[m] = sum_j weights[m, j] * rows[pos[m, j]], j in order, fp32 (multiply and add rounded
+    separately), one rounding to the row dtype.  Deterministic -- unlike an index_add of the pairs.
+    On a GPU one kernel of the library (gnf4b_combine_rows); the loop below gives the same bits."""
+    M, k = pos.shape
+    H = rows.shape[1]
+    if rows.is_cuda and rows.dtype == torch.bfloat16 and rows.is_contiguous():
+        import _gnf4b
+        import nf4_grouped
+        out = torch.empty(M, H, dtype=rows.dtype, device=rows.device)
+        pos64 = pos.to(torch.int64).contiguous()
+        w32 = weights.to(torch.float32).contiguous()
+        with torch.cuda.device(rows.device):
+            rc = _gnf4b.load().gnf4b_combine_rows(rows.data_ptr(), rows.shape[0], pos64.data_ptr(), w32.data_ptr(), k, M, H,
+                                                  out.data_ptr(), nf4_grouped._status_word(rows.device).data_ptr(),
+                                                  torch.cuda.current_stream(rows.device).cuda_stream)
+        _gnf4b.check(rc, "gnf4b_combine_rows")
+        return out
+    acc = torch.zeros(M, H, dtype=torch.float32, device=rows.device)
+    for j in range(k):
+        acc = acc + rows[pos[:, j]].float() * weights[:, j].to(torch.float32)[:, None]
+    return acc.to(rows.dtype)
 
 
 def plan_dispatch(idx: torch.Tensor, n_experts: int, world: int):
@@ -47,21 +81,30 @@ def plan_dispatch(idx: torch.Tensor, n_experts: int, world: int):
     return order, order // k, counts
 
 
-def regroup_index(recv_counts: torch.Tensor):
+def regroup_index(recv_counts: torch.Tensor, total: int | None = None):
     """recv_counts [W, E_local]: rows arrive source-major (source rank, then local expert).
     Returns (perm, sizes): ``recv[perm]`` is expert-major (expert, then source rank, token
-    order kept) and ``sizes[e]`` the rows of local expert e."""
+    order kept) and ``sizes[e]`` the rows of local expert e.  ``total`` = the row count when the
+    caller already has it on the host (saves a device read)."""
     W, E = recv_counts.shape
     rc = recv_counts.to(torch.int64)
     start = (torch.cumsum(rc.reshape(-1), 0) - rc.reshape(-1)).reshape(W, E)   # block starts, source-major
     blk_start = start.t().reshape(-1)                                         # expert-major block order
     blk_len = rc.t().reshape(-1)
-    total = int(blk_len.sum())
+    if total is None:
+        total = int(blk_len.sum())
     if total == 0:
         return torch.empty(0, dtype=torch.int64, device=rc.device), rc.sum(0)
-    within = torch.arange(total, device=rc.device) - torch.repeat_interleave(torch.cumsum(blk_len, 0) - blk_len, blk_len)
-    perm = torch.repeat_interleave(blk_start, blk_len) + within
+    within = torch.arange(total, device=rc.device) - torch.repeat_interleave(torch.cumsum(blk_len, 0) - blk_len, blk_len,
+                                                                               output_size=total)
+    perm = torch.repeat_interleave(blk_start, blk_len, output_size=total) + within
     return perm, rc.sum(0)
+
+
+#: mean rows per (source rank, local expert) block from which the blocks are multiplied where they
+#: landed -- each block its own group, the expert id repeated per source -- instead of being gathered
+#: expert-major first.  Big blocks lose nothing in the GEMM and save two passes over the rows.
+BLOCK_GROUPS_MIN_ROWS = 64
 
 
 class EPGroupedMoE:
@@ -109,34 +152,46 @@ class EPGroupedMoE:
         counts32 = counts.to(torch.int32).contiguous()
         recv_counts = torch.empty_like(counts32)
         self._a2a(recv_counts.reshape(-1), counts32.reshape(-1), None, None)
-        # the exchange needs its split sizes on the host: one small read per layer
-        both = torch.stack((counts32.sum(1), recv_counts.sum(1))).tolist()
-        send_splits, recv_splits = both
+        # work that does not depend on the counts is queued before the host waits for them
         send = hidden[tok]
-        recv = torch.empty(sum(recv_splits), hidden.shape[1], dtype=hidden.dtype, device=dev)
+        pos = torch.empty_like(order)        # pair (m, j) sits at sorted position pos[m * k + j]
+        pos[order] = torch.arange(order.numel(), device=dev)
+        # the exchange needs its split sizes on the host: ONE small read per layer brings both count
+        # tables, everything else about the layer's shape is derived from them on the host
+        host = torch.stack((counts32, recv_counts)).cpu()
+        send_splits, recv_splits = host[0].sum(1).tolist(), host[1].sum(1).tolist()
+        n_recv = sum(recv_splits)
+        recv = torch.empty(n_recv, hidden.shape[1], dtype=hidden.dtype, device=dev)
         self._a2a(recv, send, recv_splits, send_splits)
         self._mark("dispatch")
-        perm, sizes = regroup_index(recv_counts)
-        a_cat = recv[perm]
-        sizes_l = sizes.tolist()
-        self.last_rows = int(a_cat.shape[0])
-        eids = list(range(El))
+        if W > 1 and n_recv >= BLOCK_GROUPS_MIN_ROWS * W * El:
+            perm = None                     # groups = the (source, expert) blocks as they arrived
+            a_cat = recv
+            sizes_l = host[1].reshape(-1).tolist()
+            eids = list(range(El)) * W
+        else:
+            perm, _ = regroup_index(recv_counts, n_recv)
+            a_cat = recv[perm]
+            sizes_l = host[1].sum(0).tolist()
+            eids = list(range(El))
+        self.last_rows = n_recv
         gu = self.grouped_fn(a_cat, self.gate_up[0], self.gate_up[1], sizes_l, eids)
         self._mark("gate_up")
         h = silu_glu(gu)
         self._mark("glu")
         y = self.grouped_fn(h, self.down[0], self.down[1], sizes_l, eids)
         self._mark("down")
-        back = torch.empty_like(recv)
-        back[perm] = y
+        if perm is None:
+            back = y
+        else:
+            back = torch.empty_like(recv)
+            back[perm] = y
         ret = torch.empty_like(send)
         self._a2a(ret, back, send_splits, recv_splits)
         self._mark("combine")
-        out = torch.zeros(hidden.shape[0], hidden.shape[1], dtype=torch.float32, device=dev)
-        w_sorted = weights.reshape(-1)[order].to(torch.float32)
-        out.index_add_(0, tok, ret.float() * w_sorted[:, None])
+        out = combine_rows(ret, pos.reshape(idx.shape), weights)     # the k copies are summed in j order
         self._mark("sum")
-        return out.to(hidden.dtype)
+        return out
 
 
 # --------------------------------------------------------------------------- benchmark leg

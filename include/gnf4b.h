@@ -163,6 +163,20 @@ int gnf4b_dequant(int fmt,
                   const void* S, int s_dtype, int64_t s_stride_e, int64_t s_stride_n,
                   int32_t E, int64_t N, int64_t K, float* out_f32, void* cuda_stream);
 
+/* Expert-parallel layer helpers.  The reference is single-GPU and has no counterpart; its offload
+ * decode applies the same activation on the host side (bench/phase3/offload_decode_235b.py:232-233).
+ *
+ * gnf4b_silu_glu: gate_up [rows, 2h] bf16 -> out [rows, h] bf16 = silu(gate) * up, gate = first half
+ * of each row, fp32 math, one rounding.
+ *
+ * gnf4b_combine_rows: out[m, :] (bf16 [M, H]) = sum_j weights[m, j] * rows[pos[m, j], :] over the k
+ * routed copies of token m, j in order, fp32, multiply and add rounded separately: deterministic, and
+ * equal bit for bit to the same loop written with tensor operations.  rows is bf16 [P, H]; a position
+ * outside [0, P) is skipped and flagged GNF4B_ST_BAD_OFFSETS in the status word. */
+int gnf4b_silu_glu(const void* gate_up, int64_t rows, int64_t h, void* out, void* cuda_stream);
+int gnf4b_combine_rows(const void* rows, int64_t P, const int64_t* pos, const float* weights, int32_t k,
+                       int64_t M, int64_t H, void* out, int32_t* status_word, void* cuda_stream);
+
 /* Device properties this library plans with (SM count, opt-in shared memory). */
 int gnf4b_device_info(int32_t* sm_count, int32_t* smem_optin_bytes);
 

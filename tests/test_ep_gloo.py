@@ -44,9 +44,11 @@ def _tokens(rank, E, H, k, M):
     return x, idx, w
 
 
-def _worker(rank, world, port, fmt, out_q):
+def _worker(rank, world, port, fmt, out_q, block_groups=False):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
+    if block_groups:
+        ep_moe.BLOCK_GROUPS_MIN_ROWS = 0          # multiply the (source, expert) blocks where they landed
     try:
         E, H, I, k, M, gu, dn = _problem(fmt)
         el = E // world
@@ -68,13 +70,15 @@ def _free_port():
         return s.getsockname()[1]
 
 
-@pytest.mark.parametrize("fmt", ["nf4", "mxfp4"])
-def test_two_rank_layer_equals_single_process_layer(fmt):
+@pytest.mark.parametrize("fmt,block_groups", [("nf4", False), ("mxfp4", False), ("nf4", True)])
+def test_two_rank_layer_equals_single_process_layer(fmt, block_groups):
+    """Both ways of forming the local groups -- regrouped expert-major, or one group per (source rank,
+    expert) block as the rows arrived -- must reproduce the single-process layer bit for bit."""
     world = 2
     port = _free_port()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, fmt, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, fmt, q, block_groups)) for r in range(world)]
     for p in procs:
         p.start()
     got = dict()
@@ -114,3 +118,16 @@ def test_plan_and_regroup_are_exact():
     assert perm.tolist() == [0, 1, 3, 4, 5, 6, 2] and sizes.tolist() == [3, 3, 1]
     perm0, sizes0 = ep_moe.regroup_index(torch.zeros(2, 3, dtype=torch.int32))
     assert perm0.numel() == 0 and sizes0.tolist() == [0, 0, 0]
+
+
+def test_combine_rows_is_the_ordered_weighted_sum():
+    gen = torch.Generator().manual_seed(9)
+    M, k, H = 7, 3, 16
+    rows = torch.randn(M * k, H, generator=gen).to(torch.bfloat16)
+    pos = torch.randperm(M * k, generator=gen).reshape(M, k)
+    w = torch.rand(M, k, generator=gen)
+    got = ep_moe.combine_rows(rows, pos, w)
+    want = torch.zeros(M, H)
+    for j in range(k):
+        want = want + rows[pos[:, j]].float() * w[:, j, None]
+    assert torch.equal(got, want.to(torch.bfloat16))

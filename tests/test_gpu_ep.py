@@ -80,3 +80,35 @@ def test_two_gpu_layer_matches_single_gpu_layer():
         want = single.forward(x.to(dev), idx.to(dev), w.to(dev)).float().cpu().numpy()
         scale = np.abs(want).max()
         assert np.abs(got[r] - want).max() <= 2 * 2 ** -8 * scale, r
+
+
+def test_silu_glu_kernel_equals_the_tensor_expression():
+    import ep_moe
+    gen = torch.Generator().manual_seed(1)
+    for rows, h in ((33, 96), (5, 7), (0, 8)):
+        gu = (torch.randn(rows, 2 * h, generator=gen) * 3).to(torch.bfloat16).cuda()
+        got = ep_moe.silu_glu(gu)
+        g, u = gu[:, :h].float(), gu[:, h:].float()
+        want = (g / (1.0 + torch.exp(-g)) * u).to(torch.bfloat16)
+        assert got.shape == (rows, h) and torch.equal(got, want)
+
+
+def test_combine_rows_kernel_equals_the_ordered_loop():
+    import ep_moe
+    import nf4_grouped
+    gen = torch.Generator().manual_seed(2)
+    for M, k, H in ((50, 8, 256), (9, 3, 10)):
+        rows = torch.randn(M * k, H, generator=gen).to(torch.bfloat16).cuda()
+        pos = torch.randperm(M * k, generator=gen).reshape(M, k).cuda()
+        w = torch.rand(M, k, generator=gen).cuda()
+        got = ep_moe.combine_rows(rows, pos, w)
+        want = torch.zeros(M, H, device="cuda")
+        for j in range(k):
+            want = want + rows[pos[:, j]].float() * w[:, j, None]
+        assert torch.equal(got, want.to(torch.bfloat16))
+    assert nf4_grouped.last_status("cuda") == 0
+    # a position outside the rows is skipped and flagged, never dereferenced
+    pos[0, 0] = M * k + 5
+    ep_moe.combine_rows(rows, pos, w)
+    torch.cuda.synchronize()
+    assert nf4_grouped.last_status("cuda") & 2
