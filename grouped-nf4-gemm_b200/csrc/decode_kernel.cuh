@@ -1,7 +1,8 @@
-// Batch-1 decode kernel: every group is ONE activation row, weights are streamed once.
+// Decode kernel: every group has ONE activation row (RM = 1) or at most RM = 2 / 4 rows; weights are
+// streamed once per group and decoded once for all of the group's rows.
 //
 // The tight special case of the streaming path, taken when the host knows that no group has
-// more than one row, K <= 3072, N % 8 == 0 and the stack is laid out so that consecutive
+// more than RM rows, K <= 3072, N % 8 == 0 and the stack is laid out so that consecutive
 // weight rows (and their scale rows) are contiguous and 16-byte aligned.  Then a work item
 // (group, tile of R = 8m weight rows) is ONE contiguous span of packed bytes and ONE
 // contiguous span of scale bytes, so a stage of the ring is filled by two bulk copies
@@ -15,6 +16,8 @@
 //                conflict-free byte-pair table, FMAs against the activation row it keeps in
 //                registers as bf16 pairs, applies the block scale once per unit, warp-shuffle
 //                reduces.  Sixteen warps because the loop is latency-bound, not issue-bound.
+//                RM > 1: eight consumer warps (the RM activation rows need RM x 32 registers per
+//                1024 columns); the table lookups of a unit are shared by the group's rows.
 //
 // Summation order per output element is the same as in stream_kernel.cuh, so both kernels
 // give bit-identical results.
@@ -25,8 +28,8 @@
 
 namespace gnf4b {
 
-constexpr int kDConsumerWarps = 16;
-constexpr int kDThreads = (kDConsumerWarps + 1) * 32;
+__host__ __device__ constexpr int decode_consumer_warps(int rm) { return rm == 1 ? 16 : 8; }
+__host__ __device__ constexpr int decode_threads(int rm) { return (decode_consumer_warps(rm) + 1) * 32; }
 constexpr int kDMaxStages = 8;
 
 struct DecodeArgs {
@@ -58,13 +61,15 @@ __device__ __forceinline__ float2 ld_table(uint32_t addr) {
     return v;
 }
 
-__device__ __forceinline__ float unit_dot_bf16(const uint4 wv, const uint32_t* a16, uint32_t tab_lane) {
+__device__ __forceinline__ void unit_lookup(const uint4 wv, uint32_t tab_lane, float2* p) {
     const uint32_t words[4] = {wv.x, wv.y, wv.z, wv.w};
-    float2 p[16];
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
         for (int b = 0; b < 4; ++b) p[i * 4 + b] = ld_table(tab_lane + prmt(words[i], 0u, 0x4404u | (b << 4)));
+}
+
+__device__ __forceinline__ float unit_fma_bf16(const float2* p, const uint32_t* a16) {
     float part[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -76,6 +81,12 @@ __device__ __forceinline__ float unit_dot_bf16(const uint4 wv, const uint32_t* a
         }
     }
     return (part[0] + part[1]) + (part[2] + part[3]);
+}
+
+__device__ __forceinline__ float unit_dot_bf16(const uint4 wv, const uint32_t* a16, uint32_t tab_lane) {
+    float2 p[16];
+    unit_lookup(wv, tab_lane, p);
+    return unit_fma_bf16(p, a16);
 }
 
 template <int SDT>
@@ -92,7 +103,7 @@ __device__ __forceinline__ float ld_shared_scale(uint32_t row_addr, int idx) {
 }
 
 struct DGroup {
-    int32_t row0, eid;
+    int32_t row0, eid, rows;
     bool valid;
 };
 
@@ -106,6 +117,7 @@ __device__ __forceinline__ DGroup decode_group(const DecodeArgs& a, const int32_
     DGroup d;
     d.row0 = row0;
     d.eid = eid;
+    d.rows = end - row0;
     const bool bad_e = eid < 0 || eid >= a.g.E;
     const bool bad_o = end < row0 || row0 < 0 || end > a.g.T;
     d.valid = !bad_e && !bad_o && end > row0;
@@ -114,8 +126,9 @@ __device__ __forceinline__ DGroup decode_group(const DecodeArgs& a, const int32_
     return d;
 }
 
-template <int FMT, int SDT, int AU>
-__global__ void __launch_bounds__(kDThreads, 1) decode_gemv_kernel(const DecodeArgs a) {
+template <int FMT, int SDT, int AU, int RM>
+__global__ void __launch_bounds__(decode_threads(RM), 1) decode_gemv_kernel(const DecodeArgs a) {
+    constexpr int kDConsumerWarps = decode_consumer_warps(RM);
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* tab_raw = smem;
     uint8_t* ring = smem + kSTableBytes;
@@ -189,22 +202,26 @@ __global__ void __launch_bounds__(kDThreads, 1) decode_gemv_kernel(const DecodeA
     DGroup grp;
     grp.valid = false;
     grp.row0 = 0;
-    uint32_t a16[AU * 16];         // the group's activation row, bf16 pairs, units lane, lane + 32, ...
+    uint32_t a16[RM][AU * 16];     // the group's activation rows, bf16 pairs, units lane, lane + 32, ...
 
     auto load_a = [&](const DGroup& gr) {
-        const uint8_t* xrow = reinterpret_cast<const uint8_t*>(a.g.x) + (int64_t)gr.row0 * a.g.K * 2;
 #pragma unroll
-        for (int q = 0; q < AU; ++q) {
-            const int U = lane + 32 * q;
+        for (int m = 0; m < RM; ++m) {
+            const uint8_t* xrow = reinterpret_cast<const uint8_t*>(a.g.x) + (int64_t)(gr.row0 + m) * a.g.K * 2;
+            const bool have = gr.valid && m < gr.rows;
 #pragma unroll
-            for (int v = 0; v < 4; ++v) {
-                const uint4 raw = (gr.valid && U < n_units)
-                                      ? __ldg(reinterpret_cast<const uint4*>(xrow + (int64_t)U * 64 + v * 16))
-                                      : make_uint4(0, 0, 0, 0);
-                a16[q * 16 + v * 4 + 0] = raw.x;
-                a16[q * 16 + v * 4 + 1] = raw.y;
-                a16[q * 16 + v * 4 + 2] = raw.z;
-                a16[q * 16 + v * 4 + 3] = raw.w;
+            for (int q = 0; q < AU; ++q) {
+                const int U = lane + 32 * q;
+#pragma unroll
+                for (int v = 0; v < 4; ++v) {
+                    const uint4 raw = (have && U < n_units)
+                                          ? __ldg(reinterpret_cast<const uint4*>(xrow + (int64_t)U * 64 + v * 16))
+                                          : make_uint4(0, 0, 0, 0);
+                    a16[m][q * 16 + v * 4 + 0] = raw.x;
+                    a16[m][q * 16 + v * 4 + 1] = raw.y;
+                    a16[m][q * 16 + v * 4 + 2] = raw.z;
+                    a16[m][q * 16 + v * 4 + 3] = raw.w;
+                }
             }
         }
     };
@@ -250,19 +267,55 @@ __global__ void __launch_bounds__(kDThreads, 1) decode_gemv_kernel(const DecodeA
             for (int r = warp; r < rows; r += kDConsumerWarps) {
                 const uint32_t wrow = st + (uint32_t)(r * a.row_bytes);
                 const uint32_t srow = st + (uint32_t)(R * a.row_bytes + r * a.scale_row_bytes);
-                float acc = 0.f;
+                float acc[RM];
+#pragma unroll
+                for (int m = 0; m < RM; ++m) acc[m] = 0.f;
 #pragma unroll
                 for (int q = 0; q < AU; ++q) {
                     const int u = lane + 32 * q;
                     if (u < n_units) {
                         const uint4 wv = ld_shared_u32x4(wrow + u * 16);
                         const float sc = ld_shared_scale<SDT>(srow, (FMT == GNF4B_FMT_NF4) ? (u >> 1) : u);
-                        acc += unit_dot_bf16(wv, &a16[q * 16], tab_lane) * sc;
+                        if (RM == 1) {
+                            acc[0] += unit_dot_bf16(wv, &a16[0][q * 16], tab_lane) * sc;
+                        } else {
+                            // one table lookup per byte for all rows of the group; word by word to keep
+                            // the live registers down; per row the same four chains and the same order
+                            // as unit_fma_bf16
+                            const uint32_t words[4] = {wv.x, wv.y, wv.z, wv.w};
+                            float part[RM][4];
+#pragma unroll
+                            for (int m = 0; m < RM; ++m)
+#pragma unroll
+                                for (int b = 0; b < 4; ++b) part[m][b] = 0.f;
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                float2 p[4];
+#pragma unroll
+                                for (int b = 0; b < 4; ++b) p[b] = ld_table(tab_lane + prmt(words[i], 0u, 0x4404u | (b << 4)));
+#pragma unroll
+                                for (int m = 0; m < RM; ++m) {
+#pragma unroll
+                                    for (int b = 0; b < 4; ++b) {
+                                        const uint32_t ab = a16[m][q * 16 + i * 4 + b];
+                                        part[m][b] = fmaf(p[b].x, __uint_as_float(ab << 16), part[m][b]);
+                                        part[m][b] = fmaf(p[b].y, __uint_as_float(ab & 0xffff0000u), part[m][b]);
+                                    }
+                                }
+                            }
+#pragma unroll
+                            for (int m = 0; m < RM; ++m)
+                                acc[m] += ((part[m][0] + part[m][1]) + (part[m][2] + part[m][3])) * sc;
+                        }
                     }
                 }
 #pragma unroll
-                for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-                if (lane == 0) out_bf[(int64_t)grp.row0 * a.g.N + n0 + r] = f32_to_bf16_bits(acc);
+                for (int m = 0; m < RM; ++m) {
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) acc[m] += __shfl_xor_sync(0xffffffffu, acc[m], o);
+                    if (lane == 0 && m < grp.rows)
+                        out_bf[(int64_t)(grp.row0 + m) * a.g.N + n0 + r] = f32_to_bf16_bits(acc[m]);
+                }
             }
         }
         __syncwarp();

@@ -199,19 +199,28 @@ static cudaError_t launch_stream_au(const StreamArgs& sa, int au, int grid, size
 }
 
 template <int FMT, int SDT>
-static cudaError_t launch_decode_au(const DecodeArgs& da, int au, int grid, size_t smem, cudaStream_t st) {
-#define GNF4B_LAUNCH_D(AUV)                                                                           \
+static cudaError_t launch_decode_au(const DecodeArgs& da, int au, int rm, int grid, size_t smem, cudaStream_t st) {
+#define GNF4B_LAUNCH_D(AUV, RMV)                                                                      \
     do {                                                                                              \
-        auto kfn = decode_gemv_kernel<FMT, SDT, AUV>;                                                 \
+        auto kfn = decode_gemv_kernel<FMT, SDT, AUV, RMV>;                                            \
         static int granted[64];                                                                       \
         cudaError_t e = ensure_smem(kfn, smem, granted);                                              \
         if (e != cudaSuccess) return e;                                                               \
-        kfn<<<grid, kDThreads, smem, st>>>(da);                                                       \
+        kfn<<<grid, decode_threads(RMV), smem, st>>>(da);                                             \
         return cudaGetLastError();                                                                    \
     } while (0)
-    if (au <= 1) GNF4B_LAUNCH_D(1);
-    if (au == 2) GNF4B_LAUNCH_D(2);
-    GNF4B_LAUNCH_D(3);
+    if (rm == 1) {
+        if (au <= 1) GNF4B_LAUNCH_D(1, 1);
+        if (au == 2) GNF4B_LAUNCH_D(2, 1);
+        GNF4B_LAUNCH_D(3, 1);
+    }
+    if (rm == 2) {
+        if (au <= 1) GNF4B_LAUNCH_D(1, 2);
+        if (au == 2) GNF4B_LAUNCH_D(2, 2);
+        GNF4B_LAUNCH_D(3, 2);
+    }
+    if (au <= 1) GNF4B_LAUNCH_D(1, 4);          // rm == 4: the caller keeps au <= 2
+    GNF4B_LAUNCH_D(2, 4);
 #undef GNF4B_LAUNCH_D
 }
 
@@ -369,7 +378,7 @@ int gnf4b_gemm_grouped(int fmt, int op, const void* x, int x_dtype, int64_t T, c
     }
     g.split_k = p.split_k;
     {
-        // Batch-1 decode kernel: one row per group, contiguous 16-byte aligned rows and scale
+        // Decode kernel: at most 4 rows per group, contiguous 16-byte aligned rows and scale
         // rows, so a stage is two bulk copies (see decode_kernel.cuh).
         const int elt = (s_dtype == GNF4B_S_F32) ? 4 : (s_dtype == GNF4B_S_BF16 ? 2 : 1);
         const int64_t blk = (fmt == GNF4B_FMT_NF4) ? 64 : 32;
@@ -377,8 +386,11 @@ int gnf4b_gemm_grouped(int fmt, int op, const void* x, int x_dtype, int64_t T, c
         const bool contiguous = w_stride_n == row_bytes && s_stride_n == K / blk &&
                                 (((uintptr_t)W | (uint64_t)w_stride_e) & 15) == 0 &&
                                 (((uintptr_t)S | (uint64_t)(s_stride_e * elt)) & 15) == 0 && ((8 * srow) & 15) == 0;
-        if (max_rows == 1 && p.split_k == 1 && K <= 3072 && (N % 8) == 0 && contiguous &&
+        // rows held in registers per pass: 1, 2 or 4 (4 only up to K = 2048: 128 registers of activations)
+        const int rm = max_rows == 1 ? 1 : max_rows == 2 ? 2 : (max_rows >= 3 && max_rows <= 4 && K <= 2048) ? 4 : 0;
+        if (rm && p.split_k == 1 && K <= 3072 && (N % 8) == 0 && contiguous &&
             x_dtype == GNF4B_X_BF16) {
+            const int kDConsumerWarps = decode_consumer_warps(rm);
             DecodeArgs da;
             da.g = g;
             // rows per stage: one per consumer warp, more for short rows
@@ -400,11 +412,11 @@ int gnf4b_gemm_grouped(int fmt, int op, const void* x, int x_dtype, int64_t T, c
                 const int au = (int)ceil_div(K, 1024);
                 cudaError_t e;
                 if (fmt == GNF4B_FMT_NF4 && s_dtype == GNF4B_S_F32)
-                    e = launch_decode_au<GNF4B_FMT_NF4, GNF4B_S_F32>(da, au, dgrid, dsmem, st);
+                    e = launch_decode_au<GNF4B_FMT_NF4, GNF4B_S_F32>(da, au, rm, dgrid, dsmem, st);
                 else if (fmt == GNF4B_FMT_NF4)
-                    e = launch_decode_au<GNF4B_FMT_NF4, GNF4B_S_BF16>(da, au, dgrid, dsmem, st);
+                    e = launch_decode_au<GNF4B_FMT_NF4, GNF4B_S_BF16>(da, au, rm, dgrid, dsmem, st);
                 else
-                    e = launch_decode_au<GNF4B_FMT_MXFP4, GNF4B_S_E8M0>(da, au, dgrid, dsmem, st);
+                    e = launch_decode_au<GNF4B_FMT_MXFP4, GNF4B_S_E8M0>(da, au, rm, dgrid, dsmem, st);
                 if (e != cudaSuccess) return cuda_fail(e, "decode kernel launch");
                 return GNF4B_OK;
             }

@@ -219,8 +219,17 @@ __device__ __forceinline__ void build_ftable(const TensorArgs& a, FGroup* grp, i
 }
 
 // 16 packed bytes (32 elements) of one weight row.
+// A thread walks its weight row 16 bytes per own stage; on an L2 miss the load asks L2 for the whole
+// 256 bytes around it, so the next stages of the row hit L2 instead of waiting on HBM each time (the
+// register prefetch is only one own stage deep).
 __device__ __forceinline__ uint4 load_packed16(const uint8_t* p, int w_align) {
-    if (w_align >= 16) return __ldg(reinterpret_cast<const uint4*>(p));
+    if (w_align >= 16) {
+        uint4 v;
+        asm volatile("ld.global.nc.L2::256B.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                     : "l"(p));
+        return v;
+    }
     const uint2 lo = load_packed8(p, w_align), hi = load_packed8(p + 8, w_align);
     return make_uint4(lo.x, lo.y, hi.x, hi.y);
 }

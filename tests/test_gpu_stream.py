@@ -399,3 +399,30 @@ def test_decode_kernel_equals_generic_streaming_kernel_bitwise(fmt, N, K):
     assert torch.equal(dec, gen_out)
     assert rel_fro(dec, oracle_fwd64(fmt, a, W, S, sizes, ids)) <= REL_FRO_TOL
     assert nf4_grouped.last_status(DEV) == 0
+
+
+@pytest.mark.parametrize("fmt,N,K,sizes", [
+    ("nf4", 1536, 2048, [2, 1, 0, 2, 1]), ("nf4", 1536, 2048, [4, 1, 3, 0, 2]), ("nf4", 2048, 768, [3, 4, 4, 1, 2]),
+    ("nf4", 512, 2880 // 64 * 64, [2, 2, 1, 0, 2]), ("mxfp4", 2880, 2880, [1, 2, 2, 0, 1]), ("mxfp4", 64, 96, [4, 0, 3, 1, 4]),
+])
+def test_small_group_decode_kernel_equals_generic_streaming_kernel_bitwise(fmt, N, K, sizes):
+    """Groups of at most 2 (any K <= 3072) or 4 (K <= 2048) rows known on the host take the decode
+    kernel with the group's rows in registers and one table lookup per weight element for all rows;
+    device-side offsets without a row bound take the generic streaming kernel.  Same summation order
+    per output element, same bits."""
+    gen = torch.Generator().manual_seed(K + N + sum(sizes))
+    E = 6
+    if fmt == "nf4":
+        W, S = synth.nf4_stack(E, N, K, gen, device=DEV, fast=True)
+        fn = gemm_4bit_grouped
+    else:
+        W, S = synth.mxfp4_stack(E, N, K, gen, device=DEV, fast=True)
+        fn = mxfp4_grouped.gemm_mxfp4_grouped
+    ids = [4, 0, 2, 4, 5]
+    a = torch.randn(sum(sizes), K, generator=gen).to(torch.bfloat16).to(DEV)
+    dec = fn(a, W, S, sizes, ids, path=_gnf4b.PATH_STREAM)
+    off = torch.tensor([0] + list(np.cumsum(sizes)), dtype=torch.int32, device=DEV)
+    gen_out = fn(a, W, S, None, torch.tensor(ids, dtype=torch.int32, device=DEV), group_offsets=off, path=_gnf4b.PATH_STREAM)
+    assert torch.equal(dec, gen_out)
+    assert rel_fro(dec, oracle_fwd64(fmt, a, W, S, sizes, ids)) <= REL_FRO_TOL
+    assert nf4_grouped.last_status(DEV) == 0
