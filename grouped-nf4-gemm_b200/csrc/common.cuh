@@ -110,6 +110,15 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     }
 }
 
+// Programmatic dependent launch.  A kernel launched with the programmatic-serialization attribute may
+// start while the previous kernel of the stream is still running: everything up to pdl_wait() (barrier
+// set-up, lookup tables) overlaps that kernel's tail; pdl_wait() returns once all earlier grids have
+// completed and their writes are visible, so it must precede the first read of anything an earlier
+// kernel may have written and every global write.  pdl_launch_dependents() lets the NEXT kernel start
+// the same way.  Both are no-ops for a kernel launched without the attribute.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // 1-D bulk copy global -> shared, completion counted on an mbarrier (TMA engine).
 // Both addresses 16-byte aligned, bytes a multiple of 16.
 __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes,

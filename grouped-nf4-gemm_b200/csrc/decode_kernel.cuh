@@ -141,6 +141,7 @@ __global__ void __launch_bounds__(decode_threads(RM), 1) decode_gemv_kernel(cons
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
+    pdl_launch_dependents();
     if (threadIdx.x == 0) {
         for (int s = 0; s < a.stages; ++s) {
             mbar_init(full_bar + s, 1);
@@ -162,6 +163,7 @@ __global__ void __launch_bounds__(decode_threads(RM), 1) decode_gemv_kernel(cons
         // ------------------------------------------------------------ producer (two lanes)
         // lane 0 copies the packed rows, lane 1 the scale rows of the same stage
         if (lane < 2) {
+            pdl_wait();             // group tables (and, for the consumers, activations) may come from the previous kernel
             const int elt = (SDT == GNF4B_S_F32) ? 4 : (SDT == GNF4B_S_BF16 ? 2 : 1);
             const uint8_t* Sb = reinterpret_cast<const uint8_t*>(a.g.S);
             uint32_t stage = 0, phase = 0;
@@ -225,17 +227,11 @@ __global__ void __launch_bounds__(decode_threads(RM), 1) decode_gemv_kernel(cons
             }
         }
     };
-    // The first group's activation row is requested before the table is built, so its
-    // global-memory latency overlaps the table construction.
-    if (item_lo < item_hi) {
-        grp = decode_group(a, s_grp, g);
-        cur_g = g;
-    }
-    load_a(grp);
     {
         // pair table: tab[byte][slot], 32 slots of float2 per byte, all holding the same pair,
         // so a lane reading slot == its lane id never conflicts with another lane.  A half
-        // warp writes one byte's 256-byte row per step with 16-byte stores.
+        // warp writes one byte's 256-byte row per step with 16-byte stores.  Built before
+        // pdl_wait(): it overlaps the tail of the previous kernel.
         const int half = lane >> 4, hl = lane & 15;
 #pragma unroll 4
         for (int j = 0; j < 256 / kDConsumerWarps; j += 2) {
@@ -246,6 +242,12 @@ __global__ void __launch_bounds__(decode_threads(RM), 1) decode_gemv_kernel(cons
                          : "memory");
         }
     }
+    pdl_wait();
+    if (item_lo < item_hi) {
+        grp = decode_group(a, s_grp, g);
+        cur_g = g;
+    }
+    load_a(grp);
     named_bar_sync(1, kDConsumerWarps * 32);
 
     const uint32_t tab_lane = smem_u32(tab_raw) + lane * 8;

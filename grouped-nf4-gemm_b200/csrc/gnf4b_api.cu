@@ -206,8 +206,17 @@ static cudaError_t launch_decode_au(const DecodeArgs& da, int au, int rm, int gr
         static int granted[64];                                                                       \
         cudaError_t e = ensure_smem(kfn, smem, granted);                                              \
         if (e != cudaSuccess) return e;                                                               \
-        kfn<<<grid, decode_threads(RMV), smem, st>>>(da);                                             \
-        return cudaGetLastError();                                                                    \
+        cudaLaunchConfig_t cfg = {};                                                                  \
+        cfg.gridDim = dim3((unsigned)grid);                                                           \
+        cfg.blockDim = dim3(decode_threads(RMV));                                                     \
+        cfg.dynamicSmemBytes = smem;                                                                  \
+        cfg.stream = st;                                                                              \
+        cudaLaunchAttribute attr[1];                                                                  \
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;                              \
+        attr[0].val.programmaticStreamSerializationAllowed = 1;                                       \
+        cfg.attrs = attr;                                                                             \
+        cfg.numAttrs = 1;                                                                             \
+        return cudaLaunchKernelEx(&cfg, kfn, da);                                                     \
     } while (0)
     if (rm == 1) {
         if (au <= 1) GNF4B_LAUNCH_D(1, 1);
