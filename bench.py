@@ -393,16 +393,24 @@ def main():
     if args.impl == "reference":
         if rank != 0:
             return 0
-        cb = time_cpu(shape, args.tokens, args.steps, args.warmup, seed=7, max_rows_per_group=cpu_cut, budget_s=120.0)
-        base = BASELINE_US.get((shape.name, args.tokens))
+        # the whole job of the other arm: tokens per GPU x GPUs (weak scaling), on the host cores
+        n = max(1, args.gpus)
+        job_tokens = args.tokens * n
+        cpu_cut = None if job_tokens * shape.top_k <= 2048 else 2
+        cb = time_cpu(shape, job_tokens, args.steps, args.warmup, seed=7, max_rows_per_group=cpu_cut, budget_s=120.0)
+        if n == 1:
+            workload = (f"{shape.name} {shape.fmt} MoE layer, {args.tokens} tokens per GPU, top-{shape.top_k} of "
+                        f"{shape.experts} experts, gate_up {shape.gate_up} + down {shape.down}")
+        else:
+            workload = (f"{shape.name} {shape.fmt} MoE layer, expert-parallel over {n} GPUs "
+                        f"({shape.experts // n} experts per GPU), {args.tokens} tokens per GPU, top-{shape.top_k}, "
+                        f"dispatch/combine by NCCL all_to_all")
         print(json.dumps({
             "impl": "reference", "metric": "grouped 4-bit MoE GEMM us/layer", "value": cb["value"], "unit": "us/layer",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": cb["value"] / 1e3,
             "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
             "dtype": "fp32 activations x 4-bit weights, fp32 accumulate (CPU)", "data": "synthetic",
-            "config": {"workload": f"{shape.name} {shape.fmt} MoE layer, {args.tokens} tokens, top-{shape.top_k} of "
-                                   f"{shape.experts} experts, gate_up {shape.gate_up} + down {shape.down}",
-                       "tokens": args.tokens},
+            "config": {"workload": workload, "tokens": args.tokens},
             "cpu_baseline": cb,
             "e2e": {"value": cb["value"], "unit": "us/layer", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0,
