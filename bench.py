@@ -280,9 +280,12 @@ def run_gpu(args, shape, rank, world):
                 layer_resident(i, what)
         return g
 
-    def timed_replay(g, repeats):
+    def timed_replay(g, repeats, min_seconds=0.0):
+        """`repeats` timed replays; then more of the same (timed too, at most 500) until `min_seconds` of
+        load have passed, so that the 100 ms clock sampler sees the GPU under this load several times."""
         out = []
-        for _ in range(repeats):
+        t_begin = time.perf_counter()
+        while len(out) < repeats or (time.perf_counter() - t_begin < min_seconds and len(out) < 500):
             barrier()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
@@ -301,7 +304,7 @@ def run_gpu(args, shape, rank, world):
     torch.cuda.synchronize()
 
     with ClockSampler(dev.index) as clk:
-        t_layer = timed_replay(g_layer, args.repeats)
+        t_layer = timed_replay(g_layer, args.repeats, min_seconds=0.5)
         t_gu = timed_replay(g_gu, args.repeats)
         # end to end through the public entry points with host inputs
         for i in range(W):
@@ -357,14 +360,14 @@ def run_gpu(args, shape, rank, world):
                                f"{shape.experts} experts, gate_up {shape.gate_up} + down {shape.down}",
                    "tokens": args.tokens, "layers_resident": args.layers,
                    "l2": f"inputs larger than L2: {args.layers} layer stacks walked round-robin, fresh routing per step",
-                   "timing": f"K steps in one CUDA graph, median of {args.repeats} replays, CUDA events"},
+                   "timing": f"K steps in one CUDA graph, median of {len(t_layer)} replays, CUDA events"},
         "e2e": {"value": us_e2e, "unit": "us/layer", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": 2 * K,
         "roofline": roof,
         "layer": {"decode_gbs": statistics.mean(by_l) / (us_layer * 1e-6) / 1e9,
                   "tflops": statistics.mean(fl_l) / (us_layer * 1e-6) / 1e12,
                   "rows_per_active_expert": rows_per_group, "active_experts": statistics.mean(act)},
-        "clocks": clk.summary(), "device_status": status, "repeats_ms": t_layer,
+        "clocks": clk.summary(), "device_status": status, "repeats_ms": t_layer[:16],
     }
     return line
 
