@@ -1,8 +1,8 @@
-// Decode kernel: every group has ONE activation row (RM = 1) or at most RM = 2 / 4 rows; weights are
-// streamed once per group and decoded once for all of the group's rows.
+// Decode kernel: every group has ONE activation row (RM = 1), or a few: then RM = 2 rows at a time, the
+// weights streamed once per pair of rows and decoded once for both.
 //
 // The tight special case of the streaming path, taken when the host knows that no group has
-// more than RM rows, K <= 3072, N % 8 == 0 and the stack is laid out so that consecutive
+// more than 16 rows, K <= 3072, N % 8 == 0 and the stack is laid out so that consecutive
 // weight rows (and their scale rows) are contiguous and 16-byte aligned.  Then a work item
 // (group, tile of R = 8m weight rows) is ONE contiguous span of packed bytes and ONE
 // contiguous span of scale bytes, so a stage of the ring is filled by two bulk copies
@@ -43,7 +43,9 @@ struct DecodeArgs {
     int32_t stages;             // ring depth, 3..8, as many slots as shared memory holds
     int32_t items_per_cta;      // total_items / grid
     int32_t items_extra;        // total_items % grid: the first items_extra CTAs take one more
-    int64_t total_items;        // G * tiles_per_group
+    int64_t total_items;        // G * row_chunks * tiles_per_group
+    int32_t row_chunks;         // a group's rows are taken rows_per_pass at a time: ceil(max_rows / rows_per_pass)
+    int32_t rows_per_pass;      // RM of the kernel instance
 };
 
 __host__ __device__ inline size_t decode_smem_bytes(int slot_bytes, int stages, int g_cache) {
@@ -107,23 +109,43 @@ struct DGroup {
     bool valid;
 };
 
-__device__ __forceinline__ DGroup decode_group(const DecodeArgs& a, const int32_t* s_grp, int g) {
+// Rows [c * RM, c * RM + RM) of group g.  With row_chunks > 1 a group's rows are taken RM at a time:
+// the work list is (group, row chunk, tile) with the tile fastest, so a CTA keeps one chunk's activation
+// rows in registers for a run of tiles, and the group's weights are streamed once per chunk (the later
+// passes mostly from L2).  Chunks that a group does not have are not in the list (see GroupWalk).
+__device__ __forceinline__ DGroup decode_group(const DecodeArgs& a, int g, int c) {
     // a group changes once per N / R items, so its three ints come straight from global
     // memory (L1-cached) instead of a shared-memory copy that every thread would wait for
-    (void)s_grp;
     const int32_t row0 = __ldg(a.g.off + g);
     const int32_t end = __ldg(a.g.off + g + 1);
     const int32_t eid = __ldg(a.g.eids + g);
     DGroup d;
-    d.row0 = row0;
+    d.row0 = row0 + c * a.rows_per_pass;
     d.eid = eid;
-    d.rows = end - row0;
+    d.rows = min(end - d.row0, a.rows_per_pass);
     const bool bad_e = eid < 0 || eid >= a.g.E;
     const bool bad_o = end < row0 || row0 < 0 || end > a.g.T;
-    d.valid = !bad_e && !bad_o && end > row0;
-    if ((bad_e || bad_o) && end != row0 && a.g.status && (threadIdx.x & 31) == 0)
+    d.valid = !bad_e && !bad_o && d.rows > 0;
+    if ((bad_e || bad_o) && end != row0 && c == 0 && a.g.status && (threadIdx.x & 31) == 0)
         atomicOr(a.g.status, bad_e ? GNF4B_ST_BAD_EXPERT : GNF4B_ST_BAD_OFFSETS);
     return d;
+}
+
+// Position in the list of (group, row chunk) pairs.  Plain mode (row_chunks == 1): pair v is group v.
+// Chunked mode: vb[g] = number of pairs before group g (a prefix sum in shared memory, groups that are
+// empty or flagged have none), so the list holds only chunks that exist.
+struct GroupWalk {
+    int v, g, c;
+};
+__device__ __forceinline__ void walk_to(const DecodeArgs& a, const int32_t* vb, GroupWalk& w, int v) {
+    w.v = v;
+    if (a.row_chunks == 1) {
+        w.g = v;
+        w.c = 0;
+        return;
+    }
+    while (w.g + 1 < a.g.G && vb[w.g + 1] <= v) ++w.g;      // v only ever grows
+    w.c = v - vb[w.g];
 }
 
 template <int FMT, int SDT, int AU, int RM>
@@ -153,11 +175,45 @@ __global__ void __launch_bounds__(decode_threads(RM), 1) decode_gemv_kernel(cons
     __syncthreads();
 
     const int bid = (int)blockIdx.x;
-    const int64_t item_lo = (int64_t)bid * a.items_per_cta + min(bid, a.items_extra);
-    const int64_t item_hi = item_lo + a.items_per_cta + (bid < a.items_extra ? 1 : 0);
+    int64_t item_lo = (int64_t)bid * a.items_per_cta + min(bid, a.items_extra);
+    int64_t item_hi = item_lo + a.items_per_cta + (bid < a.items_extra ? 1 : 0);
+    const int32_t* vb = s_grp;
+    if (a.row_chunks > 1) {
+        // chunked mode: build the prefix sum of the groups' chunk counts (one warp, ordered scan),
+        // then cut the list of existing items evenly over the CTAs
+        pdl_wait();
+        if (warp == 0) {
+            int32_t carry = 0;
+            if (lane == 0) s_grp[0] = 0;
+            for (int base = 0; base < a.g.G; base += 32) {
+                const int gi = base + lane;
+                int32_t n = 0;
+                if (gi < a.g.G) {
+                    const int32_t r0 = __ldg(a.g.off + gi), r1 = __ldg(a.g.off + gi + 1), e = __ldg(a.g.eids + gi);
+                    const bool bad = e < 0 || e >= a.g.E || r1 < r0 || r0 < 0 || r1 > a.g.T;
+                    if (bad && r1 != r0 && a.g.status && bid == 0)
+                        atomicOr(a.g.status, (e < 0 || e >= a.g.E) ? GNF4B_ST_BAD_EXPERT : GNF4B_ST_BAD_OFFSETS);
+                    n = bad ? 0 : min((r1 - r0 + a.rows_per_pass - 1) / a.rows_per_pass, a.row_chunks);
+                }
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int32_t t = __shfl_up_sync(0xffffffffu, n, o);
+                    if (lane >= o) n += t;
+                }
+                if (gi < a.g.G) s_grp[gi + 1] = carry + n;
+                carry += __shfl_sync(0xffffffffu, n, 31);
+            }
+        }
+        __syncthreads();
+        const int64_t total = (int64_t)vb[a.g.G] * a.tiles_per_group;
+        const int64_t per = total / gridDim.x, extra = total % gridDim.x;
+        item_lo = (int64_t)bid * per + min((int64_t)bid, extra);
+        item_hi = item_lo + per + (bid < extra ? 1 : 0);
+    }
     const int R = a.rows_per_stage;
-    int g = (int)((uint32_t)item_lo / (uint32_t)a.tiles_per_group);
-    int tile = (int)((uint32_t)item_lo - (uint32_t)g * (uint32_t)a.tiles_per_group);
+    GroupWalk w{0, 0, 0};
+    walk_to(a, vb, w, (int)((uint32_t)item_lo / (uint32_t)a.tiles_per_group));
+    int tile = (int)((uint32_t)item_lo - (uint32_t)w.v * (uint32_t)a.tiles_per_group);
 
     if (warp == kDConsumerWarps) {
         // ------------------------------------------------------------ producer (two lanes)
@@ -167,12 +223,12 @@ __global__ void __launch_bounds__(decode_threads(RM), 1) decode_gemv_kernel(cons
             const int elt = (SDT == GNF4B_S_F32) ? 4 : (SDT == GNF4B_S_BF16 ? 2 : 1);
             const uint8_t* Sb = reinterpret_cast<const uint8_t*>(a.g.S);
             uint32_t stage = 0, phase = 0;
-            int cur_g = -1;
+            int cur_v = -1;
             DGroup grp;
             grp.valid = false;
             bool ok = true;
             for (int64_t item = item_lo; item < item_hi && ok; ++item) {
-                if (cur_g != g) { grp = decode_group(a, s_grp, g); cur_g = g; }
+                if (cur_v != w.v) { grp = decode_group(a, w.g, w.c); cur_v = w.v; }
                 ok = mbar_wait_bounded(empty_bar + stage, phase ^ 1, abort_flag);
                 if (!ok) break;
                 if (grp.valid) {
@@ -191,7 +247,7 @@ __global__ void __launch_bounds__(decode_threads(RM), 1) decode_gemv_kernel(cons
                     mbar_arrive(full_bar + stage);      // empty group: the stage carries nothing
                 }
                 if (++stage == (uint32_t)a.stages) { stage = 0; phase ^= 1; }
-                if (++tile == a.tiles_per_group) { tile = 0; ++g; }
+                if (++tile == a.tiles_per_group) { tile = 0; walk_to(a, vb, w, w.v + 1); }
             }
             if (!ok && lane == 0 && a.g.status) atomicOr(a.g.status, GNF4B_ST_TIMEOUT);
         }
@@ -200,10 +256,11 @@ __global__ void __launch_bounds__(decode_threads(RM), 1) decode_gemv_kernel(cons
 
     // ---------------------------------------------------------------- consumers
     const int n_units = a.row_bytes >> 4;
-    int cur_g = -1;
+    int cur_v = -1;
     DGroup grp;
     grp.valid = false;
     grp.row0 = 0;
+    grp.rows = 0;
     uint32_t a16[RM][AU * 16];     // the group's activation rows, bf16 pairs, units lane, lane + 32, ...
 
     auto load_a = [&](const DGroup& gr) {
@@ -244,8 +301,8 @@ __global__ void __launch_bounds__(decode_threads(RM), 1) decode_gemv_kernel(cons
     }
     pdl_wait();
     if (item_lo < item_hi) {
-        grp = decode_group(a, s_grp, g);
-        cur_g = g;
+        grp = decode_group(a, w.g, w.c);
+        cur_v = w.v;
     }
     load_a(grp);
     named_bar_sync(1, kDConsumerWarps * 32);
@@ -256,9 +313,9 @@ __global__ void __launch_bounds__(decode_threads(RM), 1) decode_gemv_kernel(cons
     bool poisoned = false;
 
     for (int64_t item = item_lo; item < item_hi; ++item) {
-        if (cur_g != g) {
-            grp = decode_group(a, s_grp, g);
-            cur_g = g;
+        if (cur_v != w.v) {
+            grp = decode_group(a, w.g, w.c);
+            cur_v = w.v;
             load_a(grp);
         }
         if (!poisoned && !mbar_wait_bounded(full_bar + stage, phase, abort_flag)) poisoned = true;
@@ -323,7 +380,7 @@ __global__ void __launch_bounds__(decode_threads(RM), 1) decode_gemv_kernel(cons
         __syncwarp();
         if (!poisoned && lane == 0) mbar_arrive(empty_bar + stage);
         if (++stage == (uint32_t)a.stages) { stage = 0; phase ^= 1; }
-        if (++tile == a.tiles_per_group) { tile = 0; ++g; }
+        if (++tile == a.tiles_per_group) { tile = 0; walk_to(a, vb, w, w.v + 1); }
     }
     if (poisoned && threadIdx.x == 0 && a.g.status) atomicOr(a.g.status, GNF4B_ST_TIMEOUT);
 }

@@ -110,11 +110,11 @@ static int make_plan(int fmt, int op, int64_t T, int32_t G, int64_t N, int64_t K
     const int forced_split = (int)((flags & GNF4B_SPLITK_MASK) >> GNF4B_SPLITK_SHIFT);
     int path = (int)want;
     if (path == GNF4B_PATH_AUTO) {
-        // Streaming kernel while groups are a couple of rows at most (its per-element cost
+        // Streaming kernels while groups are a couple of rows on average (their per-element cost
         // grows with the rows of a group); tensor cores beyond that.  Without a host-known
         // maximum the mean T/G decides.
         const double mean_rows = G > 0 ? (double)T / G : 0.0;
-        const bool small = (max_rows > 0) ? (max_rows <= 4 && mean_rows <= 2.0) : (mean_rows <= 1.5);
+        const bool small = (max_rows > 0) ? (max_rows <= 8 && mean_rows <= 2.0) : (mean_rows <= 1.5);
         path = (op == GNF4B_OP_DGRAD) ? GNF4B_PATH_TENSOR : (small ? GNF4B_PATH_STREAM : GNF4B_PATH_TENSOR);
         if (forced_split > 1 && op == GNF4B_OP_FWD) path = GNF4B_PATH_STREAM;
     }
@@ -226,10 +226,9 @@ static cudaError_t launch_decode_au(const DecodeArgs& da, int au, int rm, int gr
     if (rm == 2) {
         if (au <= 1) GNF4B_LAUNCH_D(1, 2);
         if (au == 2) GNF4B_LAUNCH_D(2, 2);
-        GNF4B_LAUNCH_D(3, 2);
+        if (au == 3) GNF4B_LAUNCH_D(3, 2);
     }
-    if (au <= 1) GNF4B_LAUNCH_D(1, 4);          // rm == 4: the caller keeps au <= 2
-    GNF4B_LAUNCH_D(2, 4);
+    return cudaErrorInvalidValue;
 #undef GNF4B_LAUNCH_D
 }
 
@@ -395,8 +394,9 @@ int gnf4b_gemm_grouped(int fmt, int op, const void* x, int x_dtype, int64_t T, c
         const bool contiguous = w_stride_n == row_bytes && s_stride_n == K / blk &&
                                 (((uintptr_t)W | (uint64_t)w_stride_e) & 15) == 0 &&
                                 (((uintptr_t)S | (uint64_t)(s_stride_e * elt)) & 15) == 0 && ((8 * srow) & 15) == 0;
-        // rows held in registers per pass: 1, 2 or 4 (4 only up to K = 2048: 128 registers of activations)
-        const int rm = max_rows == 1 ? 1 : max_rows == 2 ? 2 : (max_rows >= 3 && max_rows <= 4 && K <= 2048) ? 4 : 0;
+        // rows of a group held in registers per pass: 1, or 2 with larger groups taken two rows at a
+        // time (their weights are streamed once per pass; up to 8 passes)
+        const int rm = max_rows == 1 ? 1 : (max_rows == 2 || (max_rows >= 3 && max_rows <= 16 && G <= p.g_cache)) ? 2 : 0;
         if (rm && p.split_k == 1 && K <= 3072 && (N % 8) == 0 && contiguous &&
             x_dtype == GNF4B_X_BF16) {
             const int kDConsumerWarps = decode_consumer_warps(rm);
@@ -410,7 +410,9 @@ int gnf4b_gemm_grouped(int fmt, int op, const void* x, int x_dtype, int64_t T, c
             da.scale_row_bytes = (int32_t)srow;
             da.slot_bytes = (int32_t)round_up((int64_t)da.rows_per_stage * (row_bytes + srow), 128);
             da.g_cache = p.g_cache;
-            da.total_items = (int64_t)G * da.tiles_per_group;
+            da.rows_per_pass = rm;
+            da.row_chunks = (max_rows + rm - 1) / rm;
+            da.total_items = (int64_t)G * da.row_chunks * da.tiles_per_group;
             const int64_t room = (int64_t)di.smem_optin - (int64_t)decode_smem_bytes(0, 0, da.g_cache);
             da.stages = (int32_t)std::min<int64_t>(kDMaxStages, room / da.slot_bytes);
             const int dgrid = (int)std::min<int64_t>(di.sm_count, da.total_items);

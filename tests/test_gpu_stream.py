@@ -404,12 +404,13 @@ def test_decode_kernel_equals_generic_streaming_kernel_bitwise(fmt, N, K):
 @pytest.mark.parametrize("fmt,N,K,sizes", [
     ("nf4", 1536, 2048, [2, 1, 0, 2, 1]), ("nf4", 1536, 2048, [4, 1, 3, 0, 2]), ("nf4", 2048, 768, [3, 4, 4, 1, 2]),
     ("nf4", 512, 2880 // 64 * 64, [2, 2, 1, 0, 2]), ("mxfp4", 2880, 2880, [1, 2, 2, 0, 1]), ("mxfp4", 64, 96, [4, 0, 3, 1, 4]),
+    ("nf4", 256, 2048, [7, 1, 0, 16, 2]), ("mxfp4", 2880, 2880, [5, 1, 1, 0, 3]),
 ])
 def test_small_group_decode_kernel_equals_generic_streaming_kernel_bitwise(fmt, N, K, sizes):
-    """Groups of at most 2 (any K <= 3072) or 4 (K <= 2048) rows known on the host take the decode
-    kernel with the group's rows in registers and one table lookup per weight element for all rows;
-    device-side offsets without a row bound take the generic streaming kernel.  Same summation order
-    per output element, same bits."""
+    """Groups of a few rows (known on the host) take the decode kernel two rows at a time -- both rows
+    in registers, one table lookup per weight element for both, one pass over the group's weights per
+    pair of rows; device-side offsets without a row bound take the generic streaming kernel.  Same
+    summation order per output element, same bits."""
     gen = torch.Generator().manual_seed(K + N + sum(sizes))
     E = 6
     if fmt == "nf4":
