@@ -126,8 +126,9 @@ __device__ __forceinline__ DGroup decode_group(const DecodeArgs& a, int g, int c
     const bool bad_e = eid < 0 || eid >= a.g.E;
     const bool bad_o = end < row0 || row0 < 0 || end > a.g.T;
     d.valid = !bad_e && !bad_o && d.rows > 0;
-    if ((bad_e || bad_o) && end != row0 && c == 0 && a.g.status && (threadIdx.x & 31) == 0)
-        atomicOr(a.g.status, bad_e ? GNF4B_ST_BAD_EXPERT : GNF4B_ST_BAD_OFFSETS);
+    const bool pad = eid == GNF4B_PAD_EXPERT;        // padding group: skipped, not an error
+    if (((bad_e && !pad) || bad_o) && end != row0 && c == 0 && a.g.status && (threadIdx.x & 31) == 0)
+        atomicOr(a.g.status, (bad_e && !pad) ? GNF4B_ST_BAD_EXPERT : GNF4B_ST_BAD_OFFSETS);
     return d;
 }
 
@@ -191,8 +192,9 @@ __global__ void __launch_bounds__(decode_threads(RM), 1) decode_gemv_kernel(cons
                 if (gi < a.g.G) {
                     const int32_t r0 = __ldg(a.g.off + gi), r1 = __ldg(a.g.off + gi + 1), e = __ldg(a.g.eids + gi);
                     const bool bad = e < 0 || e >= a.g.E || r1 < r0 || r0 < 0 || r1 > a.g.T;
-                    if (bad && r1 != r0 && a.g.status && bid == 0)
-                        atomicOr(a.g.status, (e < 0 || e >= a.g.E) ? GNF4B_ST_BAD_EXPERT : GNF4B_ST_BAD_OFFSETS);
+                    const bool bad_off = r1 < r0 || r0 < 0 || r1 > a.g.T;
+                    if (bad && r1 != r0 && (bad_off || e != GNF4B_PAD_EXPERT) && a.g.status && bid == 0)
+                        atomicOr(a.g.status, bad_off ? GNF4B_ST_BAD_OFFSETS : GNF4B_ST_BAD_EXPERT);
                     n = bad ? 0 : min((r1 - r0 + a.rows_per_pass - 1) / a.rows_per_pass, a.row_chunks);
                 }
 #pragma unroll

@@ -101,8 +101,9 @@ __device__ __forceinline__ StreamItem walker_item(const StreamArgs& a, const int
         const bool bad_e = w.eid < 0 || w.eid >= a.g.E;
         const bool bad_o = w.rows < 0 || w.row0 < 0 || (int64_t)w.row0 + w.rows > a.g.T;
         w.gvalid = !bad_e && !bad_o && w.rows > 0;
-        if ((bad_e || bad_o) && w.rows != 0 && a.g.status && (threadIdx.x & 31) == 0)
-            atomicOr(a.g.status, bad_e ? GNF4B_ST_BAD_EXPERT : GNF4B_ST_BAD_OFFSETS);
+        const bool pad = w.eid == GNF4B_PAD_EXPERT;      // padding group: skipped, not an error
+        if (((bad_e && !pad) || bad_o) && w.rows != 0 && a.g.status && (threadIdx.x & 31) == 0)
+            atomicOr(a.g.status, (bad_e && !pad) ? GNF4B_ST_BAD_EXPERT : GNF4B_ST_BAD_OFFSETS);
         w.loaded_g = w.g;
     }
     StreamItem it;

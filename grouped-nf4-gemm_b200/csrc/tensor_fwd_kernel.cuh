@@ -194,8 +194,9 @@ __device__ __forceinline__ void build_ftable(const TensorArgs& a, FGroup* grp, i
         gr.eid = __ldg(a.g.eids + t);
         const bool bad_e = gr.eid < 0 || gr.eid >= a.g.E;
         const bool bad_o = gr.rows < 0 || gr.row0 < 0 || (int64_t)gr.row0 + gr.rows > a.g.T;
-        if ((bad_e || bad_o) && gr.rows != 0 && a.g.status && blockIdx.x == 0)
-            atomicOr(a.g.status, bad_e ? GNF4B_ST_BAD_EXPERT : GNF4B_ST_BAD_OFFSETS);
+        const bool pad = gr.eid == GNF4B_PAD_EXPERT;     // padding group: skipped, not an error
+        if (((bad_e && !pad) || bad_o) && gr.rows != 0 && a.g.status && blockIdx.x == 0)
+            atomicOr(a.g.status, (bad_e && !pad) ? GNF4B_ST_BAD_EXPERT : GNF4B_ST_BAD_OFFSETS);
         const int32_t chunks = (bad_e || bad_o || gr.rows <= 0) ? 0 : (gr.rows + kFTok - 1) / kFTok;
         // equal chunks, a multiple of 16 rows each (the MMA's N granularity)
         gr.chunk_rows = chunks ? (((gr.rows + chunks - 1) / chunks + 15) & ~15) : 0;

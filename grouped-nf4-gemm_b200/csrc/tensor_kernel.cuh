@@ -175,8 +175,9 @@ __device__ __forceinline__ bool next_item(const TensorArgs& a, ItemCursor& cur, 
             cur.eid = __ldg(a.g.eids + cur.g);
             const bool bad_e = cur.eid < 0 || cur.eid >= a.g.E;
             const bool bad_o = cur.rows < 0 || cur.row0 < 0 || (int64_t)cur.row0 + cur.rows > a.g.T;
-            if ((bad_e || bad_o) && cur.rows != 0 && a.g.status && threadIdx.x == 0 && blockIdx.x == 0)
-                atomicOr(a.g.status, bad_e ? GNF4B_ST_BAD_EXPERT : GNF4B_ST_BAD_OFFSETS);
+            const bool pad = cur.eid == GNF4B_PAD_EXPERT;    // padding group: skipped, not an error
+            if (((bad_e && !pad) || bad_o) && cur.rows != 0 && a.g.status && threadIdx.x == 0 && blockIdx.x == 0)
+                atomicOr(a.g.status, (bad_e && !pad) ? GNF4B_ST_BAD_EXPERT : GNF4B_ST_BAD_OFFSETS);
             cur.chunks = (bad_e || bad_o || cur.rows <= 0) ? 0 : (cur.rows + kTBM * kTMT - 1) / (kTBM * kTMT);
             cur.loaded = true;
         }

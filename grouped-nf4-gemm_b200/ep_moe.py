@@ -16,6 +16,12 @@ expert, ``kernel/mxfp4_qlora.py:294-329``), with one exchange each way:
   5. COMBINE: the reverse all_to_all_single of the bf16 output rows;
   6. un-sort and routing-weight sum in fp32.
 
+Small batches (decode) take a FIXED-CAPACITY exchange instead: every rank sends every rank a buffer
+of C = tokens * top_k rows (the most one destination can get), counts travel in a second equal-split
+exchange, and the received buffer is multiplied where it lies -- one group per (source, expert) plus one
+padding group per source for the unused capacity (expert id -1: skipped by the kernels).  Nothing is read
+back to the host, so the layer is a fixed sequence of launches.
+
 The collectives are NCCL over NVLink/NVSwitch on GPUs and gloo in the CPU tests; the GEMM is
 injectable (``grouped_fn``) so the exchange logic can be tested on CPU ranks against the
 oracle.  There is no TMA multicast anywhere on this path.
@@ -77,7 +83,9 @@ def plan_dispatch(idx: torch.Tensor, n_experts: int, world: int):
     k = idx.shape[1]
     flat = idx.reshape(-1)
     order = torch.argsort(flat, stable=True)
-    counts = torch.bincount(flat, minlength=n_experts).reshape(world, n_experts // world)
+    # scatter_add, not bincount: bincount reads its maximum back to the host
+    counts = torch.zeros(n_experts, dtype=torch.int64, device=flat.device).scatter_add_(
+        0, flat.to(torch.int64), torch.ones_like(flat, dtype=torch.int64)).reshape(world, n_experts // world)
     return order, order // k, counts
 
 
@@ -99,6 +107,14 @@ def regroup_index(recv_counts: torch.Tensor, total: int | None = None):
                                                                                output_size=total)
     perm = torch.repeat_interleave(blk_start, blk_len, output_size=total) + within
     return perm, rc.sum(0)
+
+
+#: bytes of exchange buffer (world * capacity * hidden * 2) up to which the fixed-capacity, host-sync-free
+#: exchange is used; above it the exact-size exchange (one host read per layer) moves fewer bytes
+FIXED_CAPACITY_MAX_BYTES = 4 << 20
+
+#: expert id of a padding group (include/gnf4b.h: GNF4B_PAD_EXPERT)
+PAD_EXPERT = -1
 
 
 #: mean rows per (source rank, local expert) block from which the blocks are multiplied where they
@@ -127,6 +143,7 @@ class EPGroupedMoE:
                 from mxfp4_grouped import gemm_mxfp4_grouped as grouped_fn
         self.grouped_fn = grouped_fn
         self.timers = None           # set to a dict of CUDA-event lists to get a phase breakdown
+        self._fixed_eids = None      # expert ids of the fixed-capacity path's groups (built once per device)
         self.last_rows = 0
 
     # -- helpers ---------------------------------------------------------------
@@ -148,6 +165,9 @@ class EPGroupedMoE:
         W, El = self.world, self.e_local
         dev = hidden.device
         self._mark("start")
+        cap = idx.numel()                    # rows one destination can get from this rank at most
+        if W > 1 and W * cap * hidden.shape[1] * hidden.element_size() <= FIXED_CAPACITY_MAX_BYTES:
+            return self._forward_fixed(hidden, idx, weights, cap)
         order, tok, counts = plan_dispatch(idx, self.n_experts, W)
         counts32 = counts.to(torch.int32).contiguous()
         recv_counts = torch.empty_like(counts32)
@@ -190,6 +210,50 @@ class EPGroupedMoE:
         self._a2a(ret, back, send_splits, recv_splits)
         self._mark("combine")
         out = combine_rows(ret, pos.reshape(idx.shape), weights)     # the k copies are summed in j order
+        self._mark("sum")
+        return out
+
+
+    def _forward_fixed(self, hidden, idx, weights, cap):
+        """The layer with fixed-capacity exchanges: no host read, a fixed sequence of launches."""
+        W, El = self.world, self.e_local
+        dev = hidden.device
+        H = hidden.shape[1]
+        order, tok, counts = plan_dispatch(idx, self.n_experts, W)          # counts [W, El]
+        counts32 = counts.to(torch.int32).contiguous()
+        recv_counts = torch.empty_like(counts32)
+        self._a2a(recv_counts.reshape(-1), counts32.reshape(-1), None, None)
+        # pair p (sorted order) goes to rank d(p) at row p - start[d] of that rank's buffer
+        per_dest = counts.sum(1)
+        start = torch.cumsum(per_dest, 0) - per_dest
+        dest = torch.repeat_interleave(torch.arange(W, device=dev), per_dest, output_size=order.numel())
+        slot = dest * cap + (torch.arange(order.numel(), device=dev) - start[dest])
+        send = torch.zeros(W * cap, H, dtype=hidden.dtype, device=dev)
+        send[slot] = hidden[tok]
+        recv = torch.empty_like(send)
+        self._a2a(recv, send, None, None)
+        self._mark("dispatch")
+        # groups as the rows lie: per source its El expert blocks, then the unused capacity as padding
+        rc = recv_counts.to(torch.int64)
+        sizes = torch.cat((rc, (cap - rc.sum(1, keepdim=True))), 1).reshape(-1)         # [W * (El + 1)]
+        offsets = torch.zeros(sizes.numel() + 1, dtype=torch.int32, device=dev)
+        offsets[1:] = torch.cumsum(sizes, 0).to(torch.int32)
+        if self._fixed_eids is None or self._fixed_eids.device != dev:
+            self._fixed_eids = torch.tensor((list(range(El)) + [PAD_EXPERT]) * W, dtype=torch.int32, device=dev)
+        self.last_rows = W * cap
+        gu = self.grouped_fn(recv, self.gate_up[0], self.gate_up[1], None, self._fixed_eids,
+                             group_offsets=offsets, max_rows=cap)
+        self._mark("gate_up")
+        h = silu_glu(gu)
+        self._mark("glu")
+        y = self.grouped_fn(h, self.down[0], self.down[1], None, self._fixed_eids, group_offsets=offsets, max_rows=cap)
+        self._mark("down")
+        ret = torch.empty_like(y)
+        self._a2a(ret, y, None, None)
+        self._mark("combine")
+        pos = torch.empty_like(order)
+        pos[order] = slot                       # pair (m, j) comes back at the row it was sent from
+        out = combine_rows(ret, pos.reshape(idx.shape), weights)
         self._mark("sum")
         return out
 
@@ -237,14 +301,45 @@ def bench_ep(args, shape, rank, world, B):
 
     for i in range(Wm):
         run(i, False)
+    # The fixed-capacity path reads nothing back to the host, so the K steps can be one CUDA graph
+    # (collectives included), like the single-GPU arm; the exact-size path is timed eagerly.
+    cap_bytes = world * args.tokens * shape.top_k * shape.hidden * 2
+    graph, timing = None, "K eager steps, CUDA events, max over ranks"
+    if cap_bytes <= FIXED_CAPACITY_MAX_BYTES and os.environ.get("GNF4B_EP_GRAPH", "1") != "0":
+        try:
+            barrier()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for i in range(Wm, Wm + K):
+                    run(i, False)
+            torch.cuda.current_stream().wait_stream(side)
+            barrier()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for i in range(Wm, Wm + K):
+                    run(i, False)
+            graph.replay()
+            barrier()
+            timing = "K steps (fixed-capacity exchange, no host read) in one CUDA graph incl. the collectives, CUDA events, max over ranks"
+        except Exception as exc:      # capture of the collectives not available: time eagerly
+            if os.environ.get("GNF4B_EP_DEBUG"):
+                import traceback
+                traceback.print_exc()
+            graph = None
+            timing += f" (graph capture failed: {type(exc).__name__}: {str(exc)[:160]})"
+            torch.cuda.synchronize()
     with B.ClockSampler(dev.index) as clk:
         t_res = []
         for _ in range(max(1, args.repeats // 2)):
             barrier()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            for i in range(Wm, Wm + K):
-                run(i, False)
+            if graph is not None:
+                graph.replay()
+            else:
+                for i in range(Wm, Wm + K):
+                    run(i, False)
             e1.record()
             barrier()
             t_res.append(e0.elapsed_time(e1))
@@ -299,7 +394,7 @@ def bench_ep(args, shape, rank, world, B):
                                f"dispatch/combine by NCCL all_to_all",
                    "tokens": args.tokens, "layers_resident": n_layers, "zipf": zipf,
                    "l2": "inputs larger than L2 per step: resident layer stacks walked round-robin, fresh routing per step",
-                   "timing": "K eager steps, CUDA events, max over ranks"},
+                   "timing": timing},
         "e2e": {"value": ms_e2e * 1e3 / K, "unit": "us/layer",
                 "h2d_bytes_per_step": args.tokens * (shape.hidden * 2 + shape.top_k * 12),
                 "d2h_bytes_per_step": args.tokens * shape.hidden * 2},

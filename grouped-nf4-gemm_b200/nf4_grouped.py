@@ -36,6 +36,9 @@ NF4_LUT = [
     0.44070982933044434, 0.5626170039176941, 0.7229568362236023, 1.0,
 ]
 BLOCKSIZE = 64
+#: expert id of a padding group: its rows are skipped and its output rows left untouched
+#: (include/gnf4b.h GNF4B_PAD_EXPERT; no counterpart in the reference)
+PAD_EXPERT = -1
 
 # Product-layer hints of the reference (ref :605-606); kept so callers that consult
 # decode_dispatch() keep working.  They were measured on sm_86 and do not steer this op.
@@ -402,7 +405,7 @@ def _group_tables(sizes, expert_ids, T: int, E: int, dev, group_offsets=None, ma
         ids = [int(v) for v in (expert_ids.tolist() if torch.is_tensor(expert_ids) else expert_ids)]
         if len(ids) != G:
             raise ValueError(f"sizes has {G} groups but expert_ids has {len(ids)}")
-        if any(v < 0 or v >= E for v in ids):
+        if any((v < 0 and v != PAD_EXPERT) or v >= E for v in ids):
             raise ValueError(f"expert id out of range for a stack of {E} experts")
     else:
         if expert_ids.numel() != G:

@@ -59,6 +59,10 @@ extern "C" {
 #define GNF4B_ETOOBIG      -6   /* size beyond a stated fixed maximum                 */
 
 /* bits a kernel may OR into *status_word (device int32) */
+/* expert_ids[g] == GNF4B_PAD_EXPERT marks a padding group: its rows are skipped (the output rows are left
+ * untouched) and nothing is flagged.  Lets a caller leave gaps in the row matrix -- e.g. unused capacity of a
+ * fixed-size exchange buffer -- without compacting it.  The reference has no such id (its ids are always valid). */
+#define GNF4B_PAD_EXPERT (-1)
 #define GNF4B_ST_BAD_EXPERT  1  /* an expert id outside [0,E) was skipped             */
 #define GNF4B_ST_BAD_OFFSETS 2  /* group_offsets not monotone / beyond T; group skipped */
 #define GNF4B_ST_TIMEOUT     4  /* a bounded device-side wait gave up                 */

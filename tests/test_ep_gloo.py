@@ -17,9 +17,22 @@ from oracle import oracle as O
 
 
 def _oracle_grouped(fmt):
-    def fn(a_cat, W, S, sizes, eids):
-        ref = O.gemm_grouped_f64(fmt, a_cat.float().numpy(), W.numpy(), S.numpy(), list(sizes), list(eids))
-        return torch.from_numpy(ref).to(torch.float32).to(torch.bfloat16)
+    """The grouped GEMM's contract on the CPU: groups by sizes or by offsets, padding groups (expert id -1)
+    skipped with their output rows left alone (zero here)."""
+    def fn(a_cat, W, S, sizes, eids, group_offsets=None, max_rows=None):
+        if group_offsets is not None:
+            off = group_offsets.tolist()
+            sizes = [off[i + 1] - off[i] for i in range(len(off) - 1)]
+        sizes = [int(v) for v in sizes]
+        eids = [int(v) for v in (eids.tolist() if torch.is_tensor(eids) else eids)]
+        out = torch.zeros(a_cat.shape[0], W.shape[1], dtype=torch.bfloat16)
+        row = 0
+        for n, e in zip(sizes, eids):
+            if n and e != ep_moe.PAD_EXPERT:
+                ref = O.gemm_grouped_f64(fmt, a_cat[row:row + n].float().numpy(), W.numpy(), S.numpy(), [n], [e])
+                out[row:row + n] = torch.from_numpy(ref).to(torch.float32).to(torch.bfloat16)
+            row += n
+        return out
     return fn
 
 
@@ -44,10 +57,12 @@ def _tokens(rank, E, H, k, M):
     return x, idx, w
 
 
-def _worker(rank, world, port, fmt, out_q, block_groups=False):
+def _worker(rank, world, port, fmt, out_q, mode="regroup"):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
-    if block_groups:
+    if mode != "fixed":
+        ep_moe.FIXED_CAPACITY_MAX_BYTES = 0       # exact-size exchange (one host read per layer)
+    if mode == "blocks":
         ep_moe.BLOCK_GROUPS_MIN_ROWS = 0          # multiply the (source, expert) blocks where they landed
     try:
         E, H, I, k, M, gu, dn = _problem(fmt)
@@ -70,15 +85,17 @@ def _free_port():
         return s.getsockname()[1]
 
 
-@pytest.mark.parametrize("fmt,block_groups", [("nf4", False), ("mxfp4", False), ("nf4", True)])
-def test_two_rank_layer_equals_single_process_layer(fmt, block_groups):
-    """Both ways of forming the local groups -- regrouped expert-major, or one group per (source rank,
-    expert) block as the rows arrived -- must reproduce the single-process layer bit for bit."""
+@pytest.mark.parametrize("fmt,mode", [("nf4", "regroup"), ("mxfp4", "regroup"), ("nf4", "blocks"), ("nf4", "fixed"),
+                                      ("mxfp4", "fixed")])
+def test_two_rank_layer_equals_single_process_layer(fmt, mode):
+    """All three ways of exchanging and grouping -- exact-size exchange with rows regrouped expert-major,
+    the same with one group per (source rank, expert) block as the rows arrived, and the fixed-capacity
+    exchange with padding groups and no host read -- must reproduce the single-process layer bit for bit."""
     world = 2
     port = _free_port()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, fmt, q, block_groups)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, fmt, q, mode)) for r in range(world)]
     for p in procs:
         p.start()
     got = dict()
@@ -97,7 +114,8 @@ def test_two_rank_layer_equals_single_process_layer(fmt, block_groups):
         want = single.forward(x, idx, w)
         assert np.array_equal(got[r][0], want.view(torch.int16).numpy()), f"rank {r}"
         total_rows += got[r][1]
-    assert total_rows == world * M * k          # every pair landed on exactly one rank
+    if mode != "fixed":
+        assert total_rows == world * M * k      # every pair landed on exactly one rank
 
 
 def test_plan_and_regroup_are_exact():

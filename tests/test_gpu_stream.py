@@ -427,3 +427,41 @@ def test_small_group_decode_kernel_equals_generic_streaming_kernel_bitwise(fmt, 
     assert torch.equal(dec, gen_out)
     assert rel_fro(dec, oracle_fwd64(fmt, a, W, S, sizes, ids)) <= REL_FRO_TOL
     assert nf4_grouped.last_status(DEV) == 0
+
+
+@pytest.mark.parametrize("path", [_gnf4b.PATH_STREAM, _gnf4b.PATH_TENSOR])
+@pytest.mark.parametrize("carrier", ["host", "device"])
+def test_padding_groups_are_skipped_silently(path, carrier):
+    """A group whose expert id is PAD_EXPERT (-1) is a gap in the row matrix: nothing is computed for its
+    rows, their output rows are left as they were, and the status word stays clean (any other id outside
+    [0, E) is skipped too but flagged)."""
+    N, K, E = 256, 512, 4
+    gen = torch.Generator().manual_seed(77)
+    W, S = synth.nf4_stack(E, N, K, gen, device=DEV, fast=True)
+    sizes, ids = [2, 3, 1, 4, 2], [1, nf4_grouped.PAD_EXPERT, 3, nf4_grouped.PAD_EXPERT, 0]
+    a = torch.randn(sum(sizes), K, generator=gen).to(torch.bfloat16).to(DEV)
+    if carrier == "host":
+        out = gemm_4bit_grouped(a, W, S, sizes, ids, path=path)
+    else:
+        off = torch.tensor([0] + list(np.cumsum(sizes)), dtype=torch.int32, device=DEV)
+        out = gemm_4bit_grouped(a, W, S, None, torch.tensor(ids, dtype=torch.int32, device=DEV), group_offsets=off,
+                                max_rows=max(sizes), path=path)
+    real = [(0, 2, 1), (5, 6, 3), (10, 12, 0)]
+    for r0, r1, e in real:
+        ref = oracle_fwd64("nf4", a[r0:r1], W, S, [r1 - r0], [e])
+        assert rel_fro(out[r0:r1], ref) <= 2 ** -8
+    assert nf4_grouped.last_status(DEV) == 0
+    # the padded rows were not written: run again into a poisoned output through the C ABI
+    lib = _gnf4b.load()
+    off = torch.tensor([0] + list(np.cumsum(sizes)), dtype=torch.int32, device=DEV)
+    idt = torch.tensor(ids, dtype=torch.int32, device=DEV)
+    poison = torch.full((sum(sizes), N), 7.0, dtype=torch.bfloat16, device=DEV)
+    rc = lib.gnf4b_gemm_grouped(_gnf4b.FMT_NF4, _gnf4b.OP_FWD, a.data_ptr(), _gnf4b.X_BF16, a.shape[0], W.data_ptr(), W.stride(0),
+                                W.stride(1), S.data_ptr(), _gnf4b.S_F32, S.stride(0), S.stride(1), off.data_ptr(), idt.data_ptr(),
+                                len(ids), E, N, K, max(sizes), poison.data_ptr(), None, 0,
+                                nf4_grouped._status_word(DEV).data_ptr(), path, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert torch.all(poison[2:5] == 7.0) and torch.all(poison[6:10] == 7.0)
+    assert torch.equal(poison[0:2], out[0:2]) and torch.equal(poison[10:12], out[10:12])
+    assert nf4_grouped.last_status(DEV) == 0
