@@ -151,6 +151,15 @@ __device__ __forceinline__ uint32_t ld_shared_u32(uint32_t addr) {
     return v;
 }
 
+// Group table in shared memory (NF4 only: its lookup table leaves 30 KiB of the table region free; at most
+// kTTabGroups groups): row range, expert id and the number of items before the group.  Without it every
+// role walks the groups through global memory -- three dependent loads per group, a dozen groups per step
+// of a CTA -- which costs the MMA issuer thousands of cycles between two items.
+constexpr int kTTabGroups = 640;
+struct TGrp {
+    int32_t row0, rows, eid, base;
+};
+
 // Walks the item space in increasing item id.  Every role of a CTA runs the same walk.
 struct ItemCursor {
     int32_t g = 0;
@@ -167,7 +176,22 @@ struct TItem {
     int32_t mts;       // row tiles in this item (1..kTMT)
 };
 
-__device__ __forceinline__ bool next_item(const TensorArgs& a, ItemCursor& cur, int64_t id, TItem* it) {
+__device__ __forceinline__ bool next_item(const TensorArgs& a, ItemCursor& cur, int64_t id, TItem* it,
+                                          const TGrp* tab = nullptr) {
+    if (tab) {
+        while (cur.g < a.g.G && id >= tab[cur.g + 1].base) cur.g++;
+        if (cur.g >= a.g.G) return false;
+        const TGrp gr = tab[cur.g];
+        const int32_t local = (int32_t)(id - gr.base);
+        const int32_t mc = local / a.c_tiles;
+        const int32_t ct = local - mc * a.c_tiles;
+        it->row0 = gr.row0 + mc * kTBM * kTMT;
+        it->row_end = gr.row0 + gr.rows;
+        it->eid = gr.eid;
+        it->c0 = ct * kTBC;
+        it->mts = min(kTMT, (it->row_end - it->row0 + kTBM - 1) / kTBM);
+        return true;
+    }
     while (cur.g < a.g.G) {
         if (!cur.loaded) {
             cur.row0 = __ldg(a.g.off + cur.g);
@@ -306,9 +330,46 @@ tensor_gemm_kernel(const TensorArgs a, const __grid_constant__ CUtensorMap x_map
     }
     // decode table, one copy per lane so lookups never conflict: NF4 lut[code][lane] fp32,
     // MXFP4 tab[byte][lane] bf16x2 (doubled e2m1 pair).
+    const TGrp* gtab = nullptr;
     if (FMT == GNF4B_FMT_NF4) {
         float* tab = reinterpret_cast<float*>(tab_raw);
         for (int i = threadIdx.x; i < 16 * 32; i += kTThreads) tab[i] = kNf4Lut[i >> 5];
+        if (a.g.G <= kTTabGroups && a.g.G <= kTThreads) {
+            // one thread per group, block-wide inclusive scan of the item counts
+            TGrp* gt = reinterpret_cast<TGrp*>(tab_raw + 2048);
+            int32_t* wtot = reinterpret_cast<int32_t*>(tab_raw + 2048 + (kTTabGroups + 1) * 16);
+            const int t = threadIdx.x;
+            int32_t items = 0;
+            TGrp gr{0, 0, 0, 0};
+            if (t < a.g.G) {
+                gr.row0 = __ldg(a.g.off + t);
+                gr.rows = __ldg(a.g.off + t + 1) - gr.row0;
+                gr.eid = __ldg(a.g.eids + t);
+                const bool bad_e = gr.eid < 0 || gr.eid >= a.g.E;
+                const bool bad_o = gr.rows < 0 || gr.row0 < 0 || (int64_t)gr.row0 + gr.rows > a.g.T;
+                const bool pad = gr.eid == GNF4B_PAD_EXPERT;
+                if (((bad_e && !pad) || bad_o) && gr.rows != 0 && a.g.status && blockIdx.x == 0)
+                    atomicOr(a.g.status, (bad_e && !pad) ? GNF4B_ST_BAD_EXPERT : GNF4B_ST_BAD_OFFSETS);
+                const int32_t chunks = (bad_e || bad_o || gr.rows <= 0) ? 0 : (gr.rows + kTBM * kTMT - 1) / (kTBM * kTMT);
+                items = chunks * a.c_tiles;
+            }
+            int32_t incl = items;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int32_t up = __shfl_up_sync(0xffffffffu, incl, d);
+                if (lane >= d) incl += up;
+            }
+            if (lane == 31) wtot[warp] = incl;
+            __syncthreads();
+            int32_t before = 0;
+            for (int v = 0; v < warp; ++v) before += wtot[v];
+            if (t < a.g.G) {
+                gr.base = before + incl - items;
+                gt[t] = gr;
+                if (t == a.g.G - 1) gt[a.g.G] = TGrp{0, 0, 0, before + incl};
+            }
+            gtab = gt;
+        }
     } else {
         uint32_t* tab = reinterpret_cast<uint32_t*>(tab_raw);
         for (int i = threadIdx.x; i < 256 * 32; i += kTThreads) {
@@ -330,7 +391,7 @@ tensor_gemm_kernel(const TensorArgs a, const __grid_constant__ CUtensorMap x_map
             TItem it;
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            for (int64_t id = blockIdx.x; ok && next_item(a, cur, id, &it); id += gridDim.x) {
+            for (int64_t id = blockIdx.x; ok && next_item(a, cur, id, &it, gtab); id += gridDim.x) {
                 for (int rb = 0; rb < a.r_blocks && ok; ++rb) {
                     ok = mbar_wait_bounded(empty + stage, phase ^ 1, abort_flag);
                     if (!ok) break;
@@ -350,7 +411,7 @@ tensor_gemm_kernel(const TensorArgs a, const __grid_constant__ CUtensorMap x_map
             uint32_t stage = 0, phase = 0, buf = 0, acc_phase = 0;
             bool ok = true;
             constexpr uint32_t idesc = umma_idesc(OP == GNF4B_OP_DGRAD ? 1 : 0);
-            for (int64_t id = blockIdx.x; ok && next_item(a, cur, id, &it); id += gridDim.x) {
+            for (int64_t id = blockIdx.x; ok && next_item(a, cur, id, &it, gtab); id += gridDim.x) {
                 ok = mbar_wait_bounded(acc_empty + buf, acc_phase ^ 1, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
@@ -399,7 +460,7 @@ tensor_gemm_kernel(const TensorArgs a, const __grid_constant__ CUtensorMap x_map
         bool ok = true;
         uint16_t* out = reinterpret_cast<uint16_t*>(a.g.out);
         const bool vec_ok = (a.C % 8) == 0;
-        for (int64_t id = blockIdx.x; ok && next_item(a, cur, id, &it); id += gridDim.x) {
+        for (int64_t id = blockIdx.x; ok && next_item(a, cur, id, &it, gtab); id += gridDim.x) {
             ok = mbar_wait_bounded(acc_full + buf, acc_phase, abort_flag);
             if (!ok) break;
             tc_fence_after();
@@ -456,7 +517,7 @@ tensor_gemm_kernel(const TensorArgs a, const __grid_constant__ CUtensorMap x_map
         TItem it;
         uint32_t stage = 0, phase = 0;
         bool ok = true;
-        for (int64_t id = blockIdx.x; ok && next_item(a, cur, id, &it); id += gridDim.x) {
+        for (int64_t id = blockIdx.x; ok && next_item(a, cur, id, &it, gtab); id += gridDim.x) {
             const uint8_t* w_e = a.g.W + (int64_t)it.eid * a.g.w_se;
             const int64_t s_e = (int64_t)it.eid * a.g.s_se;
             // Element coordinates of this thread's 16 elements in stage rb:
