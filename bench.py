@@ -47,6 +47,13 @@ BASELINE_US = {  # reference's published B200 numbers (fused Triton, gate_up + d
     ("qwen3_30b_a3b", 1): 185.0 + 100.0,       # decode_bs1
     ("qwen3_30b_a3b", 2048): 1428.0 + 794.0,   # prefill_s2048
 }
+# DRAM traffic of one gate_up launch (dram__bytes_read.sum + dram__bytes_write.sum, one ncu capture each; the
+# summaries and their commands are profiles/decode_gemv_kernel_qwen3_gate_up_m1.md and
+# profiles/tensor_fwd_kernel_qwen3_gate_up_m4096.md).  Other workloads: not captured, null.
+NCU_TRAFFIC_BYTES = {
+    ("qwen3_30b_a3b", 1): 14.22e6,                # = the algorithmic 14.21 MB: nothing re-read
+    ("qwen3_30b_a3b", 4096): 360.8e6 + 85.6e6,    # weights once + activations + scales read, output written
+}
 
 
 def measured_peaks():
@@ -344,7 +351,7 @@ def run_gpu(args, shape, rank, world):
     else:
         ach = statistics.mean(fl) / (us_gu * 1e-6) / 1e12
         roof = dict(bound="tensor", achieved=ach, peak=peaks["tflops"], unit="TFLOP/s", frac=ach / peaks["tflops"])
-    roof.update(traffic=None, kernel="gate_up grouped GEMM", us_per_launch=us_gu, peak_source=peaks["source"],
+    roof.update(traffic=NCU_TRAFFIC_BYTES.get((shape.name, args.tokens)), kernel="gate_up grouped GEMM", us_per_launch=us_gu, peak_source=peaks["source"],
                 algorithmic_bytes=statistics.mean(by), algorithmic_flops=statistics.mean(fl))
     us_layer = ms_layer * 1e3 / K
     us_e2e = ms_e2e * 1e3 / K
