@@ -85,3 +85,98 @@ __global__ void combine_rows_kernel(const uint16_t* __restrict__ rows, const int
 }
 
 }  // namespace gnf4b
+
+namespace gnf4b {
+
+// Routing plan of the fixed-capacity exchange for a small batch, ONE CTA: per-expert counts, the row of
+// every (token, choice) pair in the send buffer -- destination rank d = expert / experts_per_rank gets
+// rows [d * cap, d * cap + ...) ordered by local expert, pairs of one expert in pair order -- and the
+// copy of the pairs' hidden rows into those slots.  P = tokens * top_k <= 1024, n_experts <= 1024.
+// A pair whose expert id is out of range gets slot -1, is not sent and is flagged.
+constexpr int kEpPlanThreads = 256;
+constexpr int kEpPlanMax = 1024;
+
+__global__ void __launch_bounds__(kEpPlanThreads, 1)
+ep_plan_kernel(const int64_t* __restrict__ idx, int32_t P, int32_t k, int32_t n_experts, int32_t e_local, int32_t cap,
+               const uint16_t* __restrict__ hidden, int64_t H, int32_t* __restrict__ counts, int64_t* __restrict__ slot,
+               uint16_t* __restrict__ send, int32_t* status) {
+    __shared__ int32_t s_e[kEpPlanMax];        // expert of pair p (-1: invalid)
+    __shared__ int32_t s_hist[kEpPlanMax];     // pairs per expert
+    __shared__ int32_t s_base[kEpPlanMax];     // pairs of lower experts on the same destination rank
+    __shared__ int64_t s_slot[kEpPlanMax];
+    const int t = threadIdx.x;
+    for (int e = t; e < n_experts; e += kEpPlanThreads) s_hist[e] = 0;
+    __syncthreads();
+    for (int p = t; p < P; p += kEpPlanThreads) {
+        const int64_t e = idx[p];
+        const bool ok = e >= 0 && e < n_experts;
+        s_e[p] = ok ? (int32_t)e : -1;
+        if (ok) atomicAdd(&s_hist[e], 1);
+        else if (status) atomicOr(status, GNF4B_ST_BAD_EXPERT);
+    }
+    __syncthreads();
+    for (int e = t; e < n_experts; e += kEpPlanThreads) {
+        int32_t b = 0;
+        for (int q = (e / e_local) * e_local; q < e; ++q) b += s_hist[q];
+        s_base[e] = b;
+        counts[e] = s_hist[e];
+    }
+    __syncthreads();
+    for (int p = t; p < P; p += kEpPlanThreads) {
+        const int32_t e = s_e[p];
+        int64_t s = -1;
+        if (e >= 0) {
+            int32_t rank = 0;
+            for (int q = 0; q < p; ++q) rank += (s_e[q] == e);
+            s = (int64_t)(e / e_local) * cap + s_base[e] + rank;
+        }
+        s_slot[p] = s;
+        slot[p] = s;
+    }
+    __syncthreads();
+    // copy the rows: 16 bytes per thread and step when the rows allow it
+    const bool vec = (H % 8) == 0 && ((reinterpret_cast<uintptr_t>(hidden) | reinterpret_cast<uintptr_t>(send)) & 15) == 0;
+    if (vec) {
+        const int64_t per_row = H / 8;
+        for (int64_t i = t; i < (int64_t)P * per_row; i += kEpPlanThreads) {
+            const int p = (int)(i / per_row);
+            const int64_t c = (i - (int64_t)p * per_row) * 8;
+            if (s_slot[p] >= 0)
+                *reinterpret_cast<uint4*>(send + s_slot[p] * H + c) =
+                    __ldg(reinterpret_cast<const uint4*>(hidden + (int64_t)(p / k) * H + c));
+        }
+    } else {
+        for (int64_t i = t; i < (int64_t)P * H; i += kEpPlanThreads) {
+            const int p = (int)(i / H);
+            const int64_t c = i - (int64_t)p * H;
+            if (s_slot[p] >= 0) send[s_slot[p] * H + c] = hidden[(int64_t)(p / k) * H + c];
+        }
+    }
+}
+
+// Group offsets of a received fixed-capacity buffer: per source rank its e_local expert blocks
+// (recv_counts[s, e] rows) and then the unused capacity as one padding group.  offsets has
+// world * (e_local + 1) + 1 entries.  Counts that do not fit the capacity are clamped and flagged.
+__global__ void ep_offsets_kernel(const int32_t* __restrict__ recv_counts, int32_t world, int32_t e_local, int32_t cap,
+                                  int32_t* __restrict__ offsets, int32_t* status) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    int32_t off = 0, g = 0;
+    offsets[0] = 0;
+    for (int s = 0; s < world; ++s) {
+        int32_t used = 0;
+        for (int e = 0; e < e_local; ++e) {
+            int32_t n = recv_counts[s * e_local + e];
+            if (n < 0 || used + n > cap) {
+                if (status) atomicOr(status, GNF4B_ST_BAD_OFFSETS);
+                n = n < 0 ? 0 : cap - used;
+            }
+            used += n;
+            off += n;
+            offsets[++g] = off;
+        }
+        off += cap - used;
+        offsets[++g] = off;
+    }
+}
+
+}  // namespace gnf4b

@@ -538,6 +538,28 @@ int gnf4b_combine_rows(const void* rows, int64_t P, const int64_t* pos, const fl
     return e == cudaSuccess ? GNF4B_OK : cuda_fail(e, "combine_rows launch");
 }
 
+int gnf4b_ep_plan(const int64_t* idx, int32_t P, int32_t k, int32_t n_experts, int32_t e_local, int32_t cap,
+                  const void* hidden, int64_t H, int32_t* counts, int64_t* slot, void* send, int32_t* status_word,
+                  void* cuda_stream) {
+    if (P < 0 || k <= 0 || n_experts <= 0 || e_local <= 0 || n_experts % e_local || cap < 0 || H <= 0) return GNF4B_EINVAL;
+    if (P > kEpPlanMax || n_experts > kEpPlanMax) return GNF4B_ETOOBIG;
+    if (!counts || (P > 0 && (!idx || !hidden || !slot || !send))) return GNF4B_EINVAL;
+    ep_plan_kernel<<<1, kEpPlanThreads, 0, reinterpret_cast<cudaStream_t>(cuda_stream)>>>(
+        idx, P, k, n_experts, e_local, cap, static_cast<const uint16_t*>(hidden), H, counts, slot,
+        static_cast<uint16_t*>(send), status_word);
+    cudaError_t e = cudaPeekAtLastError();
+    return e == cudaSuccess ? GNF4B_OK : cuda_fail(e, "ep_plan launch");
+}
+
+int gnf4b_ep_offsets(const int32_t* recv_counts, int32_t world, int32_t e_local, int32_t cap, int32_t* offsets,
+                     int32_t* status_word, void* cuda_stream) {
+    if (world <= 0 || e_local <= 0 || cap < 0 || !recv_counts || !offsets) return GNF4B_EINVAL;
+    ep_offsets_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(cuda_stream)>>>(recv_counts, world, e_local, cap, offsets,
+                                                                              status_word);
+    cudaError_t e = cudaPeekAtLastError();
+    return e == cudaSuccess ? GNF4B_OK : cuda_fail(e, "ep_offsets launch");
+}
+
 int gnf4b_dequant(int fmt, const uint8_t* W, int64_t w_stride_e, int64_t w_stride_n, const void* S,
                   int s_dtype, int64_t s_stride_e, int64_t s_stride_n, int32_t E, int64_t N, int64_t K,
                   float* out_f32, void* cuda_stream) {

@@ -215,31 +215,60 @@ class EPGroupedMoE:
 
 
     def _forward_fixed(self, hidden, idx, weights, cap):
-        """The layer with fixed-capacity exchanges: no host read, a fixed sequence of launches."""
+        """The layer with fixed-capacity exchanges: no host read, a fixed sequence of launches.  On a GPU
+        the routing plan (counts, slots, row scatter) and the group offsets are one small kernel each
+        (gnf4b_ep_plan, gnf4b_ep_offsets); the tensor-operation form below them is the same computation
+        (it serves CPU ranks and batches beyond the kernels' 1024 pairs)."""
         W, El = self.world, self.e_local
         dev = hidden.device
         H = hidden.shape[1]
-        order, tok, counts = plan_dispatch(idx, self.n_experts, W)          # counts [W, El]
-        counts32 = counts.to(torch.int32).contiguous()
+        n_groups = W * (El + 1)
+        if self._fixed_eids is None or self._fixed_eids.device != dev:
+            self._fixed_eids = torch.tensor((list(range(El)) + [PAD_EXPERT]) * W, dtype=torch.int32, device=dev)
+        use_lib = (hidden.is_cuda and hidden.dtype == torch.bfloat16 and hidden.is_contiguous() and cap <= 1024
+                   and self.n_experts <= 1024)
+        if use_lib:
+            import _gnf4b
+            import nf4_grouped
+            lib = _gnf4b.load()
+            stream = torch.cuda.current_stream(dev).cuda_stream
+            status = nf4_grouped._status_word(dev).data_ptr()
+            idx64 = idx.to(torch.int64).contiguous()
+            counts32 = torch.empty(W, El, dtype=torch.int32, device=dev)
+            slot = torch.empty(cap, dtype=torch.int64, device=dev)
+            send = torch.empty(W * cap, H, dtype=hidden.dtype, device=dev)
+            with torch.cuda.device(dev):
+                _gnf4b.check(lib.gnf4b_ep_plan(idx64.data_ptr(), cap, idx.shape[1], self.n_experts, El, cap, hidden.data_ptr(), H,
+                                               counts32.data_ptr(), slot.data_ptr(), send.data_ptr(), status, stream),
+                             "gnf4b_ep_plan")
+        else:
+            order, tok, counts = plan_dispatch(idx, self.n_experts, W)          # counts [W, El]
+            counts32 = counts.to(torch.int32).contiguous()
+            # pair p (sorted order) goes to rank d(p) at row p - start[d] of that rank's buffer
+            per_dest = counts.sum(1)
+            start = torch.cumsum(per_dest, 0) - per_dest
+            dest = torch.repeat_interleave(torch.arange(W, device=dev), per_dest, output_size=order.numel())
+            slot_sorted = dest * cap + (torch.arange(order.numel(), device=dev) - start[dest])
+            send = torch.zeros(W * cap, H, dtype=hidden.dtype, device=dev)
+            send[slot_sorted] = hidden[tok]
+            slot = torch.empty_like(order)
+            slot[order] = slot_sorted                # pair (m, j) comes back at the row it was sent from
         recv_counts = torch.empty_like(counts32)
         self._a2a(recv_counts.reshape(-1), counts32.reshape(-1), None, None)
-        # pair p (sorted order) goes to rank d(p) at row p - start[d] of that rank's buffer
-        per_dest = counts.sum(1)
-        start = torch.cumsum(per_dest, 0) - per_dest
-        dest = torch.repeat_interleave(torch.arange(W, device=dev), per_dest, output_size=order.numel())
-        slot = dest * cap + (torch.arange(order.numel(), device=dev) - start[dest])
-        send = torch.zeros(W * cap, H, dtype=hidden.dtype, device=dev)
-        send[slot] = hidden[tok]
         recv = torch.empty_like(send)
         self._a2a(recv, send, None, None)
         self._mark("dispatch")
         # groups as the rows lie: per source its El expert blocks, then the unused capacity as padding
-        rc = recv_counts.to(torch.int64)
-        sizes = torch.cat((rc, (cap - rc.sum(1, keepdim=True))), 1).reshape(-1)         # [W * (El + 1)]
-        offsets = torch.zeros(sizes.numel() + 1, dtype=torch.int32, device=dev)
-        offsets[1:] = torch.cumsum(sizes, 0).to(torch.int32)
-        if self._fixed_eids is None or self._fixed_eids.device != dev:
-            self._fixed_eids = torch.tensor((list(range(El)) + [PAD_EXPERT]) * W, dtype=torch.int32, device=dev)
+        if use_lib:
+            offsets = torch.empty(n_groups + 1, dtype=torch.int32, device=dev)
+            with torch.cuda.device(dev):
+                _gnf4b.check(lib.gnf4b_ep_offsets(recv_counts.data_ptr(), W, El, cap, offsets.data_ptr(), status, stream),
+                             "gnf4b_ep_offsets")
+        else:
+            rc = recv_counts.to(torch.int64)
+            sizes = torch.cat((rc, (cap - rc.sum(1, keepdim=True))), 1).reshape(-1)         # [W * (El + 1)]
+            offsets = torch.zeros(n_groups + 1, dtype=torch.int32, device=dev)
+            offsets[1:] = torch.cumsum(sizes, 0).to(torch.int32)
         self.last_rows = W * cap
         gu = self.grouped_fn(recv, self.gate_up[0], self.gate_up[1], None, self._fixed_eids,
                              group_offsets=offsets, max_rows=cap)
@@ -251,9 +280,7 @@ class EPGroupedMoE:
         ret = torch.empty_like(y)
         self._a2a(ret, y, None, None)
         self._mark("combine")
-        pos = torch.empty_like(order)
-        pos[order] = slot                       # pair (m, j) comes back at the row it was sent from
-        out = combine_rows(ret, pos.reshape(idx.shape), weights)
+        out = combine_rows(ret, slot.reshape(idx.shape), weights)
         self._mark("sum")
         return out
 

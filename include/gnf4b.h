@@ -181,6 +181,24 @@ int gnf4b_silu_glu(const void* gate_up, int64_t rows, int64_t h, void* out, void
 int gnf4b_combine_rows(const void* rows, int64_t P, const int64_t* pos, const float* weights, int32_t k,
                        int64_t M, int64_t H, void* out, int32_t* status_word, void* cuda_stream);
 
+/* Fixed-capacity exchange of a small batch (P = tokens * top_k <= 1024 pairs, n_experts <= 1024), no host
+ * read anywhere (expert-parallel layer; no reference counterpart).
+ *
+ * gnf4b_ep_plan, one CTA: idx[P] (int64 global expert ids, pair p = token p / k) -> counts[n_experts]
+ * (int32 pairs per expert), slot[P] (int64 row of pair p in the send buffer: rank d = expert / e_local owns
+ * rows [d * cap, (d + 1) * cap), ordered by local expert, pairs of one expert in pair order; -1 and
+ * GNF4B_ST_BAD_EXPERT for an id outside [0, n_experts)), and the copy of the pairs' hidden rows (bf16
+ * [tokens, H]) into send (bf16 [world * cap, H]).
+ *
+ * gnf4b_ep_offsets: recv_counts[world, e_local] -> offsets[world * (e_local + 1) + 1] of the received buffer:
+ * per source rank its e_local expert blocks, then the unused capacity as one group (to be given
+ * GNF4B_PAD_EXPERT). */
+int gnf4b_ep_plan(const int64_t* idx, int32_t P, int32_t k, int32_t n_experts, int32_t e_local, int32_t cap,
+                  const void* hidden, int64_t H, int32_t* counts, int64_t* slot, void* send, int32_t* status_word,
+                  void* cuda_stream);
+int gnf4b_ep_offsets(const int32_t* recv_counts, int32_t world, int32_t e_local, int32_t cap, int32_t* offsets,
+                     int32_t* status_word, void* cuda_stream);
+
 /* Device properties this library plans with (SM count, opt-in shared memory). */
 int gnf4b_device_info(int32_t* sm_count, int32_t* smem_optin_bytes);
 

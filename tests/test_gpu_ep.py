@@ -112,3 +112,48 @@ def test_combine_rows_kernel_equals_the_ordered_loop():
     ep_moe.combine_rows(rows, pos, w)
     torch.cuda.synchronize()
     assert nf4_grouped.last_status("cuda") & 2
+
+
+def test_ep_plan_and_offsets_kernels_equal_the_tensor_form():
+    """gnf4b_ep_plan / gnf4b_ep_offsets against the sort-based plan of ep_moe (what CPU ranks run)."""
+    import _gnf4b
+    import ep_moe
+    import nf4_grouped
+    import synth
+    lib = _gnf4b.load()
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator().manual_seed(12)
+    E, W, k, M, H = 32, 4, 4, 9, 64
+    El, cap = E // W, M * k
+    idx, _ = synth.route_topk(torch.randn(M, E, generator=gen), k)
+    hidden = torch.randn(M, H, generator=gen).to(torch.bfloat16)
+    idx_d, hid_d = idx.to(dev), hidden.to(dev)
+    counts = torch.empty(W, El, dtype=torch.int32, device=dev)
+    slot = torch.empty(cap, dtype=torch.int64, device=dev)
+    send = torch.zeros(W * cap, H, dtype=torch.bfloat16, device=dev)
+    st = nf4_grouped._status_word(dev)
+    rc = lib.gnf4b_ep_plan(idx_d.to(torch.int64).contiguous().data_ptr(), cap, k, E, El, cap, hid_d.data_ptr(), H, counts.data_ptr(),
+                           slot.data_ptr(), send.data_ptr(), st.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    # the tensor form
+    order, tok, cnt = ep_moe.plan_dispatch(idx, E, W)
+    per_dest = cnt.sum(1)
+    start = torch.cumsum(per_dest, 0) - per_dest
+    dest = torch.repeat_interleave(torch.arange(W), per_dest)
+    slot_sorted = dest * cap + (torch.arange(order.numel()) - start[dest])
+    want_slot = torch.empty_like(order)
+    want_slot[order] = slot_sorted
+    want_send = torch.zeros(W * cap, H, dtype=torch.bfloat16)
+    want_send[slot_sorted] = hidden[tok]
+    torch.cuda.synchronize()
+    assert torch.equal(counts.cpu().to(torch.int64), cnt)
+    assert torch.equal(slot.cpu(), want_slot)
+    assert torch.equal(send.cpu(), want_send)
+    # offsets of a received buffer
+    rcnt = torch.randint(0, 3, (W, El), generator=gen).to(torch.int32)
+    off = torch.empty(W * (El + 1) + 1, dtype=torch.int32, device=dev)
+    assert lib.gnf4b_ep_offsets(rcnt.to(dev).data_ptr(), W, El, cap, off.data_ptr(), st.data_ptr(),
+                                torch.cuda.current_stream().cuda_stream) == 0
+    sizes = torch.cat((rcnt.to(torch.int64), cap - rcnt.sum(1, keepdim=True)), 1).reshape(-1)
+    assert off.cpu().tolist() == [0] + torch.cumsum(sizes, 0).tolist()
+    assert nf4_grouped.last_status(dev) == 0
