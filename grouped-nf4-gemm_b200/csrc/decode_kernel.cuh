@@ -46,6 +46,7 @@ struct DecodeArgs {
     int64_t total_items;        // G * row_chunks * tiles_per_group
     int32_t row_chunks;         // a group's rows are taken rows_per_pass at a time: ceil(max_rows / rows_per_pass)
     int32_t rows_per_pass;      // RM of the kernel instance
+    int32_t compact;            // work list holds only (group, chunk) pairs that exist (prefix sum in shared memory)
 };
 
 __host__ __device__ inline size_t decode_smem_bytes(int slot_bytes, int stages, int g_cache) {
@@ -132,15 +133,15 @@ __device__ __forceinline__ DGroup decode_group(const DecodeArgs& a, int g, int c
     return d;
 }
 
-// Position in the list of (group, row chunk) pairs.  Plain mode (row_chunks == 1): pair v is group v.
-// Chunked mode: vb[g] = number of pairs before group g (a prefix sum in shared memory, groups that are
+// Position in the list of (group, row chunk) pairs.  Plain mode: pair v is group v.
+// Compact mode (groups taken in row chunks, or a group list that is mostly empty or padding): vb[g] = number of pairs before group g (a prefix sum in shared memory, groups that are
 // empty or flagged have none), so the list holds only chunks that exist.
 struct GroupWalk {
     int v, g, c;
 };
 __device__ __forceinline__ void walk_to(const DecodeArgs& a, const int32_t* vb, GroupWalk& w, int v) {
     w.v = v;
-    if (a.row_chunks == 1) {
+    if (!a.compact) {
         w.g = v;
         w.c = 0;
         return;
@@ -179,8 +180,8 @@ __global__ void __launch_bounds__(decode_threads(RM), 1) decode_gemv_kernel(cons
     int64_t item_lo = (int64_t)bid * a.items_per_cta + min(bid, a.items_extra);
     int64_t item_hi = item_lo + a.items_per_cta + (bid < a.items_extra ? 1 : 0);
     const int32_t* vb = s_grp;
-    if (a.row_chunks > 1) {
-        // chunked mode: build the prefix sum of the groups' chunk counts (one warp, ordered scan),
+    if (a.compact) {
+        // compact mode (row chunks, or far more groups than rows): build the prefix sum of the groups' chunk counts (one warp, ordered scan),
         // then cut the list of existing items evenly over the CTAs
         pdl_wait();
         if (warp == 0) {

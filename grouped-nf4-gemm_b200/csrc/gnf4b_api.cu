@@ -412,6 +412,8 @@ int gnf4b_gemm_grouped(int fmt, int op, const void* x, int x_dtype, int64_t T, c
             da.g_cache = p.g_cache;
             da.rows_per_pass = rm;
             da.row_chunks = (max_rows + rm - 1) / rm;
+            // a list with more groups than rows is mostly empty (or padding) groups: walk only the ones that exist
+            da.compact = (da.row_chunks > 1 || ((int64_t)G > T && G <= p.g_cache)) ? 1 : 0;
             da.total_items = (int64_t)G * da.row_chunks * da.tiles_per_group;
             const int64_t room = (int64_t)di.smem_optin - (int64_t)decode_smem_bytes(0, 0, da.g_cache);
             da.stages = (int32_t)std::min<int64_t>(kDMaxStages, room / da.slot_bytes);

@@ -270,12 +270,16 @@ class EPGroupedMoE:
             offsets = torch.zeros(n_groups + 1, dtype=torch.int32, device=dev)
             offsets[1:] = torch.cumsum(sizes, 0).to(torch.int32)
         self.last_rows = W * cap
+        # a (source, expert) block has at most one row per token of the source: the row bound of the
+        # real groups is the token count, not the capacity (padding groups are skipped whatever their size)
+        max_rows = idx.shape[0]
         gu = self.grouped_fn(recv, self.gate_up[0], self.gate_up[1], None, self._fixed_eids,
-                             group_offsets=offsets, max_rows=cap)
+                             group_offsets=offsets, max_rows=max_rows)
         self._mark("gate_up")
         h = silu_glu(gu)
         self._mark("glu")
-        y = self.grouped_fn(h, self.down[0], self.down[1], None, self._fixed_eids, group_offsets=offsets, max_rows=cap)
+        y = self.grouped_fn(h, self.down[0], self.down[1], None, self._fixed_eids, group_offsets=offsets,
+                            max_rows=max_rows)
         self._mark("down")
         ret = torch.empty_like(y)
         self._a2a(ret, y, None, None)
