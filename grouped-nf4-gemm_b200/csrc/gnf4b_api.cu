@@ -403,7 +403,7 @@ int gnf4b_gemm_grouped(int fmt, int op, const void* x, int x_dtype, int64_t T, c
             DecodeArgs da;
             da.g = g;
             // rows per stage: one per consumer warp, more for short rows
-            const int m = (int)std::max<int64_t>(1, std::min<int64_t>(4, 16384 / (kDConsumerWarps * row_bytes)));
+            const int m = (int)std::max<int64_t>(1, std::min<int64_t>(4, 32768 / (kDConsumerWarps * row_bytes)));
             da.rows_per_stage = kDConsumerWarps * m;
             da.tiles_per_group = (int32_t)ceil_div(N, da.rows_per_stage);
             da.row_bytes = (int32_t)row_bytes;
