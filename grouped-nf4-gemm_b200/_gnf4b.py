@@ -96,6 +96,8 @@ def _declare(lib):
     lib.gnf4b_silu_glu.argtypes = [vp, i64, i64, vp, vp]
     lib.gnf4b_combine_rows.restype = C.c_int
     lib.gnf4b_combine_rows.argtypes = [vp, i64, vp, vp, i32, i64, i64, vp, vp, vp]
+    lib.gnf4b_route_topk.restype = C.c_int
+    lib.gnf4b_route_topk.argtypes = [vp, i64, i32, i32, i32, i32, vp, vp, vp]
     lib.gnf4b_ep_plan.restype = C.c_int
     lib.gnf4b_ep_plan.argtypes = [vp, i32, i32, i32, i32, i32, vp, i64, vp, vp, vp, vp, vp]
     lib.gnf4b_ep_offsets.restype = C.c_int
@@ -108,7 +110,7 @@ def _declare(lib):
 #: every symbol include/gnf4b.h declares
 EXPORTS = ("gnf4b_abi_version", "gnf4b_strerror", "gnf4b_last_cuda_error", "gnf4b_gemm_grouped",
            "gnf4b_gemm_grouped_noalloc",
-           "gnf4b_workspace_bytes", "gnf4b_plan_split_k", "gnf4b_build_offsets", "gnf4b_upload_i32", "gnf4b_dequant", "gnf4b_silu_glu", "gnf4b_combine_rows", "gnf4b_ep_plan", "gnf4b_ep_offsets",
+           "gnf4b_workspace_bytes", "gnf4b_plan_split_k", "gnf4b_build_offsets", "gnf4b_upload_i32", "gnf4b_dequant", "gnf4b_silu_glu", "gnf4b_combine_rows", "gnf4b_ep_plan", "gnf4b_ep_offsets", "gnf4b_route_topk",
            "gnf4b_device_info")
 
 

@@ -180,3 +180,72 @@ __global__ void ep_offsets_kernel(const int32_t* __restrict__ recv_counts, int32
 }
 
 }  // namespace gnf4b
+
+namespace gnf4b {
+
+// Router selection, one warp per token: the k largest logits in descending order, ties to the lower
+// expert index, and their weights -- mode 0: softmax over all E experts (norm: renormalised over the k),
+// mode 1: softmax over the k selected.  Same rule as the reference's CPU router
+// (gnf4_native/cpu_kernels.c:1408-1471).  k <= 32.
+__global__ void route_topk_kernel(const float* __restrict__ logits, int64_t T, int32_t E, int32_t k, int32_t mode,
+                                  int32_t norm, int64_t* __restrict__ idx, float* __restrict__ w) {
+    const int lane = threadIdx.x & 31;
+    const int64_t t = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= T) return;
+    const float* lg = logits + t * E;
+    // each lane keeps the position of its own last pick so it never offers an element twice
+    float sel_v = 0.f;            // value of the pick with rank == lane
+    int32_t sel_i = 0;
+    float prev_v = INFINITY;
+    int32_t prev_i = -1;
+    for (int j = 0; j < k; ++j) {
+        // best remaining element: smaller than the previous pick, or equal with a larger index
+        float bv = -INFINITY;
+        int32_t bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float v = __ldg(lg + e);
+            const bool after_prev = v < prev_v || (v == prev_v && e > prev_i);
+            if (after_prev && (v > bv || (v == bv && e < bi))) { bv = v; bi = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == j) { sel_v = bv; sel_i = bi; }
+        prev_v = bv;
+        prev_i = bi;
+    }
+    const float top = __shfl_sync(0xffffffffu, sel_v, 0);
+    float wj;
+    if (mode == 0) {
+        float m = -INFINITY;
+        for (int e = lane; e < E; e += 32) m = fmaxf(m, __ldg(lg + e));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        float z = 0.f;
+        for (int e = lane; e < E; e += 32) z += expf(__ldg(lg + e) - m);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) z += __shfl_xor_sync(0xffffffffu, z, o);
+        wj = (lane < k) ? expf(sel_v - m) / z : 0.f;
+        if (norm) {
+            float s = wj;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            wj /= s;
+        }
+    } else {
+        const float ej = (lane < k) ? expf(sel_v - top) : 0.f;
+        float z = ej;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) z += __shfl_xor_sync(0xffffffffu, z, o);
+        wj = ej / z;
+    }
+    if (lane < k) {
+        idx[t * k + lane] = sel_i;
+        w[t * k + lane] = wj;
+    }
+}
+
+}  // namespace gnf4b

@@ -540,6 +540,18 @@ int gnf4b_combine_rows(const void* rows, int64_t P, const int64_t* pos, const fl
     return e == cudaSuccess ? GNF4B_OK : cuda_fail(e, "combine_rows launch");
 }
 
+int gnf4b_route_topk(const float* logits, int64_t T, int32_t E, int32_t k, int32_t mode, int32_t norm, int64_t* idx,
+                     float* weights, void* cuda_stream) {
+    if (T < 0 || E <= 0 || k < 1 || k > E || k > 32 || (mode != 0 && mode != 1)) return GNF4B_EINVAL;
+    if (T > 0 && (!logits || !idx || !weights)) return GNF4B_EINVAL;
+    if (T == 0) return GNF4B_OK;
+    const int warps = 4;
+    route_topk_kernel<<<(unsigned)ceil_div(T, warps), warps * 32, 0, reinterpret_cast<cudaStream_t>(cuda_stream)>>>(
+        logits, T, E, k, mode, norm, idx, weights);
+    cudaError_t e = cudaPeekAtLastError();
+    return e == cudaSuccess ? GNF4B_OK : cuda_fail(e, "route_topk launch");
+}
+
 int gnf4b_ep_plan(const int64_t* idx, int32_t P, int32_t k, int32_t n_experts, int32_t e_local, int32_t cap,
                   const void* hidden, int64_t H, int32_t* counts, int64_t* slot, void* send, int32_t* status_word,
                   void* cuda_stream) {

@@ -76,6 +76,33 @@ def combine_rows(rows: torch.Tensor, pos: torch.Tensor, weights: torch.Tensor) -
     return acc.to(rows.dtype)
 
 
+def route_topk(logits: torch.Tensor, k: int, mode: int = 0, norm: bool = False):
+    """Router selection: logits [M, E] -> (idx [M, k] int64, weights [M, k] fp32): the k largest logits in
+    descending order, ties to the lower expert index; weights = softmax over all experts (``mode`` 0,
+    ``norm`` renormalises over the k) or over the k selected (``mode`` 1) -- the rule of the reference's CPU
+    router (gnf4_native/cpu_kernels.c:1408-1471).  On a GPU one kernel (gnf4b_route_topk), no host read."""
+    lg = logits.float().contiguous()
+    M, E = lg.shape
+    if lg.is_cuda and k <= 32:
+        import _gnf4b
+        idx = torch.empty(M, k, dtype=torch.int64, device=lg.device)
+        w = torch.empty(M, k, dtype=torch.float32, device=lg.device)
+        with torch.cuda.device(lg.device):
+            rc = _gnf4b.load().gnf4b_route_topk(lg.data_ptr(), M, E, k, mode, int(norm), idx.data_ptr(), w.data_ptr(),
+                                                torch.cuda.current_stream(lg.device).cuda_stream)
+        _gnf4b.check(rc, "gnf4b_route_topk")
+        return idx, w
+    idx = torch.argsort(-lg, dim=-1, stable=True)[:, :k]
+    top = torch.gather(lg, 1, idx)
+    if mode == 0:
+        w = torch.gather(torch.softmax(lg, dim=-1), 1, idx)
+        if norm:
+            w = w / w.sum(1, keepdim=True)
+    else:
+        w = torch.softmax(top, dim=-1)
+    return idx, w
+
+
 def plan_dispatch(idx: torch.Tensor, n_experts: int, world: int):
     """Routing ids [M, k] (global expert ids) -> (order [P], tok_of_pair [P], counts [W, E/W]).
     ``order`` is the stable argsort of the flattened ids, so pairs are grouped by destination
@@ -166,7 +193,8 @@ class EPGroupedMoE:
         dev = hidden.device
         self._mark("start")
         cap = idx.numel()                    # rows one destination can get from this rank at most
-        if W > 1 and W * cap * hidden.shape[1] * hidden.element_size() <= FIXED_CAPACITY_MAX_BYTES:
+        # (a single rank takes it too: routing plan, groups and combine without a host read)
+        if W * cap * hidden.shape[1] * hidden.element_size() <= FIXED_CAPACITY_MAX_BYTES:
             return self._forward_fixed(hidden, idx, weights, cap)
         order, tok, counts = plan_dispatch(idx, self.n_experts, W)
         counts32 = counts.to(torch.int32).contiguous()
@@ -213,6 +241,11 @@ class EPGroupedMoE:
         self._mark("sum")
         return out
 
+
+    def forward_logits(self, hidden: torch.Tensor, logits: torch.Tensor, k: int, mode: int = 0, norm: bool = False):
+        """Router included: ``logits [M, E]`` -> top-k ids and weights on the device, then ``forward``."""
+        idx, w = route_topk(logits, k, mode, norm)
+        return self.forward(hidden, idx, w)
 
     def _forward_fixed(self, hidden, idx, weights, cap):
         """The layer with fixed-capacity exchanges: no host read, a fixed sequence of launches.  On a GPU

@@ -181,6 +181,13 @@ int gnf4b_silu_glu(const void* gate_up, int64_t rows, int64_t h, void* out, void
 int gnf4b_combine_rows(const void* rows, int64_t P, const int64_t* pos, const float* weights, int32_t k,
                        int64_t M, int64_t H, void* out, int32_t* status_word, void* cuda_stream);
 
+/* Router selection on the device: logits fp32 [T, E] -> idx int64 [T, k] (the k largest, descending, ties to
+ * the lower expert index) and weights fp32 [T, k] (mode 0: softmax over all E, norm != 0 renormalises over the
+ * k; mode 1: softmax over the k selected).  The rule of the reference's CPU router
+ * (gnf4_native/cpu_kernels.c:1408-1471); k <= 32. */
+int gnf4b_route_topk(const float* logits, int64_t T, int32_t E, int32_t k, int32_t mode, int32_t norm, int64_t* idx,
+                     float* weights, void* cuda_stream);
+
 /* Fixed-capacity exchange of a small batch (P = tokens * top_k <= 1024 pairs, n_experts <= 1024), no host
  * read anywhere (expert-parallel layer; no reference counterpart).
  *

@@ -157,3 +157,56 @@ def test_ep_plan_and_offsets_kernels_equal_the_tensor_form():
     sizes = torch.cat((rcnt.to(torch.int64), cap - rcnt.sum(1, keepdim=True)), 1).reshape(-1)
     assert off.cpu().tolist() == [0] + torch.cumsum(sizes, 0).tolist()
     assert nf4_grouped.last_status(dev) == 0
+
+
+def test_router_kernel_matches_the_reference_rule(golden_dir):
+    """gnf4b_route_topk against the golden routing of the reference (indices exact, weights to fp32
+    rounding of the exponentials) and against the oracle on random logits with ties."""
+    import ep_moe
+    from oracle import oracle as O
+    g = np.load(golden_dir / "routing.npz")
+    lg = torch.from_numpy(g["logits"]).cuda()
+    for mode, norm, tag in ((0, False, "m0n0"), (0, True, "m0n1"), (1, False, "m1n0")):
+        idx, w = ep_moe.route_topk(lg, 8, mode, norm)
+        assert np.array_equal(idx.cpu().numpy(), g["idx_" + tag].astype(np.int64))
+        want_bits = g["wts_" + tag + "_bf16bits"]
+        got_bits = w.to(torch.bfloat16).view(torch.int16).cpu().numpy().view(np.uint16)
+        assert np.abs(got_bits.astype(np.int32) - want_bits.astype(np.int32)).max() <= 1       # one bf16 ulp
+    gen = torch.Generator().manual_seed(4)
+    logits = torch.randn(37, 130, generator=gen)
+    logits[3] = 0.0                       # all tied: experts 0..k-1
+    logits[5, 7] = logits[5, 99]          # a tie inside the top
+    for k, mode, norm in ((1, 0, False), (4, 0, True), (8, 1, False), (32, 0, False)):
+        idx, w = ep_moe.route_topk(logits.cuda(), k, mode, norm)
+        oi, ow = O.route_topk(logits.numpy(), k, mode, norm)
+        assert np.array_equal(idx.cpu().numpy(), oi.astype(np.int64))
+        assert np.allclose(w.cpu().numpy(), ow, rtol=2e-6, atol=1e-9)
+
+
+def test_single_gpu_layer_from_logits_without_host_reads():
+    """One rank: router kernel -> plan kernel -> grouped GEMMs over device offsets -> GLU -> combine.
+    Equal to the layer built from host-side routing and per-expert dense math at bf16 resolution."""
+    import ep_moe
+    import nf4_grouped
+    import synth
+    from nf4_grouped import dequant_ref
+    E, H, I, k, M = 16, 256, 128, 4, 12
+    gen = torch.Generator().manual_seed(31)
+    gu = synth.nf4_stack(E, 2 * I, H, gen, device="cuda", scale=0.05)
+    dn = synth.nf4_stack(E, H, I, gen, device="cuda", scale=0.05)
+    x = torch.randn(M, H, generator=gen).to(torch.bfloat16).cuda()
+    logits = torch.randn(M, E, generator=gen).cuda()
+    layer = ep_moe.EPGroupedMoE(E, gu, dn, fmt="nf4")
+    y = layer.forward_logits(x, logits, k)
+    idx, w = ep_moe.route_topk(logits, k)
+    want = torch.zeros(M, H, device="cuda")
+    for m in range(M):
+        for j in range(k):
+            e = int(idx[m, j])
+            w1 = dequant_ref(gu[0][e], gu[1][e], 2 * I, H).float()
+            w2 = dequant_ref(dn[0][e], dn[1][e], H, I).float()
+            g_ = (x[m].float() @ w1.t()).to(torch.bfloat16)
+            h = ep_moe.silu_glu(g_[None])[0]
+            want[m] += w[m, j] * (h.float() @ w2.t()).to(torch.bfloat16).float()
+    assert ((y.float() - want).norm() / want.norm()).item() < 1e-2
+    assert nf4_grouped.last_status("cuda") == 0
