@@ -262,13 +262,20 @@ def run_gpu(args, shape, rank, world):
             o = fn(d["h"], dn[0], dn[1], None, d["eids"], group_offsets=d["off"], max_rows=d["max_rows"])
         return o
 
+    host_out = {}          # pinned landing buffers for the result, by shape (a fresh pageable one per step
+                           # would put its page faults inside the timed region)
+
     def layer_e2e(i):
         (gu, dn), s = layers[i % args.layers], steps[i]
         a = s["a"].to(dev, non_blocking=True)
         fn(a, gu[0], gu[1], s["sizes"], s["eids"])
         h = s["h"].to(dev, non_blocking=True)
         o = fn(h, dn[0], dn[1], s["sizes"], s["eids"])
-        return o.to("cpu", non_blocking=False)
+        buf = host_out.get(tuple(o.shape))
+        if buf is None:
+            buf = host_out[tuple(o.shape)] = torch.empty(o.shape, dtype=o.dtype, pin_memory=True)
+        buf.copy_(o, non_blocking=False)      # device -> host read of the step's result, synchronous
+        return buf
 
     def barrier():
         if world > 1:
