@@ -4,7 +4,7 @@
 // The tight special case of the streaming path, taken when the host knows that no group has
 // more than 16 rows, K <= 3072, N % 8 == 0 and the stack is laid out so that consecutive
 // weight rows (and their scale rows) are contiguous and 16-byte aligned.  Then a work item
-// (group, tile of R = 8m weight rows) is ONE contiguous span of packed bytes and ONE
+// (group, tile of R weight rows) is ONE contiguous span of packed bytes and ONE
 // contiguous span of scale bytes, so a stage of the ring is filled by two bulk copies
 // (TMA engine) issued by a single producer lane -- no per-row copies, no register-staged
 // scale loads -- and the stage index is a closed-form function of the item index.
@@ -34,7 +34,7 @@ constexpr int kDMaxStages = 8;
 
 struct DecodeArgs {
     GemmArgs g;
-    int32_t rows_per_stage;     // R, a multiple of 8
+    int32_t rows_per_stage;     // R, a multiple of 4 or 8 (so that every scale span stays 16-byte aligned)
     int32_t tiles_per_group;    // ceil(N / R)
     int32_t row_bytes;          // K / 2
     int32_t scale_row_bytes;    // (K / block) * sizeof(scale)

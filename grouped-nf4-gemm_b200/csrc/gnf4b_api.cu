@@ -402,9 +402,22 @@ int gnf4b_gemm_grouped(int fmt, int op, const void* x, int x_dtype, int64_t T, c
             const int kDConsumerWarps = decode_consumer_warps(rm);
             DecodeArgs da;
             da.g = g;
-            // rows per stage: one per consumer warp, more for short rows
+            // rows per stage: up to 32 KiB of weight rows, chosen so that the CTA with the most items gets as
+            // few rows as possible (items are dealt out whole: with 768 items on 148 CTAs some CTAs would
+            // stream 6 tiles and others 5); a small per-item charge keeps the stages from getting tiny
             const int m = (int)std::max<int64_t>(1, std::min<int64_t>(4, 32768 / (kDConsumerWarps * row_bytes)));
-            da.rows_per_stage = kDConsumerWarps * m;
+            const int r_hi = kDConsumerWarps * m;
+            const int r_step = ((4 * srow) % 16 == 0) ? 4 : 8;
+            const int64_t groups_eff = std::max<int64_t>(1, std::min<int64_t>((int64_t)G * ((max_rows + rm - 1) / rm), T));
+            int best_r = r_hi;
+            int64_t best_cost = INT64_MAX;
+            for (int r = r_hi; r >= std::max(8, r_hi / 2); r -= r_step) {
+                const int64_t items = groups_eff * ceil_div(N, r);
+                const int64_t per_cta = ceil_div(items, std::min<int64_t>(di.sm_count, items));
+                const int64_t cost = per_cta * (r + 2);
+                if (cost < best_cost) { best_cost = cost; best_r = r; }
+            }
+            da.rows_per_stage = best_r;
             da.tiles_per_group = (int32_t)ceil_div(N, da.rows_per_stage);
             da.row_bytes = (int32_t)row_bytes;
             da.scale_row_bytes = (int32_t)srow;
