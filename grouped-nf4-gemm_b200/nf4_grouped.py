@@ -352,6 +352,27 @@ def dequant_ref(packed_row_major: torch.Tensor, absmax: torch.Tensor, N: int, K:
 # --------------------------------------------------------------------------- #
 # launch plumbing shared with mxfp4_grouped
 # --------------------------------------------------------------------------- #
+_WS_BYTES = {}       # (device, fmt, op, T, G, N, K, max_rows, flags) -> scratch bytes the planner asks for
+_STATUS_PTR = {}     # device index -> address of the status word
+
+
+def _raw_stream(dev) -> int:
+    """Address of torch's current stream on ``dev`` (the cheap accessor when this torch has it)."""
+    get = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+    if get is not None and dev.index is not None:
+        return get(dev.index)
+    return torch.cuda.current_stream(dev).cuda_stream
+
+
+def _status_ptr(dev) -> int:
+    ptr = _STATUS_PTR.get(dev.index)
+    if ptr is None:
+        ptr = _status_word(dev).data_ptr()
+        if dev.index is not None:
+            _STATUS_PTR[dev.index] = ptr
+    return ptr
+
+
 def _status_word(dev):
     dev = torch.device(dev)
     if dev.type == "cuda" and dev.index is None:
@@ -477,7 +498,7 @@ def _launch(fmt, op, x, W, S, sizes, expert_ids, n_out, *, split_k=None, path=_g
         prev = torch.cuda.current_device()          # the C library launches on the current device
         torch.cuda.set_device(dev)
     try:
-        stream_ptr = torch.cuda.current_stream(dev).cuda_stream
+        stream_ptr = _raw_stream(dev)
         off_t, ids_t, G, max_rows = _group_tables(sizes, expert_ids, T, E, dev, group_offsets, max_rows, stream_ptr)
         if G == 0:
             return out
@@ -486,13 +507,18 @@ def _launch(fmt, op, x, W, S, sizes, expert_ids, n_out, *, split_k=None, path=_g
         flags = path
         if split_k is not None:
             flags |= max(1, int(split_k)) << _gnf4b.SPLITK_SHIFT
-        need = lib.gnf4b_workspace_bytes(fmt, op, T, G, N, K, max_rows, flags)
+        key = (dev.index, fmt, op, T, G, N, K, max_rows, flags)        # the plan depends on the device's SM count
+        need = _WS_BYTES.get(key)
+        if need is None:
+            need = lib.gnf4b_workspace_bytes(*key[1:])
+            if len(_WS_BYTES) < 4096:
+                _WS_BYTES[key] = need
         ws = torch.zeros(need, dtype=torch.uint8, device=dev) if need else None
         rc = lib.gnf4b_gemm_grouped(
             fmt, op, x.data_ptr(), xdt, T, W.data_ptr(), W.stride(0), W.stride(1),
             S.data_ptr(), sdt, S.stride(0), S.stride(1), off_p, ids_p,
             G, E, N, K, max_rows, out.data_ptr(), ws.data_ptr() if ws is not None else None,
-            need, _status_word(dev).data_ptr(), flags, stream_ptr)
+            need, _status_ptr(dev), flags, stream_ptr)
     finally:
         if prev >= 0:
             torch.cuda.set_device(prev)
