@@ -395,7 +395,21 @@ def bench_ep(args, shape, rank, world, B):
             torch.cuda.synchronize()
     with B.ClockSampler(dev.index) as clk:
         t_res = []
-        for _ in range(max(1, args.repeats // 2)):
+        # at least repeats // 2 timed passes, and more of them until 0.5 s of this load have passed, so
+        # that the 100 ms clock sampler sees the GPU under it (the same count on every rank)
+        n_pass, extended = max(1, args.repeats // 2), False
+        t_begin = time.perf_counter()
+        while True:
+            if len(t_res) >= n_pass:
+                if extended:
+                    break
+                extended = True
+                per = (time.perf_counter() - t_begin) / len(t_res)
+                want = torch.tensor([min(500.0, max(float(n_pass), 0.5 / max(per, 1e-6)))], device=dev)
+                dist.all_reduce(want, op=dist.ReduceOp.MAX)
+                n_pass = int(want.item())
+                if len(t_res) >= n_pass:
+                    break
             barrier()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
