@@ -383,6 +383,16 @@ def run_gpu(args, shape, rank, world):
                   "rows_per_active_expert": rows_per_group, "active_experts": statistics.mean(act)},
         "clocks": clk.summary(), "device_status": status, "repeats_ms": t_layer[:16],
     }
+    if world == 1:
+        try:
+            ep_us = time_ep_layer_single_gpu(args, shape, layers, dev)
+        except Exception as exc:      # an extra, never at the cost of the main number
+            ep_us = None
+            line["ep_layer_note"] = f"not timed: {type(exc).__name__}: {str(exc)[:120]}"
+        if ep_us is not None:
+            # the whole MoE layer (routing plan, GEMMs over device offsets, GLU, combine) on one GPU: what the
+            # `--gpus N > 1` values (which add the exchanges) compare with
+            line["ep_layer_single_gpu_us"] = ep_us
     return line
 
 
@@ -448,6 +458,43 @@ def main():
     if world > 1:
         torch.distributed.destroy_process_group()
     return 0
+
+
+def time_ep_layer_single_gpu(args, shape, layers, dev):
+    """The expert-parallel layer's code on ONE rank (routing plan, grouped GEMMs over device offsets, GLU,
+    combine; no exchange), K steps in one CUDA graph: the N = 1 point that is comparable with the
+    `--gpus N > 1` values.  None when the batch is beyond the host-sync-free path."""
+    import ep_moe
+    if args.tokens * shape.top_k * shape.hidden * 2 > ep_moe.FIXED_CAPACITY_MAX_BYTES:
+        return None
+    K = min(args.steps, 32)
+    gen = torch.Generator().manual_seed(4242)
+    mods = [ep_moe.EPGroupedMoE(shape.experts, gu, dn, fmt=shape.fmt) for gu, dn in layers]
+    batch = [tuple(t.to(dev) for t in synth.routed_batch(shape, args.tokens, gen)) for _ in range(K)]
+    for i in range(min(K, len(mods) + 2)):
+        mods[i % len(mods)].forward(*batch[i])
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for i in range(K):
+            mods[i % len(mods)].forward(*batch[i])
+    torch.cuda.current_stream().wait_stream(side)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(K):
+            mods[i % len(mods)].forward(*batch[i])
+    g.replay()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(5):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) * 1e3 / K)
+    return statistics.median(ts)
 
 
 def run_gpu_ep(args, shape, rank, world):

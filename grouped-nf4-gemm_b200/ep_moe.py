@@ -286,10 +286,13 @@ class EPGroupedMoE:
             send[slot_sorted] = hidden[tok]
             slot = torch.empty_like(order)
             slot[order] = slot_sorted                # pair (m, j) comes back at the row it was sent from
-        recv_counts = torch.empty_like(counts32)
-        self._a2a(recv_counts.reshape(-1), counts32.reshape(-1), None, None)
-        recv = torch.empty_like(send)
-        self._a2a(recv, send, None, None)
+        if W == 1:                      # one rank: what it would send is what it receives
+            recv_counts, recv = counts32, send
+        else:
+            recv_counts = torch.empty_like(counts32)
+            self._a2a(recv_counts.reshape(-1), counts32.reshape(-1), None, None)
+            recv = torch.empty_like(send)
+            self._a2a(recv, send, None, None)
         self._mark("dispatch")
         # groups as the rows lie: per source its El expert blocks, then the unused capacity as padding
         if use_lib:
@@ -314,8 +317,11 @@ class EPGroupedMoE:
         y = self.grouped_fn(h, self.down[0], self.down[1], None, self._fixed_eids, group_offsets=offsets,
                             max_rows=max_rows)
         self._mark("down")
-        ret = torch.empty_like(y)
-        self._a2a(ret, y, None, None)
+        if W == 1:
+            ret = y
+        else:
+            ret = torch.empty_like(y)
+            self._a2a(ret, y, None, None)
         self._mark("combine")
         out = combine_rows(ret, slot.reshape(idx.shape), weights)
         self._mark("sum")
