@@ -28,6 +28,17 @@
 //
 // TMEM budget (512 columns): 256 accumulator columns + 4 stages x 64 columns of A (hi 32 + lo 32).
 // Work item = (group, balanced chunk of <= 256 rows, 128-column tile of N), column tile fastest.
+// Barriers: one ring of 8 slots, full[s] (TMA bytes + one arrival per decode warp of the stage's group)
+// and done[s] (tcgen05.commit: the stage's MMAs have completed, its two slots may be refilled); the
+// accumulator is handed over with acc_full / acc_empty once per item.
+//
+// CG = 2 (optional): a cluster of two CTAs shares every item -- same row chunk, neighbouring column
+// tiles; the leader issues tcgen05.mma.cta_group::2 for both, each CTA loads half of the activation
+// tile and decodes its own weight tile, the peer's warps arrive on the leader's barriers remotely.
+//
+// What bounds it: issuing one tcgen05.mma occupies the issuing thread for 100-125 cycles whatever the
+// shape, and NF4 needs two per k-step; a 64-k stage of 8 MMAs (1024 pipe cycles at N = 256) takes about
+// 1450 cycles including that thread's barrier wait, fence and loop and the accumulator hand-over.
 #pragma once
 
 #include "tensor_kernel.cuh"
