@@ -28,8 +28,10 @@
 
 namespace gnf4b {
 
-__host__ __device__ constexpr int decode_consumer_warps(int rm) { return rm == 1 ? 16 : 8; }
-__host__ __device__ constexpr int decode_threads(int rm) { return (decode_consumer_warps(rm) + 1) * 32; }
+// consumer warps: sixteen while a lane's share of the activation rows is small (one row, K <= 3072), fewer
+// when it needs the registers (two rows: 8 warps; one row of up to 7168 columns: 6 warps)
+__host__ __device__ constexpr int decode_consumer_warps(int rm, int au) { return au > 3 ? 6 : (rm == 1 ? 16 : 8); }
+__host__ __device__ constexpr int decode_threads(int rm, int au) { return (decode_consumer_warps(rm, au) + 1) * 32; }
 constexpr int kDMaxStages = 8;
 
 struct DecodeArgs {
@@ -151,8 +153,8 @@ __device__ __forceinline__ void walk_to(const DecodeArgs& a, const int32_t* vb, 
 }
 
 template <int FMT, int SDT, int AU, int RM>
-__global__ void __launch_bounds__(decode_threads(RM), 1) decode_gemv_kernel(const DecodeArgs a) {
-    constexpr int kDConsumerWarps = decode_consumer_warps(RM);
+__global__ void __launch_bounds__(decode_threads(RM, AU), 1) decode_gemv_kernel(const DecodeArgs a) {
+    constexpr int kDConsumerWarps = decode_consumer_warps(RM, AU);
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* tab_raw = smem;
     uint8_t* ring = smem + kSTableBytes;
@@ -294,8 +296,7 @@ __global__ void __launch_bounds__(decode_threads(RM), 1) decode_gemv_kernel(cons
         // pdl_wait(): it overlaps the tail of the previous kernel.
         const int half = lane >> 4, hl = lane & 15;
 #pragma unroll 4
-        for (int j = 0; j < 256 / kDConsumerWarps; j += 2) {
-            const int b = warp * (256 / kDConsumerWarps) + j + half;
+        for (int b = warp * 2 + half; b < 256; b += kDConsumerWarps * 2) {
             const float2 p = byte_pair<FMT>(b);
             asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(smem_u32(tab_raw) + b * 256 + hl * 16),
                          "f"(p.x), "f"(p.y), "f"(p.x), "f"(p.y)

@@ -114,7 +114,8 @@ static int make_plan(int fmt, int op, int64_t T, int32_t G, int64_t N, int64_t K
         // grows with the rows of a group); tensor cores beyond that.  Without a host-known
         // maximum the mean T/G decides.
         const double mean_rows = G > 0 ? (double)T / G : 0.0;
-        const bool small = (max_rows > 0) ? (max_rows <= 8 && mean_rows <= 2.0) : (mean_rows <= 1.5);
+        // (rows longer than 3072 columns are streamed once per row of a group, not per pair: lower crossover)
+        const bool small = (max_rows > 0) ? (max_rows <= 8 && mean_rows <= (K > 3072 ? 1.5 : 2.0)) : (mean_rows <= 1.5);
         path = (op == GNF4B_OP_DGRAD) ? GNF4B_PATH_TENSOR : (small ? GNF4B_PATH_STREAM : GNF4B_PATH_TENSOR);
         if (forced_split > 1 && op == GNF4B_OP_FWD) path = GNF4B_PATH_STREAM;
     }
@@ -208,7 +209,7 @@ static cudaError_t launch_decode_au(const DecodeArgs& da, int au, int rm, int gr
         if (e != cudaSuccess) return e;                                                               \
         cudaLaunchConfig_t cfg = {};                                                                  \
         cfg.gridDim = dim3((unsigned)grid);                                                           \
-        cfg.blockDim = dim3(decode_threads(RMV));                                                     \
+        cfg.blockDim = dim3(decode_threads(RMV, AUV));                                                     \
         cfg.dynamicSmemBytes = smem;                                                                  \
         cfg.stream = st;                                                                              \
         cudaLaunchAttribute attr[1];                                                                  \
@@ -221,7 +222,9 @@ static cudaError_t launch_decode_au(const DecodeArgs& da, int au, int rm, int gr
     if (rm == 1) {
         if (au <= 1) GNF4B_LAUNCH_D(1, 1);
         if (au == 2) GNF4B_LAUNCH_D(2, 1);
-        GNF4B_LAUNCH_D(3, 1);
+        if (au == 3) GNF4B_LAUNCH_D(3, 1);
+        if (au <= 5) GNF4B_LAUNCH_D(5, 1);
+        if (au <= 7) GNF4B_LAUNCH_D(7, 1);
     }
     if (rm == 2) {
         if (au <= 1) GNF4B_LAUNCH_D(1, 2);
@@ -396,10 +399,16 @@ int gnf4b_gemm_grouped(int fmt, int op, const void* x, int x_dtype, int64_t T, c
                                 (((uintptr_t)S | (uint64_t)(s_stride_e * elt)) & 15) == 0 && ((8 * srow) & 15) == 0;
         // rows of a group held in registers per pass: 1, or 2 with larger groups taken two rows at a
         // time (their weights are streamed once per pass; up to 8 passes)
-        const int rm = max_rows == 1 ? 1 : (max_rows == 2 || (max_rows >= 3 && max_rows <= 16 && G <= p.g_cache)) ? 2 : 0;
-        if (rm && p.split_k == 1 && K <= 3072 && (N % 8) == 0 && contiguous &&
+        // (beyond K = 3072 one row at a time: two rows of 7168 columns do not fit a lane's registers)
+        const int au_k = (int)ceil_div(K, 1024);
+        const bool chunk_ok = max_rows >= 2 && max_rows <= 16 && G <= p.g_cache;
+        const int rm = max_rows == 1 ? 1 : au_k > 3 ? (chunk_ok ? 1 : 0) : (max_rows == 2 || chunk_ok) ? 2 : 0;
+        // long rows: one row per consumer warp and stage (6 rows), so the scale span of a stage must stay
+        // 16-byte aligned at that granularity
+        const bool long_ok = au_k <= 3 || ((6 * srow) % 16 == 0 && (N % 6 == 0 || (((N % 6) * srow) % 16 == 0)));
+        if (rm && long_ok && p.split_k == 1 && K <= 7168 && (N % 8) == 0 && contiguous &&
             x_dtype == GNF4B_X_BF16) {
-            const int kDConsumerWarps = decode_consumer_warps(rm);
+            const int kDConsumerWarps = decode_consumer_warps(rm, au_k);
             DecodeArgs da;
             da.g = g;
             // rows per stage: up to 32 KiB of weight rows, chosen so that the CTA with the most items gets as
@@ -411,7 +420,7 @@ int gnf4b_gemm_grouped(int fmt, int op, const void* x, int x_dtype, int64_t T, c
             const int64_t groups_eff = std::max<int64_t>(1, std::min<int64_t>((int64_t)G * ((max_rows + rm - 1) / rm), T));
             int best_r = r_hi;
             int64_t best_cost = INT64_MAX;
-            for (int r = r_hi; r >= std::max(8, r_hi / 2); r -= r_step) {
+            for (int r = r_hi; au_k <= 3 && r >= std::max(8, r_hi / 2); r -= r_step) {
                 const int64_t items = groups_eff * ceil_div(N, r);
                 const int64_t per_cta = ceil_div(items, std::min<int64_t>(di.sm_count, items));
                 const int64_t cost = per_cta * (r + 2);

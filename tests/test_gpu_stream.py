@@ -405,6 +405,8 @@ def test_decode_kernel_equals_generic_streaming_kernel_bitwise(fmt, N, K):
     ("nf4", 1536, 2048, [2, 1, 0, 2, 1]), ("nf4", 1536, 2048, [4, 1, 3, 0, 2]), ("nf4", 2048, 768, [3, 4, 4, 1, 2]),
     ("nf4", 512, 2880 // 64 * 64, [2, 2, 1, 0, 2]), ("mxfp4", 2880, 2880, [1, 2, 2, 0, 1]), ("mxfp4", 64, 96, [4, 0, 3, 1, 4]),
     ("nf4", 256, 2048, [7, 1, 0, 16, 2]), ("mxfp4", 2880, 2880, [5, 1, 1, 0, 3]),
+    # rows of up to 7168 columns (DeepSeek-V3 hidden size): one row per pass, six consumer warps
+    ("nf4", 256, 7168, [1, 1, 0, 1, 1]), ("nf4", 136, 4096, [3, 1, 0, 2, 1]), ("mxfp4", 256, 7168, [2, 1, 1, 0, 4]),
 ])
 def test_small_group_decode_kernel_equals_generic_streaming_kernel_bitwise(fmt, N, K, sizes):
     """Groups of a few rows (known on the host) take the decode kernel two rows at a time -- both rows
