@@ -2,7 +2,7 @@
 // weights streamed once per pair of rows and decoded once for both.
 //
 // The tight special case of the streaming path, taken when the host knows that no group has
-// more than 16 rows, K <= 3072, N % 8 == 0 and the stack is laid out so that consecutive
+// more than 16 rows, K <= 7168 (beyond 3072 one row per pass), N % 8 == 0 and the stack is laid out so that consecutive
 // weight rows (and their scale rows) are contiguous and 16-byte aligned.  Then a work item
 // (group, tile of R weight rows) is ONE contiguous span of packed bytes and ONE
 // contiguous span of scale bytes, so a stage of the ring is filled by two bulk copies
