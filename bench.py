@@ -277,6 +277,49 @@ def run_gpu(args, shape, rank, world):
         buf.copy_(o, non_blocking=False)      # device -> host read of the step's result, synchronous
         return buf
 
+    # one bound host-buffer call per resident stack (the stack is checked once, not per step)
+    host_runs = [tuple(nf4_grouped.HostGroupedGemm(w, sc, fmt=shape.fmt) for (w, sc) in (gu, dn)) for (gu, dn) in layers]
+    for s in steps:                          # host group tables in the form the C entry point takes
+        s["sizes_t"] = torch.tensor(s["sizes"], dtype=torch.int32)
+        s["eids_t"] = torch.tensor(s["eids"], dtype=torch.int32)
+
+    def pinned_out(rows, cols):
+        buf = host_out.get((rows, cols))
+        if buf is None:
+            buf = host_out[(rows, cols)] = torch.empty(rows, cols, dtype=torch.bfloat16, pin_memory=True)
+        return buf
+
+    def layer_e2e_host(i):
+        """Both GEMMs through the host-buffer C entry point: host activations and group tables in, host
+        result out, each call blocking (the calling convention of the reference's native CPU kernels)."""
+        (run_gu, run_dn), s = host_runs[i % args.layers], steps[i]
+        run_gu(s["a"], s["sizes_t"], s["eids_t"], pinned_out(s["rows"], shape.gate_up[0]))
+        return run_dn(s["h"], s["sizes_t"], s["eids_t"], pinned_out(s["rows"], shape.down[0]))
+
+    host_ffns = ([nf4_grouped.HostGroupedFfn(gu[0], gu[1], dn[0], dn[1], fmt=shape.fmt) for (gu, dn) in layers]
+                 if shape.gate_up[0] == 2 * shape.down[1] else None)
+
+    def layer_e2e_ffn(i):
+        """The layer as ONE blocking host call: gate_up GEMM, SiLU-GLU, down GEMM (the down input is the
+        layer's own intermediate, not the synthetic `h`); one upload, one download, one synchronise."""
+        s = steps[i]
+        return host_ffns[i % args.layers](s["a"], s["sizes_t"], s["eids_t"], pinned_out(s["rows"], shape.down[0]))
+
+    def time_e2e(step_fn):
+        for i in range(W):
+            step_fn(i)
+        out = []
+        for _ in range(max(1, args.repeats // 2)):
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(W, W + K):
+                step_fn(i)
+            e1.record()
+            barrier()
+            out.append(e0.elapsed_time(e1))
+        return out
+
     def barrier():
         if world > 1:
             torch.distributed.barrier()
@@ -320,28 +363,22 @@ def run_gpu(args, shape, rank, world):
     with ClockSampler(dev.index) as clk:
         t_layer = timed_replay(g_layer, args.repeats, min_seconds=0.5)
         t_gu = timed_replay(g_gu, args.repeats)
-        # end to end through the public entry points with host inputs
-        for i in range(W):
-            layer_e2e(i)
-        e2e_t = []
-        for _ in range(max(1, args.repeats // 2)):
-            barrier()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for i in range(W, W + K):
-                layer_e2e(i)
-            e1.record()
-            barrier()
-            e2e_t.append(e0.elapsed_time(e1))
+        # end to end with host inputs and a host result: through the host-buffer C entry point (the
+        # headline e2e), and through the tensor entry points with torch doing the copies
+        e2e_t = time_e2e(layer_e2e_host)
+        e2e_dev_t = time_e2e(layer_e2e)
+        e2e_ffn_t = time_e2e(layer_e2e_ffn) if host_ffns else None
     status = nf4_grouped.last_status(dev)
 
     ms_layer = statistics.median(t_layer)
     ms_gu = statistics.median(t_gu)
     ms_e2e = statistics.median(e2e_t)
+    ms_e2e_dev = statistics.median(e2e_dev_t)
+    ms_e2e_ffn = statistics.median(e2e_ffn_t) if e2e_ffn_t else None
     if world > 1:
-        t = torch.tensor([ms_layer, ms_gu, ms_e2e], device=dev)
+        t = torch.tensor([ms_layer, ms_gu, ms_e2e, ms_e2e_dev], device=dev)
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-        ms_layer, ms_gu, ms_e2e = t.tolist()
+        ms_layer, ms_gu, ms_e2e, ms_e2e_dev = t.tolist()
 
     rows = [s["rows"] for s in steps[W:]]
     act = [s["active"] for s in steps[W:]]
@@ -368,8 +405,12 @@ def run_gpu(args, shape, rank, world):
                 algorithmic_bytes=statistics.mean(by), algorithmic_flops=statistics.mean(fl))
     us_layer = ms_layer * 1e3 / K
     us_e2e = ms_e2e * 1e3 / K
-    h2d = statistics.mean((s["a"].numel() + s["h"].numel()) * 2 + (2 * len(s["sizes"]) + 1) * 8 for s in steps[W:])
-    d2h = statistics.mean(s["rows"] * shape.hidden * 2 for s in steps[W:])
+    # host-buffer entry point: per GEMM the activations and (2G+2) table ints go up, the whole result comes back
+    h2d = statistics.mean((s["a"].numel() + s["h"].numel()) * 2 + 2 * (2 * len(s["sizes"]) + 2) * 4 for s in steps[W:])
+    d2h = statistics.mean(s["rows"] * (shape.gate_up[0] + shape.down[0]) * 2 for s in steps[W:])
+    # tensor entry points: the same uploads, only the layer's final result is read back
+    h2d_dev = statistics.mean((s["a"].numel() + s["h"].numel()) * 2 + (2 * len(s["sizes"]) + 1) * 8 for s in steps[W:])
+    d2h_dev = statistics.mean(s["rows"] * shape.down[0] * 2 for s in steps[W:])
     base = BASELINE_US.get((shape.name, args.tokens))
     line = {
         "metric": "grouped 4-bit MoE GEMM us/layer", "value": us_layer, "unit": "us/layer",
@@ -381,7 +422,13 @@ def run_gpu(args, shape, rank, world):
                    "tokens": args.tokens, "layers_resident": args.layers,
                    "l2": f"inputs larger than L2: {args.layers} layer stacks walked round-robin, fresh routing per step",
                    "timing": f"K steps in one CUDA graph, median of {len(t_layer)} replays, CUDA events"},
-        "e2e": {"value": us_e2e, "unit": "us/layer", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "e2e": {"value": us_e2e, "unit": "us/layer", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "api": "gnf4b_gemm_grouped_host (nf4_grouped.HostGroupedGemm): host x, sizes, expert ids and "
+                       "result per GEMM, two blocking calls per layer"},
+        "e2e_tensor_api": {"value": ms_e2e_dev * 1e3 / K, "unit": "us/layer", "h2d_bytes_per_step": h2d_dev,
+                           "d2h_bytes_per_step": d2h_dev,
+                           "api": f"{fn.__name__} on CUDA tensors, torch copies from pinned memory, final result "
+                                  "read back"},
         "gpu_launches": 2 * K,
         "roofline": roof,
         "layer": {"decode_gbs": statistics.mean(by_l) / (us_layer * 1e-6) / 1e9,
@@ -389,6 +436,17 @@ def run_gpu(args, shape, rank, world):
                   "rows_per_active_expert": rows_per_group, "active_experts": statistics.mean(act)},
         "clocks": clk.summary(), "device_status": status, "repeats_ms": t_layer[:16],
     }
+    if ms_e2e_ffn is not None:
+        if world > 1:
+            t = torch.tensor([ms_e2e_ffn], device=dev)
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+            ms_e2e_ffn = t.item()
+        line["e2e_ffn"] = {
+            "value": ms_e2e_ffn * 1e3 / K, "unit": "us/layer",
+            "h2d_bytes_per_step": statistics.mean(s["a"].numel() * 2 + (2 * len(s["sizes"]) + 2) * 4 for s in steps[W:]),
+            "d2h_bytes_per_step": d2h_dev,
+            "api": "gnf4b_ffn_grouped_host (nf4_grouped.HostGroupedFfn): gate_up GEMM, SiLU-GLU, down GEMM in one "
+                   "blocking host call per layer; three kernels, the intermediate stays on the device"}
     if world == 1:
         try:
             ep_us = time_ep_layer_single_gpu(args, shape, layers, dev)

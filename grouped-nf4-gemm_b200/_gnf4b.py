@@ -82,6 +82,18 @@ def _declare(lib):
     lib.gnf4b_gemm_grouped_noalloc.argtypes = [
         C.c_int, C.c_int, vp, C.c_int, i64, vp, i64, i64, vp, C.c_int, i64, i64,
         vp, vp, i32, i32, i64, i64, i32, vp, vp, u32, vp]
+    lib.gnf4b_gemm_grouped_host.restype = C.c_int
+    lib.gnf4b_gemm_grouped_host.argtypes = [
+        C.c_int, C.c_int, vp, C.c_int, i64, vp, i64, i64, vp, C.c_int, i64, i64,
+        vp, vp, i32, i32, i64, i64, vp, vp, sz, vp, u32, vp]
+    lib.gnf4b_ffn_grouped_host.restype = C.c_int
+    lib.gnf4b_ffn_grouped_host.argtypes = [
+        C.c_int, vp, C.c_int, i64, vp, i64, i64, vp, i64, i64, vp, i64, i64, vp, i64, i64, C.c_int,
+        vp, vp, i32, i32, i64, i64, i64, vp, vp, sz, vp, u32, vp]
+    lib.gnf4b_ffn_host_staging_bytes.restype = sz
+    lib.gnf4b_ffn_host_staging_bytes.argtypes = [C.c_int, i64, i32, i64, i64, i64, u32]
+    lib.gnf4b_host_staging_bytes.restype = sz
+    lib.gnf4b_host_staging_bytes.argtypes = [C.c_int, C.c_int, i64, i32, i64, i64, u32]
     lib.gnf4b_workspace_bytes.restype = sz
     lib.gnf4b_workspace_bytes.argtypes = [C.c_int, C.c_int, i64, i32, i64, i64, i32, u32]
     lib.gnf4b_plan_split_k.restype = C.c_int
@@ -109,7 +121,8 @@ def _declare(lib):
 
 #: every symbol include/gnf4b.h declares
 EXPORTS = ("gnf4b_abi_version", "gnf4b_strerror", "gnf4b_last_cuda_error", "gnf4b_gemm_grouped",
-           "gnf4b_gemm_grouped_noalloc",
+           "gnf4b_gemm_grouped_noalloc", "gnf4b_gemm_grouped_host", "gnf4b_host_staging_bytes",
+           "gnf4b_ffn_grouped_host", "gnf4b_ffn_host_staging_bytes",
            "gnf4b_workspace_bytes", "gnf4b_plan_split_k", "gnf4b_build_offsets", "gnf4b_upload_i32", "gnf4b_dequant", "gnf4b_silu_glu", "gnf4b_combine_rows", "gnf4b_ep_plan", "gnf4b_ep_offsets", "gnf4b_route_topk",
            "gnf4b_device_info")
 

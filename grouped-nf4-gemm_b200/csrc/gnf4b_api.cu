@@ -6,6 +6,7 @@
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <vector>
 
 #include "common.cuh"
 #include "stream_kernel.cuh"
@@ -509,6 +510,290 @@ int gnf4b_gemm_grouped_noalloc(int fmt, int op, const void* x, int x_dtype, int6
     return gnf4b_gemm_grouped(fmt, op, x, x_dtype, T, W, w_stride_e, w_stride_n, S, s_dtype, s_stride_e, s_stride_n,
                               group_offsets, expert_ids, G, E, N, K, max_rows, out, scratch,
                               (size_t)GNF4B_NOALLOC_SCRATCH_BYTES, status_word, flags, cuda_stream);
+}
+
+// ---- host-buffer entry point -------------------------------------------------------------------
+// Layout of the caller's device staging block (every piece 256-byte aligned):
+//   [ planner workspace (worst case over routings) | offsets[G+1], ids[G], status | x | out ]
+// tables, status and x are adjacent so that a small x travels in the same copy as the tables.
+struct HostStaging {
+    size_t ws = 0, tab = 0, x = 0, out = 0, total = 0;   // byte offsets; ws is at 0
+    size_t ws_bytes = 0, tab_bytes = 0, x_bytes = 0, out_bytes = 0;
+};
+
+static int host_staging_layout(int fmt, int op, int64_t T, int32_t G, int64_t N, int64_t K, uint32_t flags,
+                               const DevInfo& di, HostStaging* h) {
+    size_t worst = 0;
+    const int32_t probes[2] = {1, -1};      // scratch exists only on the streaming path: both path choices
+    for (int32_t mr : probes) {
+        Plan p;
+        const int rc = make_plan(fmt, op, T, G, N, K, mr, flags, di, &p);
+        if (rc == GNF4B_OK) worst = std::max(worst, p.counters_bytes + p.ws_bytes);
+        else if (rc != GNF4B_EUNSUPPORTED) return rc;
+    }
+    const int64_t in_cols = (op == GNF4B_OP_FWD) ? K : N, out_cols = (op == GNF4B_OP_FWD) ? N : K;
+    h->ws_bytes = worst;
+    h->tab_bytes = (size_t)(2 * (int64_t)G + 2) * 4;
+    h->x_bytes = (size_t)T * (size_t)in_cols * 2;
+    h->out_bytes = (size_t)T * (size_t)out_cols * 2;
+    h->tab = (size_t)round_up((int64_t)h->ws_bytes, 256);
+    h->x = h->tab + (size_t)round_up((int64_t)h->tab_bytes, 256);
+    h->out = h->x + (size_t)round_up((int64_t)h->x_bytes, 256);
+    h->total = h->out + (size_t)round_up((int64_t)h->out_bytes, 256);
+    return GNF4B_OK;
+}
+
+static constexpr size_t kHostPinnedBytes = 64u << 10;
+
+// The calling thread's pinned block (group tables, and x when it fits).  Freed when the thread ends.
+struct PinnedBlock {
+    unsigned char* p = nullptr;
+    ~PinnedBlock() { if (p) cudaFreeHost(p); }
+};
+
+static PinnedBlock& thread_pinned_block() {
+    static thread_local PinnedBlock pin;
+    return pin;
+}
+
+size_t gnf4b_host_staging_bytes(int fmt, int op, int64_t T, int32_t G, int64_t N, int64_t K, uint32_t flags) {
+    if (check_shape(fmt, op, GNF4B_X_BF16, fmt == GNF4B_FMT_NF4 ? GNF4B_S_F32 : GNF4B_S_E8M0, T, G, 1, N, K)) return 0;
+    DevInfo di;
+    if (device_info(&di)) return 0;
+    HostStaging h;
+    if (host_staging_layout(fmt, op, T, G, N, K, flags, di, &h)) return 0;
+    return h.total;
+}
+
+int gnf4b_gemm_grouped_host(int fmt, int op, const void* x_host, int x_dtype, int64_t T, const uint8_t* W,
+                            int64_t w_stride_e, int64_t w_stride_n, const void* S, int s_dtype,
+                            int64_t s_stride_e, int64_t s_stride_n, const int32_t* sizes_host,
+                            const int32_t* expert_ids_host, int32_t G, int32_t E, int64_t N, int64_t K,
+                            void* out_host, void* staging, size_t staging_bytes, int32_t* status_host,
+                            uint32_t flags, void* cuda_stream) {
+    int rc = check_shape(fmt, op, x_dtype, s_dtype, T, G, E, N, K);
+    if (rc) return rc;
+    if (status_host) *status_host = 0;
+    if (G > 0 && (!sizes_host || !expert_ids_host)) return GNF4B_EINVAL;
+    int64_t total = 0;
+    int32_t max_rows = 0;
+    for (int32_t g = 0; g < G; ++g) {
+        const int32_t n = sizes_host[g], e = expert_ids_host[g];
+        if (n < 0 || (e != GNF4B_PAD_EXPERT && (e < 0 || e >= E))) return GNF4B_EINVAL;
+        total += n;
+        max_rows = std::max(max_rows, n);
+    }
+    if (total != T) return GNF4B_EINVAL;
+    if (T == 0 || G == 0) return GNF4B_OK;
+    if (!x_host || !out_host || !staging || ((uintptr_t)staging & 255)) return GNF4B_EINVAL;
+    DevInfo di;
+    rc = device_info(&di);
+    if (rc) return rc;
+    HostStaging h;
+    rc = host_staging_layout(fmt, op, T, G, N, K, flags, di, &h);
+    if (rc) return rc;
+    if (staging_bytes < h.total) return GNF4B_EWORKSPACE;
+    Plan p;
+    rc = make_plan(fmt, op, T, G, N, K, max_rows, flags, di, &p);
+    if (rc) return rc;
+
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(cuda_stream);
+    unsigned char* base = static_cast<unsigned char*>(staging);
+    int32_t* d_off = reinterpret_cast<int32_t*>(base + h.tab);
+    int32_t* d_ids = d_off + (G + 1);
+    int32_t* d_status = d_ids + G;
+    void* d_x = base + h.x;
+    void* d_out = base + h.out;
+    cudaError_t e;
+
+    PinnedBlock& pin = thread_pinned_block();
+    if (!pin.p) {
+        e = cudaHostAlloc(reinterpret_cast<void**>(&pin.p), kHostPinnedBytes, cudaHostAllocDefault);
+        if (e != cudaSuccess) { pin.p = nullptr; return cuda_fail(e, "cudaHostAlloc(pinned block)"); }
+    }
+    const size_t tab_span = h.x - h.tab;                 // tables + status, padded up to where x starts
+    const bool tab_fits = tab_span <= kHostPinnedBytes;
+    const bool x_rides = tab_fits && tab_span + h.x_bytes <= kHostPinnedBytes;
+    std::vector<int32_t> big_tab;                        // only for G beyond the pinned block
+    int32_t* t = tab_fits ? reinterpret_cast<int32_t*>(pin.p) : (big_tab.resize(2 * (size_t)G + 2), big_tab.data());
+    t[0] = 0;
+    for (int32_t g = 0; g < G; ++g) t[g + 1] = t[g] + sizes_host[g];
+    std::memcpy(t + G + 1, expert_ids_host, (size_t)G * 4);
+    t[2 * (size_t)G + 1] = 0;                            // the status word starts clear
+    if (x_rides) {
+        std::memcpy(pin.p + tab_span, x_host, h.x_bytes);
+        e = cudaMemcpyAsync(d_off, pin.p, tab_span + h.x_bytes, cudaMemcpyHostToDevice, st);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(tables + x)");
+    } else {
+        e = cudaMemcpyAsync(d_off, t, h.tab_bytes, cudaMemcpyHostToDevice, st);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(tables)");
+        e = cudaMemcpyAsync(d_x, x_host, h.x_bytes, cudaMemcpyHostToDevice, st);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(x)");
+    }
+    if (p.counters_bytes) {
+        e = cudaMemsetAsync(base, 0, p.counters_bytes, st);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(arrival counters)");
+    }
+    rc = gnf4b_gemm_grouped(fmt, op, d_x, x_dtype, T, W, w_stride_e, w_stride_n, S, s_dtype, s_stride_e, s_stride_n,
+                            d_off, d_ids, G, E, N, K, max_rows, d_out, h.ws_bytes ? base : nullptr, h.ws_bytes,
+                            d_status, flags, cuda_stream);
+    if (rc) { cudaStreamSynchronize(st); return rc; }    // the copies above read host memory: let them finish
+    e = cudaMemcpyAsync(out_host, d_out, h.out_bytes, cudaMemcpyDeviceToHost, st);
+    if (e != cudaSuccess) { cudaStreamSynchronize(st); return cuda_fail(e, "cudaMemcpyAsync(out)"); }
+    if (status_host) {
+        e = cudaMemcpyAsync(status_host, d_status, 4, cudaMemcpyDeviceToHost, st);
+        if (e != cudaSuccess) { cudaStreamSynchronize(st); return cuda_fail(e, "cudaMemcpyAsync(status)"); }
+    }
+    e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaStreamSynchronize");
+    return GNF4B_OK;
+}
+
+// ---- host-buffer expert FFN: gate_up GEMM -> SiLU(gate) * up -> down GEMM, one round trip -----------
+// Staging: [ workspace (larger of the two GEMMs' worst cases) | offsets, ids, status | x | gate_up | h | out ]
+struct FfnStaging {
+    size_t tab = 0, x = 0, gu = 0, h = 0, out = 0, total = 0;
+    size_t ws_bytes = 0, tab_bytes = 0, x_bytes = 0, gu_bytes = 0, h_bytes = 0, out_bytes = 0;
+};
+
+static int ffn_staging_layout(int fmt, int64_t T, int32_t G, int64_t N_gu, int64_t K_gu, int64_t N_dn, uint32_t flags,
+                              const DevInfo& di, FfnStaging* f) {
+    HostStaging a, b;
+    int rc = host_staging_layout(fmt, GNF4B_OP_FWD, T, G, N_gu, K_gu, flags, di, &a);
+    if (rc) return rc;
+    rc = host_staging_layout(fmt, GNF4B_OP_FWD, T, G, N_dn, N_gu / 2, flags, di, &b);
+    if (rc) return rc;
+    auto up = [](size_t v) { return (size_t)round_up((int64_t)v, 256); };
+    f->ws_bytes = std::max(a.ws_bytes, b.ws_bytes);
+    f->tab_bytes = a.tab_bytes;
+    f->x_bytes = a.x_bytes;
+    f->gu_bytes = a.out_bytes;
+    f->h_bytes = b.x_bytes;
+    f->out_bytes = b.out_bytes;
+    f->tab = up(f->ws_bytes);
+    f->x = f->tab + up(f->tab_bytes);
+    f->gu = f->x + up(f->x_bytes);
+    f->h = f->gu + up(f->gu_bytes);
+    f->out = f->h + up(f->h_bytes);
+    f->total = f->out + up(f->out_bytes);
+    return GNF4B_OK;
+}
+
+static int ffn_check(int fmt, int x_dtype, int s_dtype, int64_t T, int32_t G, int32_t E, int64_t N_gu, int64_t K_gu,
+                     int64_t N_dn) {
+    int rc = check_shape(fmt, GNF4B_OP_FWD, x_dtype, s_dtype, T, G, E, N_gu, K_gu);
+    if (rc) return rc;
+    if (x_dtype != GNF4B_X_BF16) return GNF4B_EUNSUPPORTED;      // the GLU kernel writes bf16
+    if (N_gu % 2) return GNF4B_ESHAPE;
+    return check_shape(fmt, GNF4B_OP_FWD, x_dtype, s_dtype, T, G, E, N_dn, N_gu / 2);
+}
+
+size_t gnf4b_ffn_host_staging_bytes(int fmt, int64_t T, int32_t G, int64_t N_gu, int64_t K_gu, int64_t N_dn,
+                                    uint32_t flags) {
+    if (ffn_check(fmt, GNF4B_X_BF16, fmt == GNF4B_FMT_NF4 ? GNF4B_S_F32 : GNF4B_S_E8M0, T, G, 1, N_gu, K_gu, N_dn)) return 0;
+    DevInfo di;
+    if (device_info(&di)) return 0;
+    FfnStaging f;
+    if (ffn_staging_layout(fmt, T, G, N_gu, K_gu, N_dn, flags, di, &f)) return 0;
+    return f.total;
+}
+
+int gnf4b_ffn_grouped_host(int fmt, const void* x_host, int x_dtype, int64_t T,
+                           const uint8_t* W_gu, int64_t wgu_stride_e, int64_t wgu_stride_n,
+                           const void* S_gu, int64_t sgu_stride_e, int64_t sgu_stride_n,
+                           const uint8_t* W_dn, int64_t wdn_stride_e, int64_t wdn_stride_n,
+                           const void* S_dn, int64_t sdn_stride_e, int64_t sdn_stride_n, int s_dtype,
+                           const int32_t* sizes_host, const int32_t* expert_ids_host, int32_t G, int32_t E,
+                           int64_t N_gu, int64_t K_gu, int64_t N_dn, void* out_host, void* staging,
+                           size_t staging_bytes, int32_t* status_host, uint32_t flags, void* cuda_stream) {
+    int rc = ffn_check(fmt, x_dtype, s_dtype, T, G, E, N_gu, K_gu, N_dn);
+    if (rc) return rc;
+    if (status_host) *status_host = 0;
+    if (G > 0 && (!sizes_host || !expert_ids_host)) return GNF4B_EINVAL;
+    int64_t total = 0;
+    int32_t max_rows = 0;
+    for (int32_t g = 0; g < G; ++g) {
+        const int32_t n = sizes_host[g], e = expert_ids_host[g];
+        if (n < 0 || (e != GNF4B_PAD_EXPERT && (e < 0 || e >= E))) return GNF4B_EINVAL;
+        total += n;
+        max_rows = std::max(max_rows, n);
+    }
+    if (total != T) return GNF4B_EINVAL;
+    if (T == 0 || G == 0) return GNF4B_OK;
+    if (!x_host || !out_host || !staging || ((uintptr_t)staging & 255)) return GNF4B_EINVAL;
+    DevInfo di;
+    rc = device_info(&di);
+    if (rc) return rc;
+    FfnStaging f;
+    rc = ffn_staging_layout(fmt, T, G, N_gu, K_gu, N_dn, flags, di, &f);
+    if (rc) return rc;
+    if (staging_bytes < f.total) return GNF4B_EWORKSPACE;
+    const int64_t H = N_gu / 2;
+    Plan p_gu, p_dn;
+    rc = make_plan(fmt, GNF4B_OP_FWD, T, G, N_gu, K_gu, max_rows, flags, di, &p_gu);
+    if (rc) return rc;
+    rc = make_plan(fmt, GNF4B_OP_FWD, T, G, N_dn, H, max_rows, flags, di, &p_dn);
+    if (rc) return rc;
+
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(cuda_stream);
+    unsigned char* base = static_cast<unsigned char*>(staging);
+    int32_t* d_off = reinterpret_cast<int32_t*>(base + f.tab);
+    int32_t* d_ids = d_off + (G + 1);
+    int32_t* d_status = d_ids + G;
+    cudaError_t e;
+
+    PinnedBlock& pin = thread_pinned_block();
+    if (!pin.p) {
+        e = cudaHostAlloc(reinterpret_cast<void**>(&pin.p), kHostPinnedBytes, cudaHostAllocDefault);
+        if (e != cudaSuccess) { pin.p = nullptr; return cuda_fail(e, "cudaHostAlloc(pinned block)"); }
+    }
+    const size_t tab_span = f.x - f.tab;
+    const bool tab_fits = tab_span <= kHostPinnedBytes;
+    const bool x_rides = tab_fits && tab_span + f.x_bytes <= kHostPinnedBytes;
+    std::vector<int32_t> big_tab;
+    int32_t* t = tab_fits ? reinterpret_cast<int32_t*>(pin.p) : (big_tab.resize(2 * (size_t)G + 2), big_tab.data());
+    t[0] = 0;
+    for (int32_t g = 0; g < G; ++g) t[g + 1] = t[g] + sizes_host[g];
+    std::memcpy(t + G + 1, expert_ids_host, (size_t)G * 4);
+    t[2 * (size_t)G + 1] = 0;
+    if (x_rides) {
+        std::memcpy(pin.p + tab_span, x_host, f.x_bytes);
+        e = cudaMemcpyAsync(d_off, pin.p, tab_span + f.x_bytes, cudaMemcpyHostToDevice, st);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(tables + x)");
+    } else {
+        e = cudaMemcpyAsync(d_off, t, f.tab_bytes, cudaMemcpyHostToDevice, st);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(tables)");
+        e = cudaMemcpyAsync(base + f.x, x_host, f.x_bytes, cudaMemcpyHostToDevice, st);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(x)");
+    }
+    auto fail = [&](int code) { cudaStreamSynchronize(st); return code; };   // queued copies read host memory
+    if (p_gu.counters_bytes) {
+        e = cudaMemsetAsync(base, 0, p_gu.counters_bytes, st);
+        if (e != cudaSuccess) return fail(cuda_fail(e, "cudaMemsetAsync(arrival counters)"));
+    }
+    rc = gnf4b_gemm_grouped(fmt, GNF4B_OP_FWD, base + f.x, x_dtype, T, W_gu, wgu_stride_e, wgu_stride_n, S_gu, s_dtype,
+                            sgu_stride_e, sgu_stride_n, d_off, d_ids, G, E, N_gu, K_gu, max_rows, base + f.gu,
+                            f.ws_bytes ? base : nullptr, f.ws_bytes, d_status, flags, cuda_stream);
+    if (rc) return fail(rc);
+    rc = gnf4b_silu_glu(base + f.gu, T, H, base + f.h, cuda_stream);
+    if (rc) return fail(rc);
+    if (p_dn.counters_bytes) {
+        e = cudaMemsetAsync(base, 0, p_dn.counters_bytes, st);
+        if (e != cudaSuccess) return fail(cuda_fail(e, "cudaMemsetAsync(arrival counters)"));
+    }
+    rc = gnf4b_gemm_grouped(fmt, GNF4B_OP_FWD, base + f.h, x_dtype, T, W_dn, wdn_stride_e, wdn_stride_n, S_dn, s_dtype,
+                            sdn_stride_e, sdn_stride_n, d_off, d_ids, G, E, N_dn, H, max_rows, base + f.out,
+                            f.ws_bytes ? base : nullptr, f.ws_bytes, d_status, flags, cuda_stream);
+    if (rc) return fail(rc);
+    e = cudaMemcpyAsync(out_host, base + f.out, f.out_bytes, cudaMemcpyDeviceToHost, st);
+    if (e != cudaSuccess) return fail(cuda_fail(e, "cudaMemcpyAsync(out)"));
+    if (status_host) {
+        e = cudaMemcpyAsync(status_host, d_status, 4, cudaMemcpyDeviceToHost, st);
+        if (e != cudaSuccess) return fail(cuda_fail(e, "cudaMemcpyAsync(status)"));
+    }
+    e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaStreamSynchronize");
+    return GNF4B_OK;
 }
 
 int gnf4b_build_offsets(const int32_t* sizes, int32_t G, int32_t* group_offsets, void* cuda_stream) {

@@ -15,7 +15,7 @@ from __future__ import annotations
 import torch
 
 import _gnf4b
-from nf4_grouped import (_launch, _prefill_block_m, _require_cuda,  # noqa: F401  (re-exported names)
+from nf4_grouped import (_launch, _launch_host, _prefill_block_m, _require_cuda,  # noqa: F401  (re-exported names)
                          build_group_tiles)
 
 # e2m1 codebook, index = (sign << 3) | magnitude (ref :34-35)
@@ -54,6 +54,22 @@ def gemm_mxfp4_grouped(a_cat, blocks, scales, sizes, expert_ids,
         raise ValueError(f"a_cat has K={K} but blocks pack K={blocks.shape[2] * 2}")
     return _launch(_gnf4b.FMT_MXFP4, _gnf4b.OP_FWD, a_cat, blocks, scales, sizes, expert_ids, N,
                    group_offsets=group_offsets, max_rows=max_rows, path=path)
+
+
+def gemm_mxfp4_grouped_host(a_host, blocks, scales, sizes, expert_ids, out=None, *, path: int = 0,
+                            return_status: bool = False):
+    """``gemm_mxfp4_grouped`` with host activations, host group tables and a host result, the stack resident on
+    the GPU: the calling convention of the reference's native CPU kernel
+    (``gnf4_native/cpu_kernels.c:1097``).  See ``nf4_grouped.gemm_4bit_grouped_host``."""
+    assert blocks.dtype == torch.uint8 and scales.dtype == torch.uint8
+    return _launch_host(_gnf4b.FMT_MXFP4, _gnf4b.OP_FWD, a_host, blocks, scales, sizes, expert_ids,
+                        blocks.shape[1], out, path=path, return_status=return_status)
+
+
+def dgrad_mxfp4_grouped_host(grad_host, blocks, scales, sizes, expert_ids, out=None, *, return_status: bool = False):
+    """``dgrad_mxfp4_grouped`` with host buffers (``gnf4_native/cpu_kernels.c:1386-1397``)."""
+    return _launch_host(_gnf4b.FMT_MXFP4, _gnf4b.OP_DGRAD, grad_host, blocks, scales, sizes, expert_ids,
+                        blocks.shape[2] * 2, out, return_status=return_status)
 
 
 def dgrad_mxfp4_grouped(grad_out, blocks, scales, sizes, expert_ids, *, group_offsets=None, max_rows=None):

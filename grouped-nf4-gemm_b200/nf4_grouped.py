@@ -22,6 +22,7 @@ change results.
 """
 from __future__ import annotations
 
+import ctypes
 import os
 
 import torch
@@ -611,6 +612,282 @@ def dgrad_4bit_grouped(grad_out, B, absmax, sizes, expert_ids, config=None, *, g
         raise ValueError(f"grad_out has {grad_out.shape[1]} columns but the stack has N={N}")
     return _launch(_gnf4b.FMT_NF4, _gnf4b.OP_DGRAD, grad_out, B, absmax, sizes, expert_ids, K,
                    group_offsets=group_offsets, max_rows=max_rows)
+
+
+# --------------------------------------------------------------------------- #
+# host-buffer entry points (activations, group tables and result in host memory)
+# --------------------------------------------------------------------------- #
+_HOST_STAGING = {}    # device index -> uint8 CUDA tensor, grown on demand
+_HOST_NEED = {}       # (device, fmt, op, T, G, N, K, flags) -> staging bytes
+
+
+def _host_i32(v, what):
+    """-> (address, count, keep-alive) of a host int32 array."""
+    if torch.is_tensor(v):
+        if v.is_cuda:
+            raise ValueError(f"{what} must live in host memory for the host-buffer entry points")
+        if v.dtype != torch.int32 or not v.is_contiguous():
+            v = v.to(torch.int32).contiguous()
+        return v.data_ptr(), int(v.numel()), v
+    arr = (ctypes.c_int32 * len(v))(*[int(i) for i in v])
+    return ctypes.addressof(arr), len(v), arr
+
+
+def _launch_host(fmt, op, x, W, S, sizes, expert_ids, n_out, out=None, *, split_k=None, path=_gnf4b.PATH_AUTO,
+                 return_status=False):
+    """One blocking grouped GEMM with host ``x`` / ``sizes`` / ``expert_ids`` / result and a device-resident
+    stack: the library call ``gnf4b_gemm_grouped_host`` (tables and small ``x`` in one copy, launch, result
+    copy, stream synchronise)."""
+    if x.is_cuda:
+        raise ValueError("the host-buffer entry points take host activations; use the plain entry points for CUDA tensors")
+    dev = W.device
+    if dev.type != "cuda" or S.device != dev:
+        raise ValueError("the packed stack and its scales must be CUDA tensors on one device")
+    if x.dtype == torch.bfloat16:
+        xdt = _gnf4b.X_BF16
+    elif x.dtype == torch.float16:
+        xdt = _gnf4b.X_FP16
+    else:
+        raise TypeError(f"activations must be bfloat16 or float16, got {x.dtype}")
+    if W.dtype != torch.uint8:
+        raise TypeError(f"packed weights must be uint8, got {W.dtype}")
+    E, N, half = W.shape
+    K = half * 2
+    T = x.shape[0]
+    if x.shape[1] != (K if op == _gnf4b.OP_FWD else N):
+        raise ValueError(f"activations have {x.shape[1]} columns, the stack wants {K if op == _gnf4b.OP_FWD else N}")
+    if not x.is_contiguous():
+        x = x.contiguous()
+    if W.stride(2) != 1:
+        W = W.contiguous()
+    if fmt == _gnf4b.FMT_NF4:
+        if S.dtype == torch.float32:
+            sdt = _gnf4b.S_F32
+        elif S.dtype == torch.bfloat16:
+            sdt = _gnf4b.S_BF16
+        else:
+            S, sdt = S.to(torch.float32), _gnf4b.S_F32
+    else:
+        sdt = _gnf4b.S_E8M0
+    if S.stride(2) != 1:
+        S = S.contiguous()
+    if out is None:
+        out = torch.empty(T, n_out, dtype=torch.bfloat16, pin_memory=True)
+    elif out.is_cuda or out.dtype != torch.bfloat16 or tuple(out.shape) != (T, n_out) or not out.is_contiguous():
+        raise ValueError(f"out must be a contiguous host bfloat16 tensor of shape ({T}, {n_out})")
+    sz_p, G, sz_keep = _host_i32(sizes, "sizes")
+    id_p, n_ids, id_keep = _host_i32(expert_ids, "expert_ids")
+    if n_ids != G:
+        raise ValueError(f"sizes has {G} groups but expert_ids has {n_ids}")
+    if T == 0 or G == 0:
+        if T:
+            raise ValueError("rows without groups")
+        return (out, 0) if return_status else out
+    flags = path
+    if split_k is not None:
+        flags |= max(1, int(split_k)) << _gnf4b.SPLITK_SHIFT
+    lib = _gnf4b.load()
+    prev = -1
+    if dev.index is not None and dev.index != torch.cuda.current_device():
+        prev = torch.cuda.current_device()
+        torch.cuda.set_device(dev)
+    try:
+        key = (dev.index, fmt, op, T, G, N, K, flags)
+        need = _HOST_NEED.get(key)
+        if need is None:
+            need = lib.gnf4b_host_staging_bytes(*key[1:])
+            if len(_HOST_NEED) < 4096:
+                _HOST_NEED[key] = need
+        stage = _HOST_STAGING.get(dev.index)
+        if stage is None or stage.numel() < need:
+            stage = _HOST_STAGING[dev.index] = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=dev)
+        status = ctypes.c_int32(0) if return_status else None
+        rc = lib.gnf4b_gemm_grouped_host(
+            fmt, op, x.data_ptr(), xdt, T, W.data_ptr(), W.stride(0), W.stride(1),
+            S.data_ptr(), sdt, S.stride(0), S.stride(1), sz_p, id_p, G, E, N, K,
+            out.data_ptr(), stage.data_ptr(), stage.numel(),
+            ctypes.addressof(status) if return_status else None, flags, _raw_stream(dev))
+    finally:
+        if prev >= 0:
+            torch.cuda.set_device(prev)
+    if rc == -1:      # GNF4B_EINVAL
+        raise ValueError("gnf4b_gemm_grouped_host rejected the group tables: sizes must be >= 0 and sum to the "
+                         f"number of rows ({T}), expert ids must lie in [0, {E}) or be PAD_EXPERT")
+    if rc:
+        _gnf4b.check(rc, "gnf4b_gemm_grouped_host")
+    del sz_keep, id_keep
+    return (out, int(status.value)) if return_status else out
+
+
+class HostGroupedGemm:
+    """The host-buffer grouped GEMM bound to one device-resident stack, for a loop that calls it every step:
+    the stack is checked and its addresses and strides are read once, a call checks only what changes
+    (activations, group tables, result buffer).
+
+        run = HostGroupedGemm(B, absmax)                     # NF4 forward; fmt="mxfp4", op="dgrad" select the others
+        out = run(a_host, sizes_i32, expert_ids_i32, out_host)
+
+    ``a_host`` contiguous host bf16/fp16 ``[T, K]``; ``sizes_i32`` / ``expert_ids_i32`` contiguous host int32
+    tensors of the same length; ``out_host`` contiguous host bf16 ``[T, N]``.  Same results as
+    ``gemm_4bit_grouped_host`` (it is the same library call)."""
+
+    def __init__(self, packed, scales, fmt: str = "nf4", op: str = "fwd", path: int = 0):
+        if fmt not in ("nf4", "mxfp4") or op not in ("fwd", "dgrad"):
+            raise ValueError("fmt is 'nf4' or 'mxfp4', op is 'fwd' or 'dgrad'")
+        dev = packed.device
+        if dev.type != "cuda" or scales.device != dev:
+            raise ValueError("the packed stack and its scales must be CUDA tensors on one device")
+        if packed.dtype != torch.uint8:
+            raise TypeError(f"packed weights must be uint8, got {packed.dtype}")
+        if packed.stride(2) != 1:
+            packed = packed.contiguous()
+        self.fmt = _gnf4b.FMT_NF4 if fmt == "nf4" else _gnf4b.FMT_MXFP4
+        self.op = _gnf4b.OP_FWD if op == "fwd" else _gnf4b.OP_DGRAD
+        if fmt == "nf4":
+            if scales.dtype not in (torch.float32, torch.bfloat16):
+                scales = scales.to(torch.float32)
+            self.sdt = _gnf4b.S_F32 if scales.dtype == torch.float32 else _gnf4b.S_BF16
+        else:
+            if scales.dtype != torch.uint8:
+                raise TypeError("MXFP4 scales are e8m0 bytes (uint8)")
+            self.sdt = _gnf4b.S_E8M0
+        if scales.stride(2) != 1:
+            scales = scales.contiguous()
+        self.W, self.S, self.dev, self.flags = packed, scales, dev, int(path)      # keeps the stack alive
+        self.E, self.N, self.K = packed.shape[0], packed.shape[1], packed.shape[2] * 2
+        self.cols_in = self.K if op == "fwd" else self.N
+        self.cols_out = self.N if op == "fwd" else self.K
+        self._w = (packed.data_ptr(), packed.stride(0), packed.stride(1))
+        self._s = (scales.data_ptr(), self.sdt, scales.stride(0), scales.stride(1))
+        self._lib = _gnf4b.load()
+        self._need = {}
+
+    def __call__(self, x, sizes_i32, ids_i32, out):
+        T = x.shape[0]
+        G = sizes_i32.numel()
+        if (x.dtype is not torch.bfloat16 and x.dtype is not torch.float16) or x.shape[1] != self.cols_in \
+                or x.is_cuda or not x.is_contiguous():
+            raise ValueError(f"activations must be a contiguous host bf16/fp16 tensor with {self.cols_in} columns")
+        if sizes_i32.dtype is not torch.int32 or ids_i32.dtype is not torch.int32 or ids_i32.numel() != G \
+                or sizes_i32.is_cuda or ids_i32.is_cuda:
+            raise ValueError("sizes and expert ids must be host int32 tensors of the same length")
+        if out.dtype is not torch.bfloat16 or out.shape[0] != T or out.shape[1] != self.cols_out or out.is_cuda \
+                or not out.is_contiguous():
+            raise ValueError(f"out must be a contiguous host bfloat16 tensor of shape ({T}, {self.cols_out})")
+        if T == 0 or G == 0:
+            return out
+        dev = self.dev
+        if dev.index != torch.cuda.current_device():
+            with torch.cuda.device(dev):
+                return self(x, sizes_i32, ids_i32, out)
+        need = self._need.get((T, G))
+        if need is None:
+            need = self._lib.gnf4b_host_staging_bytes(self.fmt, self.op, T, G, self.N, self.K, self.flags)
+            if len(self._need) < 4096:
+                self._need[(T, G)] = need
+        stage = _HOST_STAGING.get(dev.index)
+        if stage is None or stage.numel() < need:
+            stage = _HOST_STAGING[dev.index] = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=dev)
+        rc = self._lib.gnf4b_gemm_grouped_host(
+            self.fmt, self.op, x.data_ptr(), _gnf4b.X_BF16 if x.dtype is torch.bfloat16 else _gnf4b.X_FP16, T,
+            *self._w, *self._s, sizes_i32.data_ptr(), ids_i32.data_ptr(), G, self.E, self.N, self.K,
+            out.data_ptr(), stage.data_ptr(), stage.numel(), None, self.flags, _raw_stream(dev))
+        if rc == -1:      # GNF4B_EINVAL
+            raise ValueError("gnf4b_gemm_grouped_host rejected the group tables: sizes must be >= 0 and sum to the "
+                             f"number of rows ({T}), expert ids must lie in [0, {self.E}) or be PAD_EXPERT")
+        if rc:
+            _gnf4b.check(rc, "gnf4b_gemm_grouped_host")
+        return out
+
+
+class HostGroupedFfn:
+    """One expert FFN per row with host buffers, bound to a device-resident gate_up / down pair:
+    ``out = (silu(gate) * up) @ W_dn[e].T`` with ``[gate | up] = x @ W_gu[e].T`` -- the GPU counterpart of the
+    reference's fused CPU entry point (``gnf4_native/cpu_kernels.c:947-986``).  One upload, gate_up GEMM,
+    SiLU-GLU kernel, down GEMM, one download, one synchronise (``gnf4b_ffn_grouped_host``); the ``[T, 2H]``
+    intermediate stays on the device.  Bit for bit what ``gemm -> ep_moe.silu_glu -> gemm`` gives.
+
+        ffn = HostGroupedFfn(B_gu, absmax_gu, B_dn, absmax_dn)            # fmt="mxfp4" for MXFP4 stacks
+        out = ffn(a_host, sizes_i32, expert_ids_i32, out_host)            # bf16 [T, N_dn]
+    """
+
+    def __init__(self, packed_gu, scales_gu, packed_dn, scales_dn, fmt: str = "nf4", path: int = 0):
+        gu = HostGroupedGemm(packed_gu, scales_gu, fmt=fmt, path=path)
+        dn = HostGroupedGemm(packed_dn, scales_dn, fmt=fmt, path=path)
+        if gu.dev != dn.dev or gu.E != dn.E or gu.sdt != dn.sdt:
+            raise ValueError("gate_up and down stacks must share device, expert count and scale dtype")
+        if gu.N % 2 or dn.K != gu.N // 2:
+            raise ValueError(f"down contracts over {dn.K} columns but gate_up yields 2 x {gu.N // 2}")
+        self.gu, self.dn, self.dev, self.flags = gu, dn, gu.dev, int(path)
+        self._lib = gu._lib
+        self._need = {}
+
+    def __call__(self, x, sizes_i32, ids_i32, out):
+        gu, dn = self.gu, self.dn
+        T, G = x.shape[0], sizes_i32.numel()
+        if x.dtype is not torch.bfloat16 or x.shape[1] != gu.K or x.is_cuda or not x.is_contiguous():
+            raise ValueError(f"activations must be a contiguous host bfloat16 tensor with {gu.K} columns")
+        if sizes_i32.dtype is not torch.int32 or ids_i32.dtype is not torch.int32 or ids_i32.numel() != G \
+                or sizes_i32.is_cuda or ids_i32.is_cuda:
+            raise ValueError("sizes and expert ids must be host int32 tensors of the same length")
+        if out.dtype is not torch.bfloat16 or out.shape[0] != T or out.shape[1] != dn.N or out.is_cuda \
+                or not out.is_contiguous():
+            raise ValueError(f"out must be a contiguous host bfloat16 tensor of shape ({T}, {dn.N})")
+        if T == 0 or G == 0:
+            return out
+        dev = self.dev
+        if dev.index != torch.cuda.current_device():
+            with torch.cuda.device(dev):
+                return self(x, sizes_i32, ids_i32, out)
+        need = self._need.get((T, G))
+        if need is None:
+            need = self._lib.gnf4b_ffn_host_staging_bytes(gu.fmt, T, G, gu.N, gu.K, dn.N, self.flags)
+            if len(self._need) < 4096:
+                self._need[(T, G)] = need
+        stage = _HOST_STAGING.get(dev.index)
+        if stage is None or stage.numel() < need:
+            stage = _HOST_STAGING[dev.index] = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=dev)
+        rc = self._lib.gnf4b_ffn_grouped_host(
+            gu.fmt, x.data_ptr(), _gnf4b.X_BF16, T, *gu._w, gu._s[0], gu._s[2], gu._s[3],
+            *dn._w, dn._s[0], dn._s[2], dn._s[3], gu.sdt, sizes_i32.data_ptr(), ids_i32.data_ptr(), G, gu.E,
+            gu.N, gu.K, dn.N, out.data_ptr(), stage.data_ptr(), stage.numel(), None, self.flags, _raw_stream(dev))
+        if rc == -1:      # GNF4B_EINVAL
+            raise ValueError("gnf4b_ffn_grouped_host rejected the group tables: sizes must be >= 0 and sum to the "
+                             f"number of rows ({T}), expert ids must lie in [0, {gu.E}) or be PAD_EXPERT")
+        if rc:
+            _gnf4b.check(rc, "gnf4b_ffn_grouped_host")
+        return out
+
+
+def ffn_4bit_grouped_host(a_host, B_gu, absmax_gu, B_dn, absmax_dn, sizes, expert_ids, out=None):
+    """One-shot form of ``HostGroupedFfn`` for NF4 stacks: ``sizes`` / ``expert_ids`` may be sequences, ``out``
+    is allocated (pinned) when absent."""
+    ffn = HostGroupedFfn(B_gu, absmax_gu, B_dn, absmax_dn)
+    sizes = torch.as_tensor(sizes, dtype=torch.int32).contiguous()
+    expert_ids = torch.as_tensor(expert_ids, dtype=torch.int32).contiguous()
+    if out is None:
+        out = torch.empty(a_host.shape[0], ffn.dn.N, dtype=torch.bfloat16, pin_memory=True)
+    return ffn(a_host.contiguous(), sizes, expert_ids, out)
+
+
+def gemm_4bit_grouped_host(a_host, B, absmax, sizes, expert_ids, out=None, *, split_k=None, path: int = 0,
+                           return_status: bool = False):
+    """``gemm_4bit_grouped`` for a caller that holds activations and routing in HOST memory and wants the
+    result there -- the calling convention of the reference's native CPU kernels
+    (``gnf4_native/cpu_kernels.c:751``, driven from ``kernel/cpu_grouped.py:272``), with the packed stack
+    ``B [E,N,K//2]`` / ``absmax`` resident on the GPU.  ``a_host [T,K]`` bf16/fp16 (pinned memory avoids a
+    staging copy), ``sizes`` / ``expert_ids`` host int32 tensors or sequences, ``out`` an optional host bf16
+    ``[T,N]`` to fill (a pinned tensor is allocated when absent: reuse one across calls).  Blocks until the
+    result is in ``out``.  ``return_status=True`` also returns this call's ``GNF4B_ST_*`` bits."""
+    return _launch_host(_gnf4b.FMT_NF4, _gnf4b.OP_FWD, a_host, B, absmax, sizes, expert_ids, B.shape[1], out,
+                        split_k=split_k, path=path, return_status=return_status)
+
+
+def dgrad_4bit_grouped_host(grad_host, B, absmax, sizes, expert_ids, out=None, *, return_status: bool = False):
+    """``dgrad_4bit_grouped`` with host gradients in, host input-gradients out
+    (``gnf4_native/cpu_kernels.c:1374``)."""
+    return _launch_host(_gnf4b.FMT_NF4, _gnf4b.OP_DGRAD, grad_host, B, absmax, sizes, expert_ids, B.shape[2] * 2,
+                        out, return_status=return_status)
 
 
 def dequant_stack_cuda(B, absmax):

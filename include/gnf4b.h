@@ -137,6 +137,76 @@ int gnf4b_gemm_grouped_noalloc(int fmt, int op,
                                int32_t G, int32_t E, int64_t N, int64_t K, int32_t max_rows,
                                void* out, int32_t* status_word, uint32_t flags, void* cuda_stream);
 
+/* The grouped GEMM for a caller whose activations, group tables and result live in HOST memory:
+ * the signature shape of the reference's native CPU entry points
+ *   gnf4_gemv_nf4_grouped    gnf4_native/cpu_kernels.c:751
+ *   gnf4_gemv_mxfp4_grouped  gnf4_native/cpu_kernels.c:1097
+ *   gnf4_dgrad_nf4_grouped   gnf4_native/cpu_kernels.c:1374
+ * (bound through ctypes in gnf4_native/build.py:106-118): host `x`, host `sizes[G]`, host
+ * `expert_ids[G]`, host `out`, one blocking call.  The packed stack W / S stays resident on the
+ * device (uploading it per call would cost more than the GEMM).
+ *
+ *   x_host        [T, K] (FWD) or [T, N] (DGRAD), bf16 or fp16, contiguous; pinned memory makes the
+ *                 copy asynchronous, pageable memory works
+ *   sizes_host    [G] int32 group sizes (zero allowed), sum == T or GNF4B_EINVAL
+ *   expert_ids_host [G] int32, each in [0, E) or GNF4B_PAD_EXPERT, else GNF4B_EINVAL (checked on the
+ *                 host, nothing is launched)
+ *   out_host      bf16 [T, N] (FWD) or [T, K] (DGRAD), all T rows are written; the rows of padding
+ *                 groups receive unspecified values (whatever the staging block held)
+ *   staging       device scratch of at least gnf4b_host_staging_bytes(...) bytes, 256-byte aligned;
+ *                 no initial contents required (the part kernels need zeroed is cleared per call)
+ *   status_host   optional host int32: receives the GNF4B_ST_* bits of THIS call
+ *
+ * What it does on `cuda_stream`: one host-to-device copy of the group tables -- together with `x` when
+ * both fit the 64 KiB pinned block the calling thread keeps, else `x` is copied from where it lies --,
+ * the launch (the exact largest group size is known here, so the planner's choice is exact), the
+ * device-to-host copy of the result, cudaStreamSynchronize.  Not capturable in a CUDA graph (it
+ * synchronises).  The first call of a thread allocates its pinned block (cudaHostAlloc); later calls
+ * allocate nothing.  Measured on a B200 at the decode shape (8 groups of one row, N=1536, K=2048):
+ * 33 us per call, of which the kernel is about 8: the rest is launch, copy-engine and synchronise latency
+ * (replacing the two copies by kernels that read and write mapped host memory measured the same).
+ */
+int gnf4b_gemm_grouped_host(int fmt, int op,
+                            const void* x_host, int x_dtype, int64_t T,
+                            const uint8_t* W, int64_t w_stride_e, int64_t w_stride_n,
+                            const void* S, int s_dtype, int64_t s_stride_e, int64_t s_stride_n,
+                            const int32_t* sizes_host, const int32_t* expert_ids_host,
+                            int32_t G, int32_t E, int64_t N, int64_t K,
+                            void* out_host, void* staging, size_t staging_bytes,
+                            int32_t* status_host, uint32_t flags, void* cuda_stream);
+
+/* Device scratch gnf4b_gemm_grouped_host needs: activations, result, group tables, status word and
+ * the planner's worst-case workspace for these sizes (any routing of T rows over G groups). */
+size_t gnf4b_host_staging_bytes(int fmt, int op, int64_t T, int32_t G, int64_t N, int64_t K, uint32_t flags);
+
+/* One expert FFN per row with host buffers: out = (SiLU(gate) * up) . W_dn[e]^T where
+ * [gate | up] = x . W_gu[e]^T (gate = the first N_gu/2 columns, up = the rest).  The GPU counterpart of the
+ * reference's fused CPU entry point gnf4_gemv_nf4_ffn_grouped (gnf4_native/cpu_kernels.c:947-986): same
+ * operands, host `x`, `sizes`, `expert_ids` and `out`, one blocking call -- here for both weight formats.
+ * On `cuda_stream`: one upload (tables, and x when small), the gate_up grouped GEMM, the SiLU-GLU kernel,
+ * the down grouped GEMM, one download, one synchronise; the [T, N_gu] intermediate never leaves the device.
+ * Results equal gnf4b_gemm_grouped -> gnf4b_silu_glu -> gnf4b_gemm_grouped on the same inputs bit for
+ * bit (both intermediates are rounded to bf16).  x must be bf16.  The clamped, interleaved GLU of gpt-oss
+ * is not this function's activation.
+ *
+ *   W_gu / S_gu   gate_up stack, logical [E, N_gu, K_gu/2] and scales; W_dn / S_dn the down stack,
+ *                 logical [E, N_dn, (N_gu/2)/2]; both device-resident, one scale dtype for both
+ *   out_host      bf16 [T, N_dn]
+ *   staging       device scratch of at least gnf4b_ffn_host_staging_bytes(...) bytes, 256-byte aligned
+ * Everything else as in gnf4b_gemm_grouped_host. */
+int gnf4b_ffn_grouped_host(int fmt, const void* x_host, int x_dtype, int64_t T,
+                           const uint8_t* W_gu, int64_t wgu_stride_e, int64_t wgu_stride_n,
+                           const void* S_gu, int64_t sgu_stride_e, int64_t sgu_stride_n,
+                           const uint8_t* W_dn, int64_t wdn_stride_e, int64_t wdn_stride_n,
+                           const void* S_dn, int64_t sdn_stride_e, int64_t sdn_stride_n, int s_dtype,
+                           const int32_t* sizes_host, const int32_t* expert_ids_host, int32_t G, int32_t E,
+                           int64_t N_gu, int64_t K_gu, int64_t N_dn,
+                           void* out_host, void* staging, size_t staging_bytes,
+                           int32_t* status_host, uint32_t flags, void* cuda_stream);
+
+size_t gnf4b_ffn_host_staging_bytes(int fmt, int64_t T, int32_t G, int64_t N_gu, int64_t K_gu, int64_t N_dn,
+                                    uint32_t flags);
+
 /* Scratch gnf4b_gemm_grouped needs for the same arguments (0 when none).  Replaces the
  * `ws = torch.empty(sk, T, N)` split-K buffer of kernel/nf4_grouped.py:784. */
 size_t gnf4b_workspace_bytes(int fmt, int op, int64_t T, int32_t G, int64_t N, int64_t K,

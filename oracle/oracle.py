@@ -229,6 +229,8 @@ def load_ref():
                        "gnf4_dgrad_nf4_grouped", "gnf4_dgrad_mxfp4_grouped"):
                 getattr(L, fn).restype = C.c_int
                 getattr(L, fn).argtypes = sig
+            L.gnf4_gemv_nf4_ffn_grouped.restype = C.c_int
+            L.gnf4_gemv_nf4_ffn_grouped.argtypes = [vp, vp, vp, vp, vp, vp, vp, C.c_int, i64, i64, i64, vp, C.c_int]
             L.gnf4_pool_start.restype = C.c_int
             L.gnf4_pool_start.argtypes = [C.c_int]
             L.gnf4_pool_stop.restype = None
@@ -260,5 +262,40 @@ def ref_call(kind, fmt, x, W, S, sizes, expert_ids, threads=0):
     return out
 
 
+def ref_ffn_call(x, W_gu, S_gu, W_dn, S_dn, sizes, expert_ids, threads=0):
+    """The reference's fused NF4 expert FFN (gnf4_native/cpu_kernels.c:947-986): x [R,K] fp32 ->
+    (silu(gate) * up) @ W_dn^T, [R, N_dn] fp32, gate/up the two halves of x @ W_gu^T.  sizes >= 1, G <= 512."""
+    L = load_ref()
+    if L is None:
+        raise RuntimeError("oracle/_ref is not built")
+    x, W_gu, S_gu, sizes, eids, E, N_gu, K_gu = _prep("nf4", x, W_gu, S_gu, sizes, expert_ids)
+    W_dn = np.ascontiguousarray(W_dn, np.uint8)
+    S_dn = np.ascontiguousarray(S_dn, np.float32)
+    assert S_gu.dtype == np.float32 and W_dn.shape[2] * 2 == N_gu // 2
+    N_dn = W_dn.shape[1]
+    e64 = eids.astype(np.int64)
+    out = np.empty((x.shape[0], N_dn), np.float32)
+    rc = L.gnf4_gemv_nf4_ffn_grouped(_vp(x), _vp(W_gu), _vp(S_gu), _vp(W_dn), _vp(S_dn), _vp(e64), _vp(sizes),
+                                     len(sizes), N_gu, K_gu, N_dn, _vp(out), threads)
+    if rc:
+        raise ValueError(f"reference FFN kernel rejected the call rc={rc}")
+    return out
+
+
 def host_threads() -> int:
     return len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+
+
+def ffn_grouped_f64(a, W_gu, S_gu, W_dn, S_dn, sizes, expert_ids, fmt="nf4"):
+    """fp64 oracle of the expert FFN (the computation of gnf4_native/cpu_kernels.c:947-986): gate_up GEMM,
+    h = silu(gate) * up over the two halves of its columns, down GEMM; nothing rounded in between."""
+    gu = gemm_grouped_f64(fmt, a, W_gu, S_gu, sizes, expert_ids)
+    H = gu.shape[1] // 2
+    gate, up = gu[:, :H], gu[:, H:]
+    h = gate / (1.0 + np.exp(-gate)) * up
+    # the second GEMM through the same fp64 routine: its input is taken as float32 there, so feed the
+    # high and the residual parts separately and add (exact split of a float64 into two float32)
+    hi = h.astype(np.float32)
+    lo = (h - hi.astype(np.float64)).astype(np.float32)
+    return (gemm_grouped_f64(fmt, hi, W_dn, S_dn, sizes, expert_ids)
+            + gemm_grouped_f64(fmt, lo, W_dn, S_dn, sizes, expert_ids))

@@ -139,3 +139,18 @@ def test_c_abi_rejects_contract_violations_without_a_gpu():
         _gnf4b.check(-2, "x")
     with pytest.raises(RuntimeError):
         _gnf4b.check(-5, "x")
+    # the host-buffer entry point checks its group tables on the host, before any CUDA call:
+    # sizes that do not sum to T, a negative size, an expert id outside the stack
+    def host(sizes, ids, T, E=4):
+        sz = (ctypes.c_int32 * len(sizes))(*sizes)
+        ii = (ctypes.c_int32 * len(ids))(*ids)
+        st = ctypes.c_int32(99)
+        rc = lib.gnf4b_gemm_grouped_host(0, 0, None, 0, T, None, 0, 0, None, 0, 0, 0, ctypes.addressof(sz),
+                                         ctypes.addressof(ii), len(sizes), E, 16, 128, None, None, 0,
+                                         ctypes.addressof(st), 0, None)
+        return rc, st.value
+    assert host([1, 2], [0, 1], 4) == (-1, 0)
+    assert host([-1, 5], [0, 1], 4) == (-1, 0)
+    assert host([2, 2], [0, 4], 4) == (-1, 0)
+    assert host([2, 2], [0, -2], 4) == (-1, 0)
+    assert host([0, 0], [0, -1], 0) == (0, 0)            # nothing to do: OK without touching the device

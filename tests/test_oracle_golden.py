@@ -155,3 +155,18 @@ def test_config1_reference_cpu_path(golden_dir):
     assert np.array_equal(tok.numpy(), g["tok_of_pair"])
     out = O.gemv_grouped_locked("nf4", x[tok].float().numpy(), B.numpy(), A.numpy(), sizes, eids)
     assert np.array_equal(out.view(np.uint32), g["out_cpu_bits"])
+
+
+@pytest.mark.skipif(not O.ref_available(), reason="oracle/_ref not built (no reference checkout)")
+def test_ffn_oracle_brackets_the_compiled_reference_ffn():
+    """The restated expert FFN (fp64) against the reference project's own fused CPU kernel (fp32, its
+    polynomial SiLU): agreement at fp32 accumulation level pins gate/up halves, SiLU-GLU and operand order."""
+    from nf4_pack_ref import make_stack
+    B_gu, A_gu = make_stack(3, 256, 128, seed=51)
+    B_dn, A_dn = make_stack(3, 64, 128, seed=52)
+    rng = np.random.default_rng(5)
+    for sizes, ids in (([1, 1], [2, 0]), ([3, 5, 2], [1, 0, 1])):
+        a = rng.standard_normal((sum(sizes), 128)).astype(np.float32)
+        ref = O.ref_ffn_call(a, B_gu.numpy(), A_gu.numpy(), B_dn.numpy(), A_dn.numpy(), sizes, ids)
+        want = O.ffn_grouped_f64(a, B_gu.numpy(), A_gu.numpy(), B_dn.numpy(), A_dn.numpy(), sizes, ids)
+        assert O.rel_frobenius(ref.astype(np.float64), want) < 2e-5
