@@ -199,7 +199,8 @@ def time_cpu(shape, tokens, steps, warmup, seed, max_rows_per_group=None, budget
     layers = cpu_layers(shape, n_layers, seed)
     st = make_steps(shape, tokens, warmup + steps, seed + 1)
     L.gnf4_pool_start(0)
-    times, scale_note = [], "full workload"
+    times, ffn_times, scale_note = [], [], "full workload"
+    ffn_ok = shape.fmt == "nf4" and shape.gate_up[0] == 2 * shape.down[1]
     try:
         for i, s in enumerate(st):
             sizes, eids = list(s["sizes"]), list(s["eids"])
@@ -220,6 +221,12 @@ def time_cpu(shape, tokens, steps, warmup, seed, max_rows_per_group=None, budget
             dt = time.perf_counter() - t0
             if i >= warmup:
                 times.append(dt * (rows / max(sub_rows, 1)))
+            if ffn_ok and len(sizes) <= 512 and min(sizes) >= 1:
+                # the reference's fused FFN entry point (one call per layer), for the e2e_ffn comparison
+                t0 = time.perf_counter()
+                O.ref_ffn_call(a, Wg, Sg, Wd, Sd, sizes, eids, threads=0)
+                if i >= warmup:
+                    ffn_times.append((time.perf_counter() - t0) * (rows / max(sub_rows, 1)))
             if sub_rows != rows:
                 scale_note = (f"groups cut to <= {max_rows_per_group} rows ({sub_rows} of {rows} rows timed), "
                               f"time extrapolated x rows/rows_timed")
@@ -228,7 +235,8 @@ def time_cpu(shape, tokens, steps, warmup, seed, max_rows_per_group=None, budget
     finally:
         L.gnf4_pool_stop()
     us = statistics.median(times) * 1e6
-    return dict(value=us, unit="us/layer", cores=threads, kind=kind,
+    extra = {"ffn_value": statistics.median(ffn_times) * 1e6} if ffn_times else {}
+    return dict(extra, value=us, unit="us/layer", cores=threads, kind=kind,
                 sample=f"{len(times)} layer passes, tokens={tokens}, {scale_note}; pool of {threads} threads; "
                        f"variant {L.variant}")
 
