@@ -115,8 +115,20 @@ static int make_plan(int fmt, int op, int64_t T, int32_t G, int64_t N, int64_t K
         // grows with the rows of a group); tensor cores beyond that.  Without a host-known
         // maximum the mean T/G decides.
         const double mean_rows = G > 0 ? (double)T / G : 0.0;
-        // (rows longer than 3072 columns are streamed once per row of a group, not per pair: lower crossover)
-        const bool small = (max_rows > 0) ? (max_rows <= 8 && mean_rows <= (K > 3072 ? 1.5 : 2.0)) : (mean_rows <= 1.5);
+        // Crossover in mean rows per group.  The decode kernel streams an expert's weights once per PAIR of
+        // rows at about 2.0 TB/s (1.35 TB/s for rows shorter than 2048 columns); the tensor kernel pays a
+        // fixed MMA-issue cost per (128-row tile, 64-column stage) whatever the rows: 5.6 ns (NF4, two MMAs
+        // per k-step) or 3.85 ns (MXFP4) with all SMs busy.  Measured on B200: Qwen3 gate_up crosses at a
+        // mean of 4.1 rows (model 3.9), Qwen3 down at 2.7 (2.3), gpt-oss gate_up at 2.4 (2.4).  Rows longer
+        // than 3072 columns are streamed once per row, not per pair: fixed 1.5.
+        double cross = 1.5;
+        if (K <= 3072) {
+            const double scale_bytes = (fmt == GNF4B_FMT_NF4) ? (double)(K / 64) * 4.0 : (double)(K / 32);
+            const double t_pass = (double)N * ((double)(K / 2) + scale_bytes) / (K >= 2048 ? 2.0e6 : 1.35e6);   // us
+            const double t_tensor = (double)ceil_div(N, 128) * (double)ceil_div(K, 64) * (fmt == GNF4B_FMT_NF4 ? 5.6e-3 : 3.85e-3);
+            cross = std::min(4.0, std::max(2.0, 2.0 * (t_tensor / t_pass - 0.5)));
+        }
+        const bool small = (max_rows > 0) ? (max_rows <= 8 && mean_rows <= cross) : (mean_rows <= 1.5);
         path = (op == GNF4B_OP_DGRAD) ? GNF4B_PATH_TENSOR : (small ? GNF4B_PATH_STREAM : GNF4B_PATH_TENSOR);
         if (forced_split > 1 && op == GNF4B_OP_FWD) path = GNF4B_PATH_STREAM;
     }

@@ -86,8 +86,10 @@ const char* gnf4b_last_cuda_error(void);
  *   S            scales, logical [E, N, K/64] (NF4) or [E, N, K/32] (MXFP4); ELEMENT strides
  *   group_offsets[G+1] int32, exclusive prefix sum of the group sizes (zero-size groups allowed)
  *   expert_ids   [G] int32, index into the stack handed in (may repeat, any order)
- *   max_rows     largest group size if the host knows it, else <= 0 (path choice only;
- *                results do not depend on it)
+ *   max_rows     largest group size if the host knows it, else <= 0.  Used for the choice of
+ *                kernel only: with it the streaming kernels are taken up to a mean of 2 to 4 rows
+ *                per group (by shape), without it up to 1.5.  The kernels agree to bf16 rounding,
+ *                not to the bit; pin GNF4B_PATH_* where bit-identical results across calls matter
  *   out          bf16 [T, N] (FWD) or [T, K] (DGRAD)
  *   workspace    device scratch of at least gnf4b_workspace_bytes(...) bytes (may be NULL
  *                when that is 0); must be zero-filled once before its first use, the

@@ -18,7 +18,7 @@ What is run, all imported from the reference checkout, nothing re-implemented:
 
 Usage (in a container that has the reference checkout):
     TRITON_INTERPRET=1 CC=/usr/bin/gcc GNF4_NATIVE_CACHE=/tmp/gnf4cache \
-    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py [/root/reference]
+    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py [REFERENCE_CHECKOUT]
 """
 from __future__ import annotations
 
