@@ -24,6 +24,7 @@ from __future__ import annotations
 
 import ctypes
 import os
+import threading
 
 import torch
 
@@ -617,7 +618,8 @@ def dgrad_4bit_grouped(grad_out, B, absmax, sizes, expert_ids, config=None, *, g
 # --------------------------------------------------------------------------- #
 # host-buffer entry points (activations, group tables and result in host memory)
 # --------------------------------------------------------------------------- #
-_HOST_STAGING = {}    # device index -> uint8 CUDA tensor, grown on demand
+_HOST_STAGING = {}    # (device index, thread id) -> uint8 CUDA tensor, grown on demand (a call blocks, so one
+                      # block per calling thread is enough and two threads never share one)
 _HOST_NEED = {}       # (device, fmt, op, T, G, N, K, flags) -> staging bytes
 
 
@@ -698,9 +700,9 @@ def _launch_host(fmt, op, x, W, S, sizes, expert_ids, n_out, out=None, *, split_
             need = lib.gnf4b_host_staging_bytes(*key[1:])
             if len(_HOST_NEED) < 4096:
                 _HOST_NEED[key] = need
-        stage = _HOST_STAGING.get(dev.index)
+        stage = _HOST_STAGING.get((dev.index, threading.get_ident()))
         if stage is None or stage.numel() < need:
-            stage = _HOST_STAGING[dev.index] = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=dev)
+            stage = _HOST_STAGING[(dev.index, threading.get_ident())] = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=dev)
         status = ctypes.c_int32(0) if return_status else None
         rc = lib.gnf4b_gemm_grouped_host(
             fmt, op, x.data_ptr(), xdt, T, W.data_ptr(), W.stride(0), W.stride(1),
@@ -785,9 +787,9 @@ class HostGroupedGemm:
             need = self._lib.gnf4b_host_staging_bytes(self.fmt, self.op, T, G, self.N, self.K, self.flags)
             if len(self._need) < 4096:
                 self._need[(T, G)] = need
-        stage = _HOST_STAGING.get(dev.index)
+        stage = _HOST_STAGING.get((dev.index, threading.get_ident()))
         if stage is None or stage.numel() < need:
-            stage = _HOST_STAGING[dev.index] = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=dev)
+            stage = _HOST_STAGING[(dev.index, threading.get_ident())] = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=dev)
         rc = self._lib.gnf4b_gemm_grouped_host(
             self.fmt, self.op, x.data_ptr(), _gnf4b.X_BF16 if x.dtype is torch.bfloat16 else _gnf4b.X_FP16, T,
             *self._w, *self._s, sizes_i32.data_ptr(), ids_i32.data_ptr(), G, self.E, self.N, self.K,
@@ -844,9 +846,9 @@ class HostGroupedFfn:
             need = self._lib.gnf4b_ffn_host_staging_bytes(gu.fmt, T, G, gu.N, gu.K, dn.N, self.flags)
             if len(self._need) < 4096:
                 self._need[(T, G)] = need
-        stage = _HOST_STAGING.get(dev.index)
+        stage = _HOST_STAGING.get((dev.index, threading.get_ident()))
         if stage is None or stage.numel() < need:
-            stage = _HOST_STAGING[dev.index] = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=dev)
+            stage = _HOST_STAGING[(dev.index, threading.get_ident())] = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=dev)
         rc = self._lib.gnf4b_ffn_grouped_host(
             gu.fmt, x.data_ptr(), _gnf4b.X_BF16, T, *gu._w, gu._s[0], gu._s[2], gu._s[3],
             *dn._w, dn._s[0], dn._s[2], dn._s[3], gu.sdt, sizes_i32.data_ptr(), ids_i32.data_ptr(), G, gu.E,
