@@ -160,3 +160,17 @@ def test_bound_host_ffn_reuse_and_errors():
         ffn(a, torch.tensor([1, 2], dtype=torch.int32), ids, out)
     with pytest.raises(ValueError):
         nf4_grouped.HostGroupedFfn(B_gu, A_gu, B_gu, A_gu)            # down does not contract over H
+
+
+def test_host_entry_with_more_groups_than_the_pinned_block_holds():
+    """20000 groups (tables of 160 KB: beyond the thread's pinned block, copied from a heap array), most of one row,
+    some empty: same bits as the tensor entry point on the same kernel."""
+    B, A = make_stack(4, 64, 64, seed=13, device=DEV)
+    gen = torch.Generator().manual_seed(3)
+    sizes = (torch.rand(20000, generator=gen) < 0.9).to(torch.int32)
+    ids = torch.randint(0, 4, (20000,), generator=gen, dtype=torch.int32)
+    T = int(sizes.sum())
+    a = torch.randn(T, 64, generator=gen).to(torch.bfloat16)
+    got, status = nf4_grouped.gemm_4bit_grouped_host(a, B, A, sizes, ids, path=_gnf4b.PATH_STREAM, return_status=True)
+    want = nf4_grouped.gemm_4bit_grouped(a.to(DEV), B, A, sizes.tolist(), ids.tolist(), path=_gnf4b.PATH_STREAM).cpu()
+    assert status == 0 and torch.equal(got, want)
