@@ -30,7 +30,11 @@ namespace gnf4b {
 
 // consumer warps: sixteen while a lane's share of the activation rows is small (one row, K <= 3072), fewer
 // when it needs the registers (two rows: 8 warps; one row of up to 7168 columns: 6 warps)
-__host__ __device__ constexpr int decode_consumer_warps(int rm, int au) { return au > 3 ? 6 : (rm == 1 ? 16 : 8); }
+// (two rows per pass: 12 warps while a row's activations fit 32 registers per row (AU <= 2: 128 registers per
+// thread, no spills; the 8-warp form was issue-bound at 14 % warp occupancy), 8 warps at AU = 3)
+__host__ __device__ constexpr int decode_consumer_warps(int rm, int au) {
+    return au > 3 ? 6 : (rm == 1 ? 16 : (au <= 2 ? 12 : 8));
+}
 __host__ __device__ constexpr int decode_threads(int rm, int au) { return (decode_consumer_warps(rm, au) + 1) * 32; }
 constexpr int kDMaxStages = 8;
 

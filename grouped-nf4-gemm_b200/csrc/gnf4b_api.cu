@@ -116,15 +116,15 @@ static int make_plan(int fmt, int op, int64_t T, int32_t G, int64_t N, int64_t K
         // maximum the mean T/G decides.
         const double mean_rows = G > 0 ? (double)T / G : 0.0;
         // Crossover in mean rows per group.  The decode kernel streams an expert's weights once per PAIR of
-        // rows at about 2.0 TB/s (1.35 TB/s for rows shorter than 2048 columns); the tensor kernel pays a
+        // rows at about 2.0 TB/s (1.6 TB/s for rows shorter than 2048 columns); the tensor kernel pays a
         // fixed MMA-issue cost per (128-row tile, 64-column stage) whatever the rows: 5.6 ns (NF4, two MMAs
         // per k-step) or 3.85 ns (MXFP4) with all SMs busy.  Measured on B200: Qwen3 gate_up crosses at a
-        // mean of 4.1 rows (model 3.9), Qwen3 down at 2.7 (2.3), gpt-oss gate_up at 2.4 (2.4).  Rows longer
+        // mean of 4.3 rows (model 3.9), Qwen3 down at 3.2 (3.1), gpt-oss gate_up at 2.4 (2.5).  Rows longer
         // than 3072 columns are streamed once per row, not per pair: fixed 1.5.
         double cross = 1.5;
         if (K <= 3072) {
             const double scale_bytes = (fmt == GNF4B_FMT_NF4) ? (double)(K / 64) * 4.0 : (double)(K / 32);
-            const double t_pass = (double)N * ((double)(K / 2) + scale_bytes) / (K >= 2048 ? 2.0e6 : 1.35e6);   // us
+            const double t_pass = (double)N * ((double)(K / 2) + scale_bytes) / (K >= 2048 ? 2.0e6 : 1.6e6);   // us
             const double t_tensor = (double)ceil_div(N, 128) * (double)ceil_div(K, 64) * (fmt == GNF4B_FMT_NF4 ? 5.6e-3 : 3.85e-3);
             cross = std::min(4.0, std::max(2.0, 2.0 * (t_tensor / t_pass - 0.5)));
         }
@@ -428,8 +428,10 @@ int gnf4b_gemm_grouped(int fmt, int op, const void* x, int x_dtype, int64_t T, c
             // few rows as possible (items are dealt out whole: with 768 items on 148 CTAs some CTAs would
             // stream 6 tiles and others 5); a small per-item charge keeps the stages from getting tiny
             const int m = (int)std::max<int64_t>(1, std::min<int64_t>(4, 32768 / (kDConsumerWarps * row_bytes)));
-            const int r_hi = kDConsumerWarps * m;
+            // a stage's scale span must stay 16-byte aligned: rows per stage in multiples of 4 when four scale
+            // rows are, else of 8 (`contiguous` guarantees eight are); the upper end is rounded down to that
             const int r_step = ((4 * srow) % 16 == 0) ? 4 : 8;
+            const int r_hi = std::max(r_step, (kDConsumerWarps * m / r_step) * r_step);
             const int64_t groups_eff = std::max<int64_t>(1, std::min<int64_t>((int64_t)G * ((max_rows + rm - 1) / rm), T));
             int best_r = r_hi;
             int64_t best_cost = INT64_MAX;

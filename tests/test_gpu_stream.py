@@ -485,3 +485,22 @@ def test_padding_groups_are_skipped_silently(path, carrier):
     assert torch.all(poison[2:5] == 7.0) and torch.all(poison[6:10] == 7.0)
     assert torch.equal(poison[0:2], out[0:2]) and torch.equal(poison[10:12], out[10:12])
     assert nf4_grouped.last_status(DEV) == 0
+
+
+@pytest.mark.parametrize("K", [1984, 2880])
+def test_two_row_decode_keeps_stage_scale_spans_16_byte_aligned(K):
+    """MXFP4 rows whose scale row is not a multiple of 4 bytes (K = 1984: 62, K = 2880: 90): four scale rows are
+    not 16-byte aligned, eight are, so the rows of a stage must come in multiples of 8 whatever the number of
+    consumer warps.  Groups of 1-3 rows take the two-rows-per-pass decode kernel; same bits as the general
+    streaming kernel (device-side sizes), and the oracle's tolerance."""
+    E, N = 3, 64
+    gen = torch.Generator().manual_seed(17)
+    B, S = synth.mxfp4_stack(E, N, K, gen, device=DEV, fast=True)
+    sizes, ids = [2, 3, 1, 2], [1, 0, 2, 1]
+    a = torch.randn(sum(sizes), K, generator=gen).to(torch.bfloat16).to(DEV)
+    out = mxfp4_grouped.gemm_mxfp4_grouped(a, B, S, sizes, ids, path=_gnf4b.PATH_STREAM)
+    general = mxfp4_grouped.gemm_mxfp4_grouped(a, B, S, torch.tensor(sizes, device=DEV), torch.tensor(ids, device=DEV),
+                                               path=_gnf4b.PATH_STREAM)
+    assert torch.equal(out, general)
+    assert rel_fro(out, oracle_fwd64("mxfp4", a, B, S, sizes, ids)) <= REL_FRO_TOL
+    assert nf4_grouped.last_status(DEV) == 0
