@@ -136,6 +136,9 @@ __device__ __forceinline__ DGroup decode_group(const DecodeArgs& a, int g, int c
     const bool pad = eid == GNF4B_PAD_EXPERT;        // padding group: skipped, not an error
     if (((bad_e && !pad) || bad_o) && end != row0 && c == 0 && a.g.status && (threadIdx.x & 31) == 0)
         atomicOr(a.g.status, (bad_e && !pad) ? GNF4B_ST_BAD_EXPERT : GNF4B_ST_BAD_OFFSETS);
+    // a group with more rows than the caller's max_rows promised: the rows beyond are not visited
+    if (d.valid && c == 0 && end - row0 > a.row_chunks * a.rows_per_pass && a.g.status && (threadIdx.x & 31) == 0)
+        atomicOr(a.g.status, GNF4B_ST_BAD_OFFSETS);
     return d;
 }
 

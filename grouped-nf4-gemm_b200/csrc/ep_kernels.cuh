@@ -92,7 +92,8 @@ namespace gnf4b {
 // every (token, choice) pair in the send buffer -- destination rank d = expert / experts_per_rank gets
 // rows [d * cap, d * cap + ...) ordered by local expert, pairs of one expert in pair order -- and the
 // copy of the pairs' hidden rows into those slots.  P = tokens * top_k <= 1024, n_experts <= 1024.
-// A pair whose expert id is out of range gets slot -1, is not sent and is flagged.
+// A pair whose expert id is out of range gets slot -1, is not sent and is flagged (GNF4B_ST_BAD_EXPERT);
+// so does a pair beyond the cap rows of its destination rank (GNF4B_ST_BAD_OFFSETS).
 constexpr int kEpPlanThreads = 256;
 constexpr int kEpPlanMax = 1024;
 
@@ -128,7 +129,10 @@ ep_plan_kernel(const int64_t* __restrict__ idx, int32_t P, int32_t k, int32_t n_
         if (e >= 0) {
             int32_t rank = 0;
             for (int q = 0; q < p; ++q) rank += (s_e[q] == e);
-            s = (int64_t)(e / e_local) * cap + s_base[e] + rank;
+            // a destination rank that would get more than cap pairs: the pair is not sent and the call is
+            // flagged, never written into the next rank's block (or past the end of send)
+            if (s_base[e] + rank < cap) s = (int64_t)(e / e_local) * cap + s_base[e] + rank;
+            else if (status) atomicOr(status, GNF4B_ST_BAD_OFFSETS);
         }
         s_slot[p] = s;
         slot[p] = s;

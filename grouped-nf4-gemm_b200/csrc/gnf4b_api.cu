@@ -105,7 +105,10 @@ static int check_shape(int fmt, int op, int x_dtype, int s_dtype, int64_t T, int
     return GNF4B_OK;
 }
 
-static int make_plan(int fmt, int op, int64_t T, int32_t G, int64_t N, int64_t K, int32_t max_rows,
+// x_dtype < 0: not known (sizing calls).  The tensor kernels multiply bf16 x bf16: when the planner would
+// pick them for fp16 activations it picks the streaming kernel instead, so the plan made here is the plan
+// that launches and its scratch sizes are the ones the launch uses.
+static int make_plan(int fmt, int op, int x_dtype, int64_t T, int32_t G, int64_t N, int64_t K, int32_t max_rows,
                      uint32_t flags, const DevInfo& di, Plan* p) {
     const uint32_t want = flags & GNF4B_PATH_MASK;
     const int forced_split = (int)((flags & GNF4B_SPLITK_MASK) >> GNF4B_SPLITK_SHIFT);
@@ -131,6 +134,7 @@ static int make_plan(int fmt, int op, int64_t T, int32_t G, int64_t N, int64_t K
         const bool small = (max_rows > 0) ? (max_rows <= 8 && mean_rows <= cross) : (mean_rows <= 1.5);
         path = (op == GNF4B_OP_DGRAD) ? GNF4B_PATH_TENSOR : (small ? GNF4B_PATH_STREAM : GNF4B_PATH_TENSOR);
         if (forced_split > 1 && op == GNF4B_OP_FWD) path = GNF4B_PATH_STREAM;
+        if (x_dtype == GNF4B_X_FP16 && op == GNF4B_OP_FWD) path = GNF4B_PATH_STREAM;
     }
     if (path == GNF4B_PATH_STREAM && op == GNF4B_OP_DGRAD) return GNF4B_EUNSUPPORTED;
     p->path = path;
@@ -333,9 +337,14 @@ size_t gnf4b_workspace_bytes(int fmt, int op, int64_t T, int32_t G, int64_t N, i
                              int32_t max_rows, uint32_t flags) {
     DevInfo di;
     if (device_info(&di)) return 0;
-    Plan p;
-    if (make_plan(fmt, op, T, G, N, K, max_rows, flags, di, &p)) return 0;
-    return p.counters_bytes + p.ws_bytes;
+    // the call does not say which activation dtype will come: the larger of the two plans' needs
+    size_t need = 0;
+    for (int xdt : {GNF4B_X_BF16, GNF4B_X_FP16}) {
+        Plan p;
+        if (make_plan(fmt, op, xdt, T, G, N, K, max_rows, flags, di, &p) == GNF4B_OK)
+            need = std::max(need, p.counters_bytes + p.ws_bytes);
+    }
+    return need;
 }
 
 int gnf4b_plan_split_k(int fmt, int op, int64_t T, int32_t G, int64_t N, int64_t K, int32_t max_rows,
@@ -344,7 +353,7 @@ int gnf4b_plan_split_k(int fmt, int op, int64_t T, int32_t G, int64_t N, int64_t
     int rc = device_info(&di);
     if (rc) return rc;
     Plan p;
-    rc = make_plan(fmt, op, T, G, N, K, max_rows, flags, di, &p);
+    rc = make_plan(fmt, op, GNF4B_X_BF16, T, G, N, K, max_rows, flags, di, &p);
     if (rc) return rc;
     return p.path == GNF4B_PATH_STREAM ? p.split_k : 1;
 }
@@ -365,7 +374,7 @@ int gnf4b_gemm_grouped(int fmt, int op, const void* x, int x_dtype, int64_t T, c
     rc = device_info(&di);
     if (rc) return rc;
     Plan p;
-    rc = make_plan(fmt, op, T, G, N, K, max_rows, flags, di, &p);
+    rc = make_plan(fmt, op, x_dtype, T, G, N, K, max_rows, flags, di, &p);
     if (rc) return rc;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(cuda_stream);
 
@@ -386,12 +395,15 @@ int gnf4b_gemm_grouped(int fmt, int op, const void* x, int x_dtype, int64_t T, c
             rc = launch_tensor(fmt, op, s_dtype, g, max_rows, di.sm_count, di.smem_optin,
                                align_class(W, w_stride_e, w_stride_n), st);
         if (rc == GNF4B_ECUDA) return cuda_fail(cudaGetLastError(), "tensor kernel launch");
-        // A forward the tensor kernel declines (e.g. fp16 activations) still has a CUDA
-        // kernel that takes it when the caller left the choice to the planner.
+        // A forward the tensor kernels decline for a reason the planner cannot see (no tensor-map encoder
+        // in this driver, not enough shared memory) still has a CUDA kernel that takes it when the caller
+        // left the choice to the planner.  Callers sized and cleared their scratch for the plan above, which
+        // had none, so this second plan runs without split-K: it needs no scratch at all.
         const bool may_stream = rc == GNF4B_EUNSUPPORTED && op == GNF4B_OP_FWD &&
                                 (flags & GNF4B_PATH_MASK) == GNF4B_PATH_AUTO;
         if (!may_stream) return rc;
-        rc = make_plan(fmt, op, T, G, N, K, max_rows, (flags & ~GNF4B_PATH_MASK) | GNF4B_PATH_STREAM, di, &p);
+        const uint32_t f2 = (flags & ~(GNF4B_PATH_MASK | GNF4B_SPLITK_MASK)) | GNF4B_PATH_STREAM | (1u << GNF4B_SPLITK_SHIFT);
+        rc = make_plan(fmt, op, x_dtype, T, G, N, K, max_rows, f2, di, &p);
         if (rc) return rc;
     }
 
@@ -509,7 +521,7 @@ int gnf4b_gemm_grouped_noalloc(int fmt, int op, const void* x, int x_dtype, int6
     rc = device_info(&di);
     if (rc) return rc;
     Plan p;
-    rc = make_plan(fmt, op, T, G, N, K, max_rows, flags, di, &p);
+    rc = make_plan(fmt, op, x_dtype, T, G, N, K, max_rows, flags, di, &p);      // the plan that will launch
     if (rc) return rc;
     const size_t need = p.counters_bytes + p.ws_bytes;
     if (need > (size_t)GNF4B_NOALLOC_SCRATCH_BYTES) return GNF4B_ETOOBIG;
@@ -538,12 +550,14 @@ struct HostStaging {
 static int host_staging_layout(int fmt, int op, int64_t T, int32_t G, int64_t N, int64_t K, uint32_t flags,
                                const DevInfo& di, HostStaging* h) {
     size_t worst = 0;
-    const int32_t probes[2] = {1, -1};      // scratch exists only on the streaming path: both path choices
-    for (int32_t mr : probes) {
-        Plan p;
-        const int rc = make_plan(fmt, op, T, G, N, K, mr, flags, di, &p);
-        if (rc == GNF4B_OK) worst = std::max(worst, p.counters_bytes + p.ws_bytes);
-        else if (rc != GNF4B_EUNSUPPORTED) return rc;
+    const int32_t probes[2] = {1, -1};      // scratch exists only on the streaming path: both path choices,
+    for (int32_t mr : probes) {             // and both activation dtypes (fp16 always streams)
+        for (int xdt : {GNF4B_X_BF16, GNF4B_X_FP16}) {
+            Plan p;
+            const int rc = make_plan(fmt, op, xdt, T, G, N, K, mr, flags, di, &p);
+            if (rc == GNF4B_OK) worst = std::max(worst, p.counters_bytes + p.ws_bytes);
+            else if (rc != GNF4B_EUNSUPPORTED) return rc;
+        }
     }
     const int64_t in_cols = (op == GNF4B_OP_FWD) ? K : N, out_cols = (op == GNF4B_OP_FWD) ? N : K;
     h->ws_bytes = worst;
@@ -608,7 +622,7 @@ int gnf4b_gemm_grouped_host(int fmt, int op, const void* x_host, int x_dtype, in
     if (rc) return rc;
     if (staging_bytes < h.total) return GNF4B_EWORKSPACE;
     Plan p;
-    rc = make_plan(fmt, op, T, G, N, K, max_rows, flags, di, &p);
+    rc = make_plan(fmt, op, x_dtype, T, G, N, K, max_rows, flags, di, &p);      // the plan that will launch
     if (rc) return rc;
 
     cudaStream_t st = reinterpret_cast<cudaStream_t>(cuda_stream);
@@ -744,9 +758,9 @@ int gnf4b_ffn_grouped_host(int fmt, const void* x_host, int x_dtype, int64_t T,
     if (staging_bytes < f.total) return GNF4B_EWORKSPACE;
     const int64_t H = N_gu / 2;
     Plan p_gu, p_dn;
-    rc = make_plan(fmt, GNF4B_OP_FWD, T, G, N_gu, K_gu, max_rows, flags, di, &p_gu);
+    rc = make_plan(fmt, GNF4B_OP_FWD, x_dtype, T, G, N_gu, K_gu, max_rows, flags, di, &p_gu);
     if (rc) return rc;
-    rc = make_plan(fmt, GNF4B_OP_FWD, T, G, N_dn, H, max_rows, flags, di, &p_dn);
+    rc = make_plan(fmt, GNF4B_OP_FWD, x_dtype, T, G, N_dn, H, max_rows, flags, di, &p_dn);
     if (rc) return rc;
 
     cudaStream_t st = reinterpret_cast<cudaStream_t>(cuda_stream);

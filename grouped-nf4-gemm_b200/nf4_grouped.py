@@ -576,7 +576,8 @@ def gemm_4bit_grouped(a_cat, B, absmax, sizes, expert_ids, block_m: int | None =
 
 
 def dgrad_eligible(grad_out, B, absmax, block_k: int = 64):
-    """None if ``dgrad_4bit_grouped`` can take this problem, else the reason (ref :1034-1053)."""
+    """None if ``dgrad_4bit_grouped`` can take this problem, else the reason (ref :1034-1053; restated
+    from there, message strings included, plus one rule of this kernel: N % 8 == 0)."""
     if grad_out.dtype != torch.bfloat16:
         return f"grad_out dtype {grad_out.dtype} is not bfloat16"
     if BLOCKSIZE % block_k:
@@ -588,6 +589,10 @@ def dgrad_eligible(grad_out, B, absmax, block_k: int = 64):
         return f"absmax blocks {absmax.shape[2]} do not tile K {K} at blocksize {BLOCKSIZE}"
     if B.numel() == 0:
         return "packed storage is empty (evicted?)"
+    if B.shape[1] % 8:
+        # not a rule of the reference: the sm_100a kernel fetches grad_out [T, N] by TMA, whose row
+        # pitch (2 N bytes) must be a multiple of 16 bytes
+        return f"N {B.shape[1]} is not a multiple of 8 (grad_out rows are fetched by TMA: 16-byte row pitch)"
     return None
 
 

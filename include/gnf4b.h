@@ -86,10 +86,12 @@ const char* gnf4b_last_cuda_error(void);
  *   S            scales, logical [E, N, K/64] (NF4) or [E, N, K/32] (MXFP4); ELEMENT strides
  *   group_offsets[G+1] int32, exclusive prefix sum of the group sizes (zero-size groups allowed)
  *   expert_ids   [G] int32, index into the stack handed in (may repeat, any order)
- *   max_rows     largest group size if the host knows it, else <= 0.  Used for the choice of
- *                kernel only: with it the streaming kernels are taken up to a mean of 2 to 4 rows
- *                per group (by shape), without it up to 1.5.  The kernels agree to bf16 rounding,
- *                not to the bit; pin GNF4B_PATH_* where bit-identical results across calls matter
+ *   max_rows     largest group size if the host knows it, else <= 0.  Steers the choice of kernel:
+ *                with it the streaming kernels are taken up to a mean of 2 to 4 rows per group (by
+ *                shape), without it up to 1.5.  It must not be understated: the decode kernel visits
+ *                max_rows rows of a group, rows beyond that are NOT computed and the call raises
+ *                GNF4B_ST_BAD_OFFSETS.  The kernels agree to bf16 rounding, not to the bit; pin
+ *                GNF4B_PATH_* where bit-identical results across calls matter
  *   out          bf16 [T, N] (FWD) or [T, K] (DGRAD)
  *   workspace    device scratch of at least gnf4b_workspace_bytes(...) bytes (may be NULL
  *                when that is 0); must be zero-filled once before its first use, the
@@ -267,7 +269,8 @@ int gnf4b_route_topk(const float* logits, int64_t T, int32_t E, int32_t k, int32
  * (int32 pairs per expert), slot[P] (int64 row of pair p in the send buffer: rank d = expert / e_local owns
  * rows [d * cap, (d + 1) * cap), ordered by local expert, pairs of one expert in pair order; -1 and
  * GNF4B_ST_BAD_EXPERT for an id outside [0, n_experts)), and the copy of the pairs' hidden rows (bf16
- * [tokens, H]) into send (bf16 [world * cap, H]).
+ * [tokens, H]) into send (bf16 [world * cap, H]).  cap >= the pairs any one rank can receive (cap = P is always
+ * enough); a pair that does not fit its rank's cap rows gets slot -1, is not sent, and GNF4B_ST_BAD_OFFSETS is raised.
  *
  * gnf4b_ep_offsets: recv_counts[world, e_local] -> offsets[world * (e_local + 1) + 1] of the received buffer:
  * per source rank its e_local expert blocks, then the unused capacity as one group (to be given
