@@ -261,13 +261,16 @@ def run_gpu(args, shape, rank, world):
                            max_rows=max(s["sizes"]) if s["sizes"] else 0))
     torch.cuda.synchronize()
 
+    # the group tables of every step were uploaded during set-up: no kernel of the timed region writes them
+    kw = dict(tables_ready=True, path=args.path)
+
     def layer_resident(i, what="both"):
         (gu, dn), d = layers[i % args.layers], dsteps[i]
         o = None
         if what in ("both", "gate_up"):
-            o = fn(d["a"], gu[0], gu[1], None, d["eids"], group_offsets=d["off"], max_rows=d["max_rows"])
+            o = fn(d["a"], gu[0], gu[1], None, d["eids"], group_offsets=d["off"], max_rows=d["max_rows"], **kw)
         if what in ("both", "down"):
-            o = fn(d["h"], dn[0], dn[1], None, d["eids"], group_offsets=d["off"], max_rows=d["max_rows"])
+            o = fn(d["h"], dn[0], dn[1], None, d["eids"], group_offsets=d["off"], max_rows=d["max_rows"], **kw)
         return o
 
     host_out = {}          # pinned landing buffers for the result, by shape (a fresh pageable one per step
@@ -479,6 +482,8 @@ def main():
     ap.add_argument("--layers", type=int, default=16)
     ap.add_argument("--repeats", type=int, default=7)
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--path", type=lambda v: int(v, 0), default=0,
+                    help="kernel choice / ablation flags of the device-resident timed region (0 = the planner)")
     ap.add_argument("--random-bytes", action="store_true",
                     help="NF4 stacks from uniform random bytes (few set-up kernels; for profiler captures)")
     args = ap.parse_args()

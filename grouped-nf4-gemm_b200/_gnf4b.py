@@ -30,6 +30,8 @@ PATH_AUTO, PATH_STREAM, PATH_TENSOR = 0, 1, 2
 SPLITK_SHIFT = 8
 FLAG_CTA_PAIR = 0x20000           # forward tensor kernel as CTA pairs (cta_group::2) instead of single CTAs
 FLAG_SMEM_OPERANDS = 0x10000      # ablation: forward on the kernel with both MMA operands in shared memory
+FLAG_TABLES_READY = 0x40000       # the group tables were not written by the kernel launched just before
+FLAG_DECODE_ONE_ROW = 0x80000     # ablation: decode kernel with one weight row per warp in flight, not two
 ST_BAD_EXPERT, ST_BAD_OFFSETS, ST_TIMEOUT = 1, 2, 4
 NOALLOC_SCRATCH_BYTES = 8 << 20
 

@@ -36,6 +36,25 @@ __device__ __forceinline__ float2 byte_pair(uint32_t b) {
     return make_float2(2.0f * kFp4Lut[b & 15], 2.0f * kFp4Lut[b >> 4]);
 }
 
+// The same pair with the codebook values taken from instruction immediates (a select chain) instead of constant
+// memory: a kernel that decodes only while it builds a lookup table would otherwise start with a constant-cache
+// miss (about a microsecond before its first table row is written).  MXFP4 doubled as above.
+template <int FMT>
+__device__ __forceinline__ float code_value_imm(uint32_t c) {
+    constexpr uint32_t nf4[16] = {0xbf800000u, 0xbf3239b1u, 0xbf066b30u, 0xbeca32a0u, 0xbe91a24du, 0xbe3d353fu, 0xbdba7871u, 0x0u,
+                                  0x3da2faffu, 0x3e24cae3u, 0x3e7c04ddu, 0x3ead033au, 0x3ee1a4b8u, 0x3f1007abu, 0x3f3913b3u, 0x3f800000u};
+    if (FMT == GNF4B_FMT_NF4) {
+        uint32_t v = nf4[15];
+#pragma unroll
+        for (int i = 14; i >= 0; --i) v = (c == (uint32_t)i) ? nf4[i] : v;
+        return __uint_as_float(v);
+    }
+    // doubled e2m1 magnitudes 0, 1, 2, 3, 4, 6, 8, 12: small integers, exact in every float format
+    const uint32_t m = c & 7u;
+    const uint32_t v = __float_as_uint((float)(m < 4u ? m : (2u + (m & 1u)) << ((m >> 1) - 1u)));
+    return __uint_as_float(v | ((c & 8u) << 28));
+}
+
 __device__ __forceinline__ float bf16_bits_to_float(uint32_t h) { return __uint_as_float(h << 16); }
 
 // One block scale as fp32.  NF4: the absmax itself (bf16 widened exactly).  MXFP4:
@@ -64,6 +83,12 @@ __device__ __forceinline__ void fence_proxy_async() {
 }
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Arrive without ordering earlier memory operations.  For "this warp has finished READING a ring stage": the
+// reads have completed when their values were used, and a release arrive would also wait for the
+// acknowledgement of every global store the thread issued before it (half a microsecond per output row).
+__device__ __forceinline__ void mbar_arrive_relaxed(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.relaxed.cta.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),

@@ -9,15 +9,18 @@
 // (TMA engine) issued by a single producer lane -- no per-row copies, no register-staged
 // scale loads -- and the stage index is a closed-form function of the item index.
 //
-//   warp 16      producer: two lanes walk this CTA's contiguous item range and issue, per
-//                item, cp.async.bulk(weights) + cp.async.bulk(raw scales) on full[stage]
-//   warps 0..15  consumers: warp w owns rows w, w + 16, ... of the stage; a lane owns the
-//                16-byte units lane, lane + 32, ... of a row, decodes through the
-//                conflict-free byte-pair table, FMAs against the activation row it keeps in
-//                registers as bf16 pairs, applies the block scale once per unit, warp-shuffle
-//                reduces.  Sixteen warps because the loop is latency-bound, not issue-bound.
-//                RM > 1: eight consumer warps (the RM activation rows need RM x 32 registers per
-//                1024 columns); the table lookups of a unit are shared by the group's rows.
+//   last warp      producer: two lanes walk this CTA's contiguous item range and issue, per
+//                  item, cp.async.bulk(weights) + cp.async.bulk(raw scales) on full[stage]
+//   warps 0..CW-1  consumers: warp w owns rows w, w + CW, ... of the stage, RW of them in flight at a
+//                  time; a lane owns the 16-byte units lane, lane + 32, ... of a row, decodes through a
+//                  conflict-free lookup table indexed by the packed byte, FMAs against the activation row
+//                  it keeps in registers, applies the block scale once per unit, warp-shuffle reduces.
+//
+// What bounds it (measured on B200 with the consumer loop alone, weights already in shared memory): every
+// element costs one table read of 4 bytes (fp32 codebook value) through the 128 B/clk shared-memory pipe, so
+// NF4 tops out at about 23 weight rows of 2048 elements per microsecond and SM, 3.9 TB/s of packed bytes
+// chip-wide, before HBM does.  MXFP4 values are exact in bf16: 2 bytes per element and the mixed-precision FMA
+// take it to 5.5 TB/s.
 //
 // Summation order per output element is the same as in stream_kernel.cuh, so both kernels
 // give bit-identical results.
@@ -29,14 +32,18 @@
 namespace gnf4b {
 
 // consumer warps: sixteen while a lane's share of the activation rows is small (one row, K <= 3072), fewer
-// when it needs the registers (two rows: 8 warps; one row of up to 7168 columns: 6 warps)
-// (two rows per pass: 12 warps while a row's activations fit 32 registers per row (AU <= 2: 128 registers per
-// thread, no spills; the 8-warp form was issue-bound at 14 % warp occupancy), 8 warps at AU = 3)
+// when it needs the registers (one row of up to 7168 columns: 6 warps; two rows per pass: 12 warps while a
+// row's activations fit 32 registers per row (AU <= 2), 8 warps at AU = 3)
 __host__ __device__ constexpr int decode_consumer_warps(int rm, int au) {
     return au > 3 ? 6 : (rm == 1 ? 16 : (au <= 2 ? 12 : 8));
 }
 __host__ __device__ constexpr int decode_threads(int rm, int au) { return (decode_consumer_warps(rm, au) + 1) * 32; }
 constexpr int kDMaxStages = 8;
+
+// The lookup table sits at a FIXED address of the CTA's shared-memory window (dynamic shared memory
+// starts below it: the kernel checks), so the address of a lookup is one PRMT -- (byte << 8) | lane * 8
+// -- plus the load's immediate offset: two instructions per packed byte, no address arithmetic.
+constexpr int kDTabAbs = 2048;
 
 struct DecodeArgs {
     GemmArgs g;
@@ -53,49 +60,93 @@ struct DecodeArgs {
     int32_t row_chunks;         // a group's rows are taken rows_per_pass at a time: ceil(max_rows / rows_per_pass)
     int32_t rows_per_pass;      // RM of the kernel instance
     int32_t compact;            // work list holds only (group, chunk) pairs that exist (prefix sum in shared memory)
+    int32_t tables_ready;       // group_offsets / expert_ids were NOT written by the kernel launched just before
 };
 
+
+// Dynamic shared memory: [slack up to kDTabAbs][table 64 KiB][ring][barriers, abort flag: 256 B][group prefix]
 __host__ __device__ inline size_t decode_smem_bytes(int slot_bytes, int stages, int g_cache) {
-    return (size_t)kSTableBytes + (size_t)stages * slot_bytes + 256 + (size_t)(2 * g_cache + 1) * 4;
+    return (size_t)kDTabAbs + (size_t)kSTableBytes + (size_t)stages * slot_bytes + 256 + (size_t)(2 * g_cache + 1) * 4;
 }
 
-// One unit (16 packed bytes = 32 elements) against the activation row kept in registers as
-// 16 bf16 pairs (widened on use: a bf16 is the top half of its fp32).  Same four partial
-// sums and the same order as unit_dot_regs of the streaming kernel, so the bits agree.
-__device__ __forceinline__ float2 ld_table(uint32_t addr) {
+// (byte B of w) << 8 | lane8, with lane8 = lane * 8 < 256
+template <int B>
+__device__ __forceinline__ uint32_t tab_index(uint32_t w, uint32_t lane8) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(w), "r"(lane8), "n"(0x7604 | (B << 4)));
+    return d;
+}
+__device__ __forceinline__ float2 ld_table(uint32_t idx) {
     // the pair table is written once before the consumers' barrier and never again, so this
     // load may be scheduled freely (no volatile, no memory clobber)
     float2 v;
-    asm("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+    asm("ld.shared.v2.f32 {%0, %1}, [%2 + %3];" : "=f"(v.x), "=f"(v.y) : "r"(idx), "n"(kDTabAbs));
     return v;
 }
 
-__device__ __forceinline__ void unit_lookup(const uint4 wv, uint32_t tab_lane, float2* p) {
-    const uint32_t words[4] = {wv.x, wv.y, wv.z, wv.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int b = 0; b < 4; ++b) p[i * 4 + b] = ld_table(tab_lane + prmt(words[i], 0u, 0x4404u | (b << 4)));
+__device__ __forceinline__ uint32_t ld_table_b32(uint32_t idx) {
+    uint32_t v;
+    asm("ld.shared.u32 %0, [%1 + %2];" : "=r"(v) : "r"(idx), "n"(kDTabAbs));
+    return v;
+}
+// acc += w.lo * x.lo, then acc += w.hi * x.hi, w and x pairs of bf16: the mixed-precision FMA of sm_100 (bf16
+// operands, fp32 addend and result, one rounding), i.e. exactly fmaf() on the widened values.
+__device__ __forceinline__ void fma_bf16_pair(float& acc, uint32_t w, uint32_t x) {
+    asm("{ .reg .b16 wl, wh, xl, xh;\n\t"
+        "mov.b32 {wl, wh}, %1;\n\t"
+        "mov.b32 {xl, xh}, %2;\n\t"
+        "fma.rn.f32.bf16 %0, wl, xl, %0;\n\t"
+        "fma.rn.f32.bf16 %0, wh, xh, %0; }"
+        : "+f"(acc)
+        : "r"(w), "r"(x));
 }
 
-__device__ __forceinline__ float unit_fma_bf16(const float2* p, const uint32_t* a16) {
-    float part[4] = {0.f, 0.f, 0.f, 0.f};
+// One word (4 packed bytes = 8 elements) of a unit against RM activation rows.  part[m][b] is the partial
+// sum of byte position b: the same four chains and the same order as unit_dot_regs of the streaming
+// kernel, so the bits agree.
+//   XF = 1: activations as fp32 bits (x[m][base + e], e = 0..7), table of float2 pairs.
+//   XF = 0: activations as bf16 pairs (x[m][base + b] holds elements 2b, 2b + 1), widened on use -- a bf16 is
+//           the top half of its fp32 --, table of float2 pairs.
+//   XF = 2: codebooks whose values are exact in bf16 (MXFP4): table of bf16 pairs (4 bytes per packed byte: half
+//           the shared-memory traffic of the float2 table), activations as bf16 pairs, mixed-precision FMA (no
+//           widening instructions at all).  lane8 is then lane * 4.
+template <int RM, int XF, int XN>
+__device__ __forceinline__ void word_fma(uint32_t w, uint32_t lane8, const uint32_t (&x)[RM][XN], int base,
+                                         float (&part)[RM][4]) {
+    if (XF == 2) {
+        uint32_t p[4];
+        p[0] = ld_table_b32(tab_index<0>(w, lane8));
+        p[1] = ld_table_b32(tab_index<1>(w, lane8));
+        p[2] = ld_table_b32(tab_index<2>(w, lane8));
+        p[3] = ld_table_b32(tab_index<3>(w, lane8));
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+        for (int m = 0; m < RM; ++m)
+#pragma unroll
+            for (int b = 0; b < 4; ++b) fma_bf16_pair(part[m][b], p[b], x[m][base + b]);
+        return;
+    }
+    float2 p[4];
+    p[0] = ld_table(tab_index<0>(w, lane8));
+    p[1] = ld_table(tab_index<1>(w, lane8));
+    p[2] = ld_table(tab_index<2>(w, lane8));
+    p[3] = ld_table(tab_index<3>(w, lane8));
+#pragma unroll
+    for (int m = 0; m < RM; ++m) {
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
-            const uint32_t ab = a16[i * 4 + b];
-            part[b] = fmaf(p[i * 4 + b].x, __uint_as_float(ab << 16), part[b]);
-            part[b] = fmaf(p[i * 4 + b].y, __uint_as_float(ab & 0xffff0000u), part[b]);
+            float x0, x1;
+            if (XF == 1) {
+                x0 = __uint_as_float(x[m][base + 2 * b]);
+                x1 = __uint_as_float(x[m][base + 2 * b + 1]);
+            } else {
+                const uint32_t ab = x[m][base + b];
+                x0 = __uint_as_float(ab << 16);
+                x1 = __uint_as_float(ab & 0xffff0000u);
+            }
+            part[m][b] = fmaf(p[b].x, x0, part[m][b]);
+            part[m][b] = fmaf(p[b].y, x1, part[m][b]);
         }
     }
-    return (part[0] + part[1]) + (part[2] + part[3]);
-}
-
-__device__ __forceinline__ float unit_dot_bf16(const uint4 wv, const uint32_t* a16, uint32_t tab_lane) {
-    float2 p[16];
-    unit_lookup(wv, tab_lane, p);
-    return unit_fma_bf16(p, a16);
 }
 
 template <int SDT>
@@ -120,12 +171,20 @@ struct DGroup {
 // the work list is (group, row chunk, tile) with the tile fastest, so a CTA keeps one chunk's activation
 // rows in registers for a run of tiles, and the group's weights are streamed once per chunk (the later
 // passes mostly from L2).  Chunks that a group does not have are not in the list (see GroupWalk).
-__device__ __forceinline__ DGroup decode_group(const DecodeArgs& a, int g, int c) {
-    // a group changes once per N / R items, so its three ints come straight from global
-    // memory (L1-cached) instead of a shared-memory copy that every thread would wait for
-    const int32_t row0 = __ldg(a.g.off + g);
-    const int32_t end = __ldg(a.g.off + g + 1);
-    const int32_t eid = __ldg(a.g.eids + g);
+struct DGroupRaw {
+    int32_t row0, end, eid;
+};
+// a group changes once per N / R items, so its three ints come straight from global memory (L1-cached) instead
+// of a shared-memory copy that every thread would wait for
+__device__ __forceinline__ DGroupRaw decode_group_load(const DecodeArgs& a, int g) {
+    DGroupRaw r;
+    r.row0 = __ldg(a.g.off + g);
+    r.end = __ldg(a.g.off + g + 1);
+    r.eid = __ldg(a.g.eids + g);
+    return r;
+}
+__device__ __forceinline__ DGroup decode_group_check(const DecodeArgs& a, const DGroupRaw& r, int c) {
+    const int32_t row0 = r.row0, end = r.end, eid = r.eid;
     DGroup d;
     d.row0 = row0 + c * a.rows_per_pass;
     d.eid = eid;
@@ -140,6 +199,9 @@ __device__ __forceinline__ DGroup decode_group(const DecodeArgs& a, int g, int c
     if (d.valid && c == 0 && end - row0 > a.row_chunks * a.rows_per_pass && a.g.status && (threadIdx.x & 31) == 0)
         atomicOr(a.g.status, GNF4B_ST_BAD_OFFSETS);
     return d;
+}
+__device__ __forceinline__ DGroup decode_group(const DecodeArgs& a, int g, int c) {
+    return decode_group_check(a, decode_group_load(a, g), c);
 }
 
 // Position in the list of (group, row chunk) pairs.  Plain mode: pair v is group v.
@@ -159,12 +221,18 @@ __device__ __forceinline__ void walk_to(const DecodeArgs& a, const int32_t* vb, 
     w.c = v - vb[w.g];
 }
 
-template <int FMT, int SDT, int AU, int RM>
+// FMT, SDT: weight format and scale dtype.  AU: 16-byte units of a row per lane (K <= AU * 1024).
+// RM: activation rows per pass.  RW: weight rows of a stage that a warp works on at the same time (two
+// independent streams of lookups and FMAs hide the table-read latency that one leaves exposed).  XF: form of the
+// activations in registers and of the lookup table (see word_fma).
+template <int FMT, int SDT, int AU, int RM, int RW, int XF>
 __global__ void __launch_bounds__(decode_threads(RM, AU), 1) decode_gemv_kernel(const DecodeArgs a) {
-    constexpr int kDConsumerWarps = decode_consumer_warps(RM, AU);
+    constexpr int kCW = decode_consumer_warps(RM, AU);
+    constexpr int kXN = XF == 1 ? AU * 32 : AU * 16;     // registers per activation row
     extern __shared__ __align__(1024) uint8_t smem[];
-    uint8_t* tab_raw = smem;
-    uint8_t* ring = smem + kSTableBytes;
+    const uint32_t smem_base = smem_u32(smem);
+    uint8_t* tab_raw = smem + ((uint32_t)kDTabAbs - smem_base);     // window address kDTabAbs
+    uint8_t* ring = tab_raw + kSTableBytes;
     uint8_t* tail = ring + (size_t)a.stages * a.slot_bytes;
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(tail);
     uint64_t* empty_bar = full_bar + kDMaxStages;
@@ -175,10 +243,15 @@ __global__ void __launch_bounds__(decode_threads(RM, AU), 1) decode_gemv_kernel(
     const int lane = threadIdx.x & 31;
 
     pdl_launch_dependents();
+    if (smem_base > (uint32_t)kDTabAbs) {
+        // dynamic shared memory starts beyond the table's fixed address (never seen): nothing is computed
+        if (threadIdx.x == 0 && a.g.status) atomicOr(a.g.status, GNF4B_ST_TIMEOUT);
+        return;
+    }
     if (threadIdx.x == 0) {
         for (int s = 0; s < a.stages; ++s) {
             mbar_init(full_bar + s, 1);
-            mbar_init(empty_bar + s, kDConsumerWarps);
+            mbar_init(empty_bar + s, kCW);
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -192,7 +265,7 @@ __global__ void __launch_bounds__(decode_threads(RM, AU), 1) decode_gemv_kernel(
     if (a.compact) {
         // compact mode (row chunks, or far more groups than rows): build the prefix sum of the groups' chunk counts (one warp, ordered scan),
         // then cut the list of existing items evenly over the CTAs
-        pdl_wait();
+        if (!a.tables_ready) pdl_wait();
         if (warp == 0) {
             int32_t carry = 0;
             if (lane == 0) s_grp[0] = 0;
@@ -227,11 +300,14 @@ __global__ void __launch_bounds__(decode_threads(RM, AU), 1) decode_gemv_kernel(
     walk_to(a, vb, w, (int)((uint32_t)item_lo / (uint32_t)a.tiles_per_group));
     int tile = (int)((uint32_t)item_lo - (uint32_t)w.v * (uint32_t)a.tiles_per_group);
 
-    if (warp == kDConsumerWarps) {
+    if (warp == kCW) {
         // ------------------------------------------------------------ producer (two lanes)
         // lane 0 copies the packed rows, lane 1 the scale rows of the same stage
         if (lane < 2) {
-            pdl_wait();             // group tables (and, for the consumers, activations) may come from the previous kernel
+            // The group tables may have been written by the kernel launched just before this one: wait for
+            // it, unless the caller said they were not.  The packed weights never are, so with ready tables
+            // the ring fills while the previous kernel of the stream is still running.
+            if (!a.tables_ready) pdl_wait();
             const int elt = (SDT == GNF4B_S_F32) ? 4 : (SDT == GNF4B_S_BF16 ? 2 : 1);
             const uint8_t* Sb = reinterpret_cast<const uint8_t*>(a.g.S);
             uint32_t stage = 0, phase = 0;
@@ -273,7 +349,7 @@ __global__ void __launch_bounds__(decode_threads(RM, AU), 1) decode_gemv_kernel(
     grp.valid = false;
     grp.row0 = 0;
     grp.rows = 0;
-    uint32_t a16[RM][AU * 16];     // the group's activation rows, bf16 pairs, units lane, lane + 32, ...
+    uint32_t xr[RM][kXN];     // the group's activation rows: units lane, lane + 32, ... (fp32 bits or bf16 pairs)
 
     auto load_a = [&](const DGroup& gr) {
 #pragma unroll
@@ -288,37 +364,71 @@ __global__ void __launch_bounds__(decode_threads(RM, AU), 1) decode_gemv_kernel(
                     const uint4 raw = (have && U < n_units)
                                           ? __ldg(reinterpret_cast<const uint4*>(xrow + (int64_t)U * 64 + v * 16))
                                           : make_uint4(0, 0, 0, 0);
-                    a16[m][q * 16 + v * 4 + 0] = raw.x;
-                    a16[m][q * 16 + v * 4 + 1] = raw.y;
-                    a16[m][q * 16 + v * 4 + 2] = raw.z;
-                    a16[m][q * 16 + v * 4 + 3] = raw.w;
+                    const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        if (XF == 1) {
+                            xr[m][q * 32 + v * 8 + 2 * j] = rw[j] << 16;
+                            xr[m][q * 32 + v * 8 + 2 * j + 1] = rw[j] & 0xffff0000u;
+                        } else {
+                            xr[m][q * 16 + v * 4 + j] = rw[j];
+                        }
+                    }
                 }
             }
         }
     };
+    // Before waiting for the previous kernel: with ready tables, the loads of this CTA's first group (three ints
+    // that the activation row's address depends on) go out now and are used after the table is built.
+    const bool early = a.tables_ready != 0 && item_lo < item_hi;
+    DGroupRaw raw0 = {0, 0, 0};
+    if (early) raw0 = decode_group_load(a, w.g);
     {
-        // pair table: tab[byte][slot], 32 slots of float2 per byte, all holding the same pair,
-        // so a lane reading slot == its lane id never conflicts with another lane.  A half
-        // warp writes one byte's 256-byte row per step with 16-byte stores.  Built before
-        // pdl_wait(): it overlaps the tail of the previous kernel.
-        const int half = lane >> 4, hl = lane & 15;
+        // Lookup table, one 256-byte row per packed byte value, built from instruction immediates (no constant
+        // memory).  XF < 2: 32 slots of float2, all holding the byte's pair of codebook values, so a lane reading
+        // slot == its lane id never conflicts with another lane; a half warp writes one row per step with 16-byte
+        // stores.  XF = 2: 32 slots of bf16 pairs in the first 128 bytes of the row.  Built before pdl_wait(): it
+        // overlaps the tail of the previous kernel.
+        const float mine = code_value_imm<FMT>((uint32_t)lane & 15u);
+        if (XF == 2) {
+            for (int b = warp; b < 256; b += kCW) {
+                const float e0 = __shfl_sync(0xffffffffu, mine, (FMT == GNF4B_FMT_NF4) ? (b >> 4) : (b & 15));
+                const float e1 = __shfl_sync(0xffffffffu, mine, (FMT == GNF4B_FMT_NF4) ? (b & 15) : (b >> 4));
+                const uint32_t v = (__float_as_uint(e0) >> 16) | (__float_as_uint(e1) & 0xffff0000u);
+                asm volatile("st.shared.u32 [%0], %1;" ::"r"((uint32_t)kDTabAbs + b * 256 + lane * 4), "r"(v) : "memory");
+            }
+        } else {
+            const int half = lane >> 4, hl = lane & 15;
 #pragma unroll 4
-        for (int b = warp * 2 + half; b < 256; b += kDConsumerWarps * 2) {
-            const float2 p = byte_pair<FMT>(b);
-            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(smem_u32(tab_raw) + b * 256 + hl * 16),
-                         "f"(p.x), "f"(p.y), "f"(p.x), "f"(p.y)
-                         : "memory");
+            for (int b0 = warp * 2; b0 < 256; b0 += kCW * 2) {
+                const int b = b0 + half;
+                const float e0 = __shfl_sync(0xffffffffu, mine, (FMT == GNF4B_FMT_NF4) ? (b >> 4) : (b & 15));
+                const float e1 = __shfl_sync(0xffffffffu, mine, (FMT == GNF4B_FMT_NF4) ? (b & 15) : (b >> 4));
+                asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"((uint32_t)kDTabAbs + b * 256 + hl * 16),
+                             "f"(e0), "f"(e1), "f"(e0), "f"(e1)
+                             : "memory");
+            }
+        }
+    }
+    if (early) {
+        grp = decode_group_check(a, raw0, w.c);
+        cur_v = w.v;
+        if (warp == 0 && grp.valid) {       // a hint that brings the activation rows' lines into L2
+            const uint8_t* xrow = reinterpret_cast<const uint8_t*>(a.g.x) + (int64_t)grp.row0 * a.g.K * 2;
+            const int64_t bytes = (int64_t)min(grp.rows, RM) * a.g.K * 2;
+            for (int64_t o = (int64_t)lane * 128; o < bytes; o += 32 * 128)
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(xrow + o));
         }
     }
     pdl_wait();
-    if (item_lo < item_hi) {
+    if (!early && item_lo < item_hi) {
         grp = decode_group(a, w.g, w.c);
         cur_v = w.v;
     }
     load_a(grp);
-    named_bar_sync(1, kDConsumerWarps * 32);
+    named_bar_sync(1, kCW * 32);
 
-    const uint32_t tab_lane = smem_u32(tab_raw) + lane * 8;
+    const uint32_t lane8 = (uint32_t)lane * (XF == 2 ? 4u : 8u);     // slot of this lane in a table row
     uint16_t* out_bf = reinterpret_cast<uint16_t*>(a.g.out);
     uint32_t stage = 0, phase = 0;
     bool poisoned = false;
@@ -334,62 +444,67 @@ __global__ void __launch_bounds__(decode_threads(RM, AU), 1) decode_gemv_kernel(
             const uint32_t st = smem_u32(ring + (size_t)stage * a.slot_bytes);
             const int n0 = tile * R;
             const int rows = min(R, (int)(a.g.N - n0));
-            for (int r = warp; r < rows; r += kDConsumerWarps) {
-                const uint32_t wrow = st + (uint32_t)(r * a.row_bytes);
-                const uint32_t srow = st + (uint32_t)(R * a.row_bytes + r * a.scale_row_bytes);
-                float acc[RM];
+            for (int r = warp; r < rows; r += kCW * RW) {
+                // RW rows of the stage: r, r + kCW, ...; one past the end repeats the last valid row (its result
+                // is not stored)
+                uint32_t wrow[RW], srow[RW];
+                float acc[RW][RM];
 #pragma unroll
-                for (int m = 0; m < RM; ++m) acc[m] = 0.f;
+                for (int j = 0; j < RW; ++j) {
+                    const int rj = min(r + j * kCW, rows - 1);
+                    wrow[j] = st + (uint32_t)(rj * a.row_bytes);
+                    srow[j] = st + (uint32_t)(R * a.row_bytes + rj * a.scale_row_bytes);
+#pragma unroll
+                    for (int m = 0; m < RM; ++m) acc[j][m] = 0.f;
+                }
 #pragma unroll
                 for (int q = 0; q < AU; ++q) {
                     const int u = lane + 32 * q;
                     if (u < n_units) {
-                        const uint4 wv = ld_shared_u32x4(wrow + u * 16);
-                        const float sc = ld_shared_scale<SDT>(srow, (FMT == GNF4B_FMT_NF4) ? (u >> 1) : u);
-                        if (RM == 1) {
-                            acc[0] += unit_dot_bf16(wv, &a16[0][q * 16], tab_lane) * sc;
-                        } else {
-                            // one table lookup per byte for all rows of the group; word by word to keep
-                            // the live registers down; per row the same four chains and the same order
-                            // as unit_fma_bf16
-                            const uint32_t words[4] = {wv.x, wv.y, wv.z, wv.w};
-                            float part[RM][4];
+                        constexpr int kPerUnit = kXN / AU, kPerWord = kPerUnit / 4;
+                        uint4 wv[RW];
+                        float sc[RW];
+                        float part[RW][RM][4];
+#pragma unroll
+                        for (int j = 0; j < RW; ++j) {
+                            wv[j] = ld_shared_u32x4(wrow[j] + u * 16);
+                            sc[j] = ld_shared_scale<SDT>(srow[j], (FMT == GNF4B_FMT_NF4) ? (u >> 1) : u);
 #pragma unroll
                             for (int m = 0; m < RM; ++m)
 #pragma unroll
-                                for (int b = 0; b < 4; ++b) part[m][b] = 0.f;
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                float2 p[4];
-#pragma unroll
-                                for (int b = 0; b < 4; ++b) p[b] = ld_table(tab_lane + prmt(words[i], 0u, 0x4404u | (b << 4)));
-#pragma unroll
-                                for (int m = 0; m < RM; ++m) {
-#pragma unroll
-                                    for (int b = 0; b < 4; ++b) {
-                                        const uint32_t ab = a16[m][q * 16 + i * 4 + b];
-                                        part[m][b] = fmaf(p[b].x, __uint_as_float(ab << 16), part[m][b]);
-                                        part[m][b] = fmaf(p[b].y, __uint_as_float(ab & 0xffff0000u), part[m][b]);
-                                    }
-                                }
-                            }
-#pragma unroll
-                            for (int m = 0; m < RM; ++m)
-                                acc[m] += ((part[m][0] + part[m][1]) + (part[m][2] + part[m][3])) * sc;
+                                for (int b = 0; b < 4; ++b) part[j][m][b] = 0.f;
                         }
+                        // one table lookup per byte serves all activation rows of the pass; word by word and row by
+                        // row, so that few looked-up pairs are live at a time
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+#pragma unroll
+                            for (int j = 0; j < RW; ++j) {
+                                const uint32_t word = i == 0 ? wv[j].x : i == 1 ? wv[j].y : i == 2 ? wv[j].z : wv[j].w;
+                                word_fma<RM, XF, kXN>(word, lane8, xr, q * kPerUnit + i * kPerWord, part[j]);
+                            }
+                        }
+#pragma unroll
+                        for (int j = 0; j < RW; ++j)
+#pragma unroll
+                            for (int m = 0; m < RM; ++m)
+                                acc[j][m] += ((part[j][m][0] + part[j][m][1]) + (part[j][m][2] + part[j][m][3])) * sc[j];
                     }
                 }
 #pragma unroll
-                for (int m = 0; m < RM; ++m) {
+                for (int j = 0; j < RW; ++j) {
 #pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) acc[m] += __shfl_xor_sync(0xffffffffu, acc[m], o);
-                    if (lane == 0 && m < grp.rows)
-                        out_bf[(int64_t)(grp.row0 + m) * a.g.N + n0 + r] = f32_to_bf16_bits(acc[m]);
+                    for (int m = 0; m < RM; ++m) {
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) acc[j][m] += __shfl_xor_sync(0xffffffffu, acc[j][m], o);
+                        if (lane == 0 && m < grp.rows && r + j * kCW < rows)
+                            out_bf[(int64_t)(grp.row0 + m) * a.g.N + n0 + r + j * kCW] = f32_to_bf16_bits(acc[j][m]);
+                    }
                 }
             }
         }
         __syncwarp();
-        if (!poisoned && lane == 0) mbar_arrive(empty_bar + stage);
+        if (!poisoned && lane == 0) mbar_arrive_relaxed(empty_bar + stage);
         if (++stage == (uint32_t)a.stages) { stage = 0; phase ^= 1; }
         if (++tile == a.tiles_per_group) { tile = 0; walk_to(a, vb, w, w.v + 1); }
     }

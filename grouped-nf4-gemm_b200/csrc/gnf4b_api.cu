@@ -4,6 +4,7 @@
 
 #include <algorithm>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <vector>
@@ -216,40 +217,52 @@ static cudaError_t launch_stream_au(const StreamArgs& sa, int au, int grid, size
 #undef GNF4B_LAUNCH_AU
 }
 
+template <int FMT, int SDT, int AUV, int RMV, int RW, int XF>
+static cudaError_t launch_decode_one(const DecodeArgs& da, int grid, size_t smem, cudaStream_t st) {
+    auto kfn = decode_gemv_kernel<FMT, SDT, AUV, RMV, RW, XF>;
+    static int granted[64];
+    cudaError_t e = ensure_smem(kfn, smem, granted);
+    if (e != cudaSuccess) return e;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(decode_threads(RMV, AUV));
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kfn, da);
+}
+
+// rw: weight rows of a stage per warp in flight (2 only with one activation row per pass and short rows).
+// Form of the activations and of the table (XF of the kernel): fp32 activations while they fit the registers
+// (AU <= 2), bf16 pairs beyond; MXFP4, whose codebook is exact in bf16, always takes the bf16-pair table with the
+// mixed-precision FMA.
 template <int FMT, int SDT>
-static cudaError_t launch_decode_au(const DecodeArgs& da, int au, int rm, int grid, size_t smem, cudaStream_t st) {
-#define GNF4B_LAUNCH_D(AUV, RMV)                                                                      \
-    do {                                                                                              \
-        auto kfn = decode_gemv_kernel<FMT, SDT, AUV, RMV>;                                            \
-        static int granted[64];                                                                       \
-        cudaError_t e = ensure_smem(kfn, smem, granted);                                              \
-        if (e != cudaSuccess) return e;                                                               \
-        cudaLaunchConfig_t cfg = {};                                                                  \
-        cfg.gridDim = dim3((unsigned)grid);                                                           \
-        cfg.blockDim = dim3(decode_threads(RMV, AUV));                                                     \
-        cfg.dynamicSmemBytes = smem;                                                                  \
-        cfg.stream = st;                                                                              \
-        cudaLaunchAttribute attr[1];                                                                  \
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;                              \
-        attr[0].val.programmaticStreamSerializationAllowed = 1;                                       \
-        cfg.attrs = attr;                                                                             \
-        cfg.numAttrs = 1;                                                                             \
-        return cudaLaunchKernelEx(&cfg, kfn, da);                                                     \
-    } while (0)
+static cudaError_t launch_decode_au(const DecodeArgs& da, int au, int rm, int rw, int grid, size_t smem,
+                                    cudaStream_t st) {
+    constexpr int X1 = (FMT == GNF4B_FMT_MXFP4) ? 2 : 1;     // short rows
+    constexpr int X0 = (FMT == GNF4B_FMT_MXFP4) ? 2 : 0;     // long rows, two activation rows per pass
+    if (rm == 1 && rw == 2) {
+        if (au <= 1) return launch_decode_one<FMT, SDT, 1, 1, 2, X1>(da, grid, smem, st);
+        if (au == 2) return launch_decode_one<FMT, SDT, 2, 1, 2, X1>(da, grid, smem, st);
+        if (au == 3) return launch_decode_one<FMT, SDT, 3, 1, 2, X0>(da, grid, smem, st);
+    }
     if (rm == 1) {
-        if (au <= 1) GNF4B_LAUNCH_D(1, 1);
-        if (au == 2) GNF4B_LAUNCH_D(2, 1);
-        if (au == 3) GNF4B_LAUNCH_D(3, 1);
-        if (au <= 5) GNF4B_LAUNCH_D(5, 1);
-        if (au <= 7) GNF4B_LAUNCH_D(7, 1);
+        if (au <= 1) return launch_decode_one<FMT, SDT, 1, 1, 1, X1>(da, grid, smem, st);
+        if (au == 2) return launch_decode_one<FMT, SDT, 2, 1, 1, X1>(da, grid, smem, st);
+        if (au == 3) return launch_decode_one<FMT, SDT, 3, 1, 1, X0>(da, grid, smem, st);
+        if (au <= 5) return launch_decode_one<FMT, SDT, 5, 1, 1, X0>(da, grid, smem, st);
+        if (au <= 7) return launch_decode_one<FMT, SDT, 7, 1, 1, X0>(da, grid, smem, st);
     }
     if (rm == 2) {
-        if (au <= 1) GNF4B_LAUNCH_D(1, 2);
-        if (au == 2) GNF4B_LAUNCH_D(2, 2);
-        if (au == 3) GNF4B_LAUNCH_D(3, 2);
+        if (au <= 1) return launch_decode_one<FMT, SDT, 1, 2, 1, X0>(da, grid, smem, st);
+        if (au == 2) return launch_decode_one<FMT, SDT, 2, 2, 1, X0>(da, grid, smem, st);
+        if (au == 3) return launch_decode_one<FMT, SDT, 3, 2, 1, X0>(da, grid, smem, st);
     }
     return cudaErrorInvalidValue;
-#undef GNF4B_LAUNCH_D
 }
 
 static int align_class(const void* p, int64_t a, int64_t b) {
@@ -308,6 +321,7 @@ using namespace gnf4b;
 extern "C" {
 
 int gnf4b_abi_version(void) { return GNF4B_ABI_VERSION; }
+
 
 const char* gnf4b_strerror(int rc) {
     switch (rc) {
@@ -428,30 +442,41 @@ int gnf4b_gemm_grouped(int fmt, int op, const void* x, int x_dtype, int64_t T, c
         const int au_k = (int)ceil_div(K, 1024);
         const bool chunk_ok = max_rows >= 2 && max_rows <= 16 && G <= p.g_cache;
         const int rm = max_rows == 1 ? 1 : au_k > 3 ? (chunk_ok ? 1 : 0) : (max_rows == 2 || chunk_ok) ? 2 : 0;
-        // long rows: one row per consumer warp and stage (6 rows), so the scale span of a stage must stay
-        // 16-byte aligned at that granularity
+        // long rows (one row per consumer warp and stage, 6 rows): the scale span of a stage and of the last,
+        // shorter stage of a group must stay 16-byte aligned at that granularity
         const bool long_ok = au_k <= 3 || ((6 * srow) % 16 == 0 && (N % 6 == 0 || (((N % 6) * srow) % 16 == 0)));
         if (rm && long_ok && p.split_k == 1 && K <= 7168 && (N % 8) == 0 && contiguous &&
             x_dtype == GNF4B_X_BF16) {
-            const int kDConsumerWarps = decode_consumer_warps(rm, au_k);
+            const int cw = decode_consumer_warps(rm, au_k);
+            // two weight rows per warp in flight for one-row groups with short rows (see decode_kernel.cuh)
+            const int rw = (rm == 1 && au_k <= 3 && !(flags & GNF4B_FLAG_DECODE_ONE_ROW)) ? 2 : 1;
             DecodeArgs da;
             da.g = g;
-            // rows per stage: up to 32 KiB of weight rows, chosen so that the CTA with the most items gets as
-            // few rows as possible (items are dealt out whole: with 768 items on 148 CTAs some CTAs would
-            // stream 6 tiles and others 5); a small per-item charge keeps the stages from getting tiny
-            const int m = (int)std::max<int64_t>(1, std::min<int64_t>(4, 32768 / (kDConsumerWarps * row_bytes)));
+            const int64_t ring_room = (int64_t)di.smem_optin - (int64_t)decode_smem_bytes(0, 0, p.g_cache);
             // a stage's scale span must stay 16-byte aligned: rows per stage in multiples of 4 when four scale
-            // rows are, else of 8 (`contiguous` guarantees eight are); the upper end is rounded down to that
+            // rows are, else of 8 (`contiguous` guarantees eight are)
             const int r_step = ((4 * srow) % 16 == 0) ? 4 : 8;
-            const int r_hi = std::max(r_step, (kDConsumerWarps * m / r_step) * r_step);
-            const int64_t groups_eff = std::max<int64_t>(1, std::min<int64_t>((int64_t)G * ((max_rows + rm - 1) / rm), T));
-            int best_r = r_hi;
-            int64_t best_cost = INT64_MAX;
-            for (int r = r_hi; au_k <= 3 && r >= std::max(8, r_hi / 2); r -= r_step) {
-                const int64_t items = groups_eff * ceil_div(N, r);
-                const int64_t per_cta = ceil_div(items, std::min<int64_t>(di.sm_count, items));
-                const int64_t cost = per_cta * (r + 2);
-                if (cost < best_cost) { best_cost = cost; best_r = r; }
+            int best_r;
+            if (au_k > 3) {
+                best_r = cw;                       // long_ok checked this granularity
+            } else {
+                // rows per stage: up to 32 KiB of weight rows (at least rw per warp when three such stages fit the
+                // ring), a whole number of rows per warp with rw = 2, and among the candidates the one that gives the
+                // CTA with the most items the fewest rows (items are dealt out whole: with 768 items on 148 CTAs some
+                // CTAs would stream 6 tiles and others 5); a small per-item charge keeps the stages from getting tiny
+                int m = (int)std::max<int64_t>(1, std::min<int64_t>(4, 32768 / (cw * row_bytes)));
+                if (m < rw && 3 * (int64_t)cw * rw * (row_bytes + srow) <= ring_room) m = rw;
+                const int gran = (rw == 2 && m >= 2) ? cw * rw : r_step;
+                const int r_hi = std::max(gran, (cw * m / gran) * gran);
+                const int64_t groups_eff = std::max<int64_t>(1, std::min<int64_t>((int64_t)G * ((max_rows + rm - 1) / rm), T));
+                best_r = r_hi;
+                int64_t best_cost = INT64_MAX;
+                for (int r = r_hi; r >= std::max(std::max(8, gran), r_hi / 2); r -= gran) {
+                    const int64_t items = groups_eff * ceil_div(N, r);
+                    const int64_t per_cta = ceil_div(items, std::min<int64_t>(di.sm_count, items));
+                    const int64_t cost = per_cta * (r + 2);
+                    if (cost < best_cost) { best_cost = cost; best_r = r; }
+                }
             }
             da.rows_per_stage = best_r;
             da.tiles_per_group = (int32_t)ceil_div(N, da.rows_per_stage);
@@ -464,21 +489,20 @@ int gnf4b_gemm_grouped(int fmt, int op, const void* x, int x_dtype, int64_t T, c
             // a list with more groups than rows is mostly empty (or padding) groups: walk only the ones that exist
             da.compact = (da.row_chunks > 1 || ((int64_t)G > T && G <= p.g_cache)) ? 1 : 0;
             da.total_items = (int64_t)G * da.row_chunks * da.tiles_per_group;
-            const int64_t room = (int64_t)di.smem_optin - (int64_t)decode_smem_bytes(0, 0, da.g_cache);
-            da.stages = (int32_t)std::min<int64_t>(kDMaxStages, room / da.slot_bytes);
+            da.tables_ready = (flags & GNF4B_FLAG_TABLES_READY) ? 1 : 0;
+            da.stages = (int32_t)std::min<int64_t>(kDMaxStages, ring_room / da.slot_bytes);
             const int dgrid = (int)std::min<int64_t>(di.sm_count, da.total_items);
             da.items_per_cta = (int32_t)(da.total_items / dgrid);
             da.items_extra = (int32_t)(da.total_items % dgrid);
             const size_t dsmem = decode_smem_bytes(da.slot_bytes, std::max(da.stages, 1), da.g_cache);
             if (da.stages >= 3 && da.total_items < (int64_t)1 << 31) {
-                const int au = (int)ceil_div(K, 1024);
                 cudaError_t e;
                 if (fmt == GNF4B_FMT_NF4 && s_dtype == GNF4B_S_F32)
-                    e = launch_decode_au<GNF4B_FMT_NF4, GNF4B_S_F32>(da, au, rm, dgrid, dsmem, st);
+                    e = launch_decode_au<GNF4B_FMT_NF4, GNF4B_S_F32>(da, au_k, rm, rw, dgrid, dsmem, st);
                 else if (fmt == GNF4B_FMT_NF4)
-                    e = launch_decode_au<GNF4B_FMT_NF4, GNF4B_S_BF16>(da, au, rm, dgrid, dsmem, st);
+                    e = launch_decode_au<GNF4B_FMT_NF4, GNF4B_S_BF16>(da, au_k, rm, rw, dgrid, dsmem, st);
                 else
-                    e = launch_decode_au<GNF4B_FMT_MXFP4, GNF4B_S_E8M0>(da, au, rm, dgrid, dsmem, st);
+                    e = launch_decode_au<GNF4B_FMT_MXFP4, GNF4B_S_E8M0>(da, au_k, rm, rw, dgrid, dsmem, st);
                 if (e != cudaSuccess) return cuda_fail(e, "decode kernel launch");
                 return GNF4B_OK;
             }
@@ -662,9 +686,10 @@ int gnf4b_gemm_grouped_host(int fmt, int op, const void* x_host, int x_dtype, in
         e = cudaMemsetAsync(base, 0, p.counters_bytes, st);
         if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(arrival counters)");
     }
+    // the tables were uploaded by the copy above: ready when the kernel starts
     rc = gnf4b_gemm_grouped(fmt, op, d_x, x_dtype, T, W, w_stride_e, w_stride_n, S, s_dtype, s_stride_e, s_stride_n,
                             d_off, d_ids, G, E, N, K, max_rows, d_out, h.ws_bytes ? base : nullptr, h.ws_bytes,
-                            d_status, flags, cuda_stream);
+                            d_status, flags | GNF4B_FLAG_TABLES_READY, cuda_stream);
     if (rc) { cudaStreamSynchronize(st); return rc; }    // the copies above read host memory: let them finish
     e = cudaMemcpyAsync(out_host, d_out, h.out_bytes, cudaMemcpyDeviceToHost, st);
     if (e != cudaSuccess) { cudaStreamSynchronize(st); return cuda_fail(e, "cudaMemcpyAsync(out)"); }
@@ -801,7 +826,7 @@ int gnf4b_ffn_grouped_host(int fmt, const void* x_host, int x_dtype, int64_t T,
     }
     rc = gnf4b_gemm_grouped(fmt, GNF4B_OP_FWD, base + f.x, x_dtype, T, W_gu, wgu_stride_e, wgu_stride_n, S_gu, s_dtype,
                             sgu_stride_e, sgu_stride_n, d_off, d_ids, G, E, N_gu, K_gu, max_rows, base + f.gu,
-                            f.ws_bytes ? base : nullptr, f.ws_bytes, d_status, flags, cuda_stream);
+                            f.ws_bytes ? base : nullptr, f.ws_bytes, d_status, flags | GNF4B_FLAG_TABLES_READY, cuda_stream);
     if (rc) return fail(rc);
     rc = gnf4b_silu_glu(base + f.gu, T, H, base + f.h, cuda_stream);
     if (rc) return fail(rc);
@@ -811,7 +836,7 @@ int gnf4b_ffn_grouped_host(int fmt, const void* x_host, int x_dtype, int64_t T,
     }
     rc = gnf4b_gemm_grouped(fmt, GNF4B_OP_FWD, base + f.h, x_dtype, T, W_dn, wdn_stride_e, wdn_stride_n, S_dn, s_dtype,
                             sdn_stride_e, sdn_stride_n, d_off, d_ids, G, E, N_dn, H, max_rows, base + f.out,
-                            f.ws_bytes ? base : nullptr, f.ws_bytes, d_status, flags, cuda_stream);
+                            f.ws_bytes ? base : nullptr, f.ws_bytes, d_status, flags | GNF4B_FLAG_TABLES_READY, cuda_stream);
     if (rc) return fail(rc);
     e = cudaMemcpyAsync(out_host, base + f.out, f.out_bytes, cudaMemcpyDeviceToHost, st);
     if (e != cudaSuccess) return fail(cuda_fail(e, "cudaMemcpyAsync(out)"));

@@ -36,13 +36,13 @@ def _lut(device):
 
 def gemm_mxfp4_grouped(a_cat, blocks, scales, sizes, expert_ids,
                        block_m: int | None = None, prefill_variant: int | None = None, *,
-                       group_offsets=None, max_rows=None, path: int = 0):
+                       group_offsets=None, max_rows=None, path: int = 0, tables_ready: bool | None = None):
     """Single-launch grouped MXFP4 GEMM (ref :134-172).  ``a_cat [T,K]`` bf16/fp16 rows
     sorted by group; ``blocks [E,N,K//2]`` uint8; ``scales [E,N,K//32]`` uint8 (e8m0);
     ``sizes`` per-group row counts; ``expert_ids [G]`` list / CPU / CUDA int tensor.
     Returns ``[T,N]`` bf16 in the same row order.  ``block_m`` and ``prefill_variant`` are
     Triton knobs of the reference, accepted and ignored.  ``group_offsets`` / ``max_rows`` /
-    ``path`` are the keyword-only additions described at ``nf4_grouped.gemm_4bit_grouped``."""
+    ``path`` / ``tables_ready`` are the keyword-only additions described at ``nf4_grouped.gemm_4bit_grouped``."""
     E, N, _ = blocks.shape
     T, K = a_cat.shape
     assert scales.shape == (E, N, K // MX_BLOCK), (scales.shape, (E, N, K // MX_BLOCK))
@@ -53,7 +53,7 @@ def gemm_mxfp4_grouped(a_cat, blocks, scales, sizes, expert_ids,
     if blocks.shape[2] * 2 != K:
         raise ValueError(f"a_cat has K={K} but blocks pack K={blocks.shape[2] * 2}")
     return _launch(_gnf4b.FMT_MXFP4, _gnf4b.OP_FWD, a_cat, blocks, scales, sizes, expert_ids, N,
-                   group_offsets=group_offsets, max_rows=max_rows, path=path)
+                   group_offsets=group_offsets, max_rows=max_rows, path=path, tables_ready=tables_ready)
 
 
 def gemm_mxfp4_grouped_host(a_host, blocks, scales, sizes, expert_ids, out=None, *, path: int = 0,

@@ -458,7 +458,7 @@ def _group_tables(sizes, expert_ids, T: int, E: int, dev, group_offsets=None, ma
 
 
 def _launch(fmt, op, x, W, S, sizes, expert_ids, n_out, *, split_k=None, path=_gnf4b.PATH_AUTO,
-            group_offsets=None, max_rows=None):
+            group_offsets=None, max_rows=None, tables_ready=None):
     """One grouped launch.  x [T, C] bf16/fp16, W [E, N, K/2] u8, S scales -> bf16 [T, n_out]."""
     dev = x.device
     E, N, half = W.shape
@@ -509,6 +509,14 @@ def _launch(fmt, op, x, W, S, sizes, expert_ids, n_out, *, split_k=None, path=_g
         flags = path
         if split_k is not None:
             flags |= max(1, int(split_k)) << _gnf4b.SPLITK_SHIFT
+        # Group tables that this call uploaded from host lists travel by a stream-ordered copy, which no kernel
+        # overtakes: they are ready when the kernel starts.  Device tables may have been written by the kernel
+        # launched just before (a router, a prefix sum): only the caller can say that they were not.
+        if tables_ready is None:
+            tables_ready = group_offsets is None and not (torch.is_tensor(sizes) and sizes.is_cuda) \
+                and not (torch.is_tensor(expert_ids) and expert_ids.is_cuda)
+        if tables_ready:
+            flags |= _gnf4b.FLAG_TABLES_READY
         key = (dev.index, fmt, op, T, G, N, K, max_rows, flags)        # the plan depends on the device's SM count
         need = _WS_BYTES.get(key)
         if need is None:
@@ -542,7 +550,8 @@ def _require_cuda(t, fn_name: str, hint: str):
 def gemm_4bit_grouped(a_cat, B, absmax, sizes, expert_ids, block_m: int | None = None,
                       decode_config: tuple | None = None, split_k: int | None = None,
                       prefill_config: tuple | None = None, prefill_variant: int | None = None,
-                      prefill_groups: int = 1, *, group_offsets=None, max_rows=None, path: int = 0):
+                      prefill_groups: int = 1, *, group_offsets=None, max_rows=None, path: int = 0,
+                      tables_ready: bool | None = None):
     """Single-launch grouped NF4 GEMM (ref :697-907).
 
     ``a_cat [T,K]`` bf16/fp16 rows sorted by group, ``B [E,N,K//2]`` uint8 (any expert / row
@@ -561,6 +570,10 @@ def gemm_4bit_grouped(a_cat, B, absmax, sizes, expert_ids, block_m: int | None =
     device and the call never synchronises (routing can change under CUDA-graph replay).
     ``max_rows`` -- the largest group size if the caller knows it (a path hint only).
     ``path`` -- 0 planner, 1 streaming kernel, 2 tensor-core kernel (ablation).
+    ``tables_ready`` -- True promises that device-side ``group_offsets`` / ``expert_ids`` / ``sizes`` were NOT
+    written by the kernel launched just before this call on the stream; the decode kernel then starts
+    streaming weights while that kernel still runs.  Default: true for host lists (they are uploaded by a
+    stream-ordered copy), false for device tensors.
     """
     E, N, _ = B.shape
     T, K = a_cat.shape
@@ -572,7 +585,7 @@ def gemm_4bit_grouped(a_cat, B, absmax, sizes, expert_ids, block_m: int | None =
     if tuple(absmax.shape) != (E, N, K // BLOCKSIZE):
         raise ValueError(f"absmax shape {tuple(absmax.shape)} != {(E, N, K // BLOCKSIZE)}")
     return _launch(_gnf4b.FMT_NF4, _gnf4b.OP_FWD, a_cat, B, absmax, sizes, expert_ids, N, split_k=split_k,
-                   group_offsets=group_offsets, max_rows=max_rows, path=path)
+                   group_offsets=group_offsets, max_rows=max_rows, path=path, tables_ready=tables_ready)
 
 
 def dgrad_eligible(grad_out, B, absmax, block_k: int = 64):

@@ -49,6 +49,13 @@ extern "C" {
 #define GNF4B_FLAG_SMEM_OPERANDS 0x10000u /* ablation: forward on the first tensor kernel (both MMA
                                             operands in shared memory) instead of weights in TMEM */
 
+#define GNF4B_FLAG_TABLES_READY   0x40000u /* group_offsets / expert_ids were not written by the kernel launched
+                                            just before this call on the stream (they were uploaded, or made
+                                            earlier): the decode kernel then streams its first weights while
+                                            that previous kernel is still running */
+#define GNF4B_FLAG_DECODE_ONE_ROW 0x80000u /* ablation: decode kernel with one weight row per warp in flight where it
+                                            would keep two */
+
 /* error codes */
 #define GNF4B_OK            0
 #define GNF4B_EINVAL       -1   /* bad enum / null pointer / negative size            */
