@@ -123,6 +123,20 @@ def algorithmic(shape, proj, rows, active):
     return wbytes + 2 * rows * (K + N), 2 * rows * N * K
 
 
+def workload_config(shape, tokens, layers, n_gpus=1):
+    """The `config` object of the JSON line; the same for both arms of a run."""
+    if n_gpus <= 1:
+        workload = (f"{shape.name} {shape.fmt} MoE layer, {tokens} tokens per GPU, top-{shape.top_k} of "
+                    f"{shape.experts} experts, gate_up {shape.gate_up} + down {shape.down}")
+    else:
+        workload = (f"{shape.name} {shape.fmt} MoE layer, expert-parallel over {n_gpus} GPUs "
+                    f"({shape.experts // n_gpus} experts per GPU), {tokens} tokens per GPU, top-{shape.top_k}, "
+                    f"dispatch/combine by NCCL all_to_all")
+    return {"workload": workload, "tokens": tokens, "layers_resident": layers,
+            "l2": f"inputs larger than L2: {layers} layer stacks walked round-robin, fresh routing per step",
+            "timing": "K steps in one CUDA graph, median over replays, CUDA events (GPU arm); wall clock per layer pass (CPU arm)"}
+
+
 def make_steps(shape, tokens, n_steps, seed, zipf=None):
     """Per-step routing and host activations (pinned)."""
     gen = torch.Generator().manual_seed(seed)
@@ -428,11 +442,7 @@ def run_gpu(args, shape, rank, world):
         "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_layer / K, "higher_is_better": False,
         "scaling": "weak", "vs_baseline": (us_layer / base) if base else None,
         "dtype": "bf16 activations x 4-bit weights, fp32 accumulate", "data": "synthetic",
-        "config": {"workload": f"{shape.name} {shape.fmt} MoE layer, {args.tokens} tokens per GPU, top-{shape.top_k} of "
-                               f"{shape.experts} experts, gate_up {shape.gate_up} + down {shape.down}",
-                   "tokens": args.tokens, "layers_resident": args.layers,
-                   "l2": f"inputs larger than L2: {args.layers} layer stacks walked round-robin, fresh routing per step",
-                   "timing": f"K steps in one CUDA graph, median of {len(t_layer)} replays, CUDA events"},
+        "config": workload_config(shape, args.tokens, args.layers),
         "e2e": {"value": us_e2e, "unit": "us/layer", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "api": "gnf4b_gemm_grouped_host (nf4_grouped.HostGroupedGemm): host x, sizes, expert ids and "
                        "result per GEMM, two blocking calls per layer"},
@@ -458,6 +468,11 @@ def run_gpu(args, shape, rank, world):
             "d2h_bytes_per_step": d2h_dev,
             "api": "gnf4b_ffn_grouped_host (nf4_grouped.HostGroupedFfn): gate_up GEMM, SiLU-GLU, down GEMM in one "
                    "blocking host call per layer; three kernels, the intermediate stays on the device"}
+    if world == 1 and not args.no_cells:
+        del dsteps, host_runs, host_ffns
+        t0 = time.perf_counter()
+        line["cells"] = measure_cells(args, dev, peaks, layers)
+        line["cells_seconds"] = time.perf_counter() - t0
     if world == 1:
         try:
             ep_us = time_ep_layer_single_gpu(args, shape, layers, dev)
@@ -471,6 +486,171 @@ def run_gpu(args, shape, rank, world):
     return line
 
 
+# --------------------------------------------------------------------------- more cells of the same run
+def _roofline(shape, proj, rows, active, us, peaks, dgrad=False):
+    """Roofline of ONE grouped call: HBM-bound while groups are decode-sized, tensor-bound beyond."""
+    by, fl = algorithmic(shape, proj, rows, active)
+    if not dgrad and rows / max(active, 1) <= 16:
+        ach = by / (us * 1e-6) / 1e9
+        return dict(bound="hbm", achieved=ach, peak=peaks["hbm_gbs"], unit="GB/s", frac=ach / peaks["hbm_gbs"],
+                    us_per_launch=us, algorithmic_bytes=by, algorithmic_flops=fl)
+    ach = fl / (us * 1e-6) / 1e12
+    return dict(bound="tensor", achieved=ach, peak=peaks["tflops"], unit="TFLOP/s", frac=ach / peaks["tflops"],
+                peak_kind="burst", us_per_launch=us, algorithmic_bytes=by, algorithmic_flops=fl)
+
+
+def _graph_us(fn_step, n_steps, replays=5):
+    """Median microseconds per step of `n_steps` calls of fn_step(i) captured in one CUDA graph."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        fn_step(0)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(n_steps):
+            fn_step(i)
+    g.replay()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(replays):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) * 1e3 / n_steps)
+    return statistics.median(ts)
+
+
+def _sampled_error(shape, proj, op, x, out, W, S, sizes, eids):
+    """max |out - ref| / max |ref| against the fp64 oracle on the first rows (at most 4) of the first and the
+    last group."""
+    import numpy as np
+    from oracle import oracle as O
+    offs = [0]
+    for v in sizes:
+        offs.append(offs[-1] + v)
+    worst = 0.0
+    for gi in sorted({0, len(sizes) - 1}):
+        n = min(4, sizes[gi])
+        if n == 0:
+            continue
+        r0, e = offs[gi], eids[gi]
+        xs = x[r0:r0 + n].float().cpu().numpy()
+        Wn = W[e:e + 1].cpu().numpy()
+        Sn = S[e:e + 1].cpu()
+        Sn = Sn.view(torch.int16).numpy().view(np.uint16) if Sn.dtype == torch.bfloat16 else Sn.numpy()
+        f = O.dgrad_grouped_f64 if op == "dgrad" else O.gemm_grouped_f64
+        ref = f(shape.fmt, xs, Wn, Sn, [n], [0])
+        got = out[r0:r0 + n].double().cpu().numpy()
+        worst = max(worst, float(np.abs(got - ref).max() / max(np.abs(ref).max(), 1e-30)))
+    return worst
+
+
+def measure_cells(args, dev, peaks, default_layers):
+    """The other cells of the benchmark matrix, each a few seconds: same method as the headline (K steps in one
+    CUDA graph over resident layer stacks walked round-robin, CUDA events, median of 5 replays), each with the
+    roofline of its gate_up call (of the one call, for dgrad) and an error sample against the fp64 oracle."""
+    import nf4_grouped
+    cells = []
+    stacks = {"qwen3_30b_a3b": default_layers if args.config == "qwen3_30b_a3b" else None}
+
+    def layers_of(name):
+        if stacks.get(name) is None:
+            shape = synth.CONFIGS[name]
+            per_layer = sum(shape.experts * n * (k // 2 + k // 16) for n, k in (shape.gate_up, shape.down))
+            n_layers = max(2, min(16, int(3.0e9 // per_layer)))
+            stacks[name] = build_layers(shape, n_layers, dev, seed=4321, random_bytes=True)
+        return stacks[name]
+
+    def fwd_cell(name, tokens, one_row_groups=0):
+        shape = synth.CONFIGS[name]
+        layers = layers_of(name)
+        fn = grouped(shape)
+        n_steps = 4 if tokens >= 512 else 16
+        gen = torch.Generator().manual_seed(1000 + tokens + one_row_groups)
+        st = []
+        for _ in range(n_steps):
+            if one_row_groups:
+                eids = torch.randperm(shape.experts, generator=gen)[:one_row_groups].sort().values.tolist()
+                sizes = [1] * one_row_groups
+                a = torch.randn(one_row_groups, shape.hidden, generator=gen).to(torch.bfloat16)
+            else:
+                x, idx, _ = synth.routed_batch(shape, tokens, gen)
+                tok, sizes, eids, _ = synth.dispatch(idx, shape.experts)
+                a = x[tok].contiguous()
+            off = [0]
+            for v in sizes:
+                off.append(off[-1] + v)
+            st.append(dict(a=a.to(dev), h=torch.randn(a.shape[0], shape.inter, generator=gen).to(torch.bfloat16).to(dev),
+                           off=torch.tensor(off, dtype=torch.int32, device=dev),
+                           eids=torch.tensor(eids, dtype=torch.int32, device=dev), sizes=sizes, eid_list=eids,
+                           max_rows=max(sizes)))
+
+        def step(i, what):
+            (gu, dn), d = layers[i % len(layers)], st[i]
+            o = None
+            if what != "down":
+                o = fn(d["a"], gu[0], gu[1], None, d["eids"], group_offsets=d["off"], max_rows=d["max_rows"], tables_ready=True)
+            if what != "gate_up":
+                o = fn(d["h"], dn[0], dn[1], None, d["eids"], group_offsets=d["off"], max_rows=d["max_rows"], tables_ready=True)
+            return o
+
+        us_layer = _graph_us(lambda i: step(i, "both"), n_steps)
+        us_gu = _graph_us(lambda i: step(i, "gate_up"), n_steps)
+        rows = statistics.mean(len(d["a"]) for d in st)
+        active = statistics.mean(len(d["sizes"]) for d in st)
+        d0 = st[0]
+        err = _sampled_error(shape, "gate_up", "fwd", d0["a"], step(0, "gate_up"), layers[0][0][0], layers[0][0][1],
+                             d0["sizes"], d0["eid_list"])
+        what = f"{one_row_groups} one-row groups" if one_row_groups else f"{tokens} tokens"
+        cells.append({"workload": f"{shape.name} {shape.fmt} MoE layer, {what}, gate_up {shape.gate_up} + down {shape.down}",
+                      "tokens": tokens, "value": us_layer, "unit": "us/layer", "rows": rows, "active_experts": active,
+                      "roofline": _roofline(shape, "gate_up", rows, active, us_gu, peaks), "max_rel_err": err})
+
+    def dgrad_cell(name, tokens):
+        shape = synth.CONFIGS[name]
+        layers = layers_of(name)
+        gen = torch.Generator().manual_seed(2000 + tokens)
+        _, idx, _ = synth.routed_batch(shape, tokens, gen)
+        tok, sizes, eids, _ = synth.dispatch(idx, shape.experts)
+        off = [0]
+        for v in sizes:
+            off.append(off[-1] + v)
+        off_t = torch.tensor(off, dtype=torch.int32, device=dev)
+        eid_t = torch.tensor(eids, dtype=torch.int32, device=dev)
+        for proj, pi in (("gate_up", 0), ("down", 1)):
+            N, K = getattr(shape, proj)
+            go = (torch.randn(len(tok), N, generator=gen) * 1e-3).to(torch.bfloat16).to(dev)
+            call = (nf4_grouped.dgrad_4bit_grouped if shape.fmt == "nf4"
+                    else __import__("mxfp4_grouped").dgrad_mxfp4_grouped)
+
+            def step(i):
+                W, S = layers[i % len(layers)][pi]
+                return call(go, W, S, None, eid_t, group_offsets=off_t, max_rows=max(sizes))
+
+            us = _graph_us(step, 4)
+            err = _sampled_error(shape, proj, "dgrad", go, step(0), layers[0][pi][0], layers[0][pi][1], sizes, eids)
+            cells.append({"workload": f"{shape.name} {shape.fmt} QLoRA dgrad, {proj} stack [{shape.experts}, {N}, {K}], "
+                                      f"{len(tok)} rows of dY ~ N(0, 1e-3)",
+                          "tokens": tokens, "value": us, "unit": "us/call", "rows": len(tok), "active_experts": len(eids),
+                          "roofline": _roofline(shape, proj, len(tok), len(eids), us, peaks, dgrad=True), "max_rel_err": err})
+
+    plan = [lambda: fwd_cell("qwen3_30b_a3b", 0, one_row_groups=64), lambda: fwd_cell("qwen3_30b_a3b", 8),
+            lambda: fwd_cell("qwen3_30b_a3b", 64), lambda: fwd_cell("qwen3_30b_a3b", 4096),
+            lambda: dgrad_cell("qwen3_30b_a3b", 4096),
+            lambda: fwd_cell("gpt_oss_20b", 1), lambda: fwd_cell("gpt_oss_20b", 0, one_row_groups=32),
+            lambda: fwd_cell("gpt_oss_20b", 4096)]
+    for job in plan:
+        try:
+            job()
+        except Exception as exc:      # a cell must never cost the headline
+            cells.append({"workload": "cell failed", "error": f"{type(exc).__name__}: {str(exc)[:200]}"})
+    return cells
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -482,6 +662,7 @@ def main():
     ap.add_argument("--layers", type=int, default=16)
     ap.add_argument("--repeats", type=int, default=7)
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-cells", action="store_true", help="skip the extra cells (other batch sizes, MXFP4, dgrad)")
     ap.add_argument("--path", type=lambda v: int(v, 0), default=0,
                     help="kernel choice / ablation flags of the device-resident timed region (0 = the planner)")
     ap.add_argument("--random-bytes", action="store_true",
@@ -502,19 +683,12 @@ def main():
         job_tokens = args.tokens * n
         cpu_cut = None if job_tokens * shape.top_k <= 2048 else 2
         cb = time_cpu(shape, job_tokens, args.steps, args.warmup, seed=7, max_rows_per_group=cpu_cut, budget_s=120.0)
-        if n == 1:
-            workload = (f"{shape.name} {shape.fmt} MoE layer, {args.tokens} tokens per GPU, top-{shape.top_k} of "
-                        f"{shape.experts} experts, gate_up {shape.gate_up} + down {shape.down}")
-        else:
-            workload = (f"{shape.name} {shape.fmt} MoE layer, expert-parallel over {n} GPUs "
-                        f"({shape.experts // n} experts per GPU), {args.tokens} tokens per GPU, top-{shape.top_k}, "
-                        f"dispatch/combine by NCCL all_to_all")
         print(json.dumps({
             "impl": "reference", "metric": "grouped 4-bit MoE GEMM us/layer", "value": cb["value"], "unit": "us/layer",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": cb["value"] / 1e3,
             "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
             "dtype": "fp32 activations x 4-bit weights, fp32 accumulate (CPU)", "data": "synthetic",
-            "config": {"workload": workload, "tokens": args.tokens},
+            "config": workload_config(shape, args.tokens, args.layers, n),
             "cpu_baseline": cb,
             "e2e": {"value": cb["value"], "unit": "us/layer", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0,
