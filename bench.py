@@ -350,16 +350,32 @@ def run_gpu(args, shape, rank, world):
             torch.distributed.barrier()
         torch.cuda.synchronize()
 
+    import mxfp4_grouped
+
+    def layer_ffn(i):
+        """The layer as the fused expert FFN on device-resident inputs: gate_up, activation and down in one call
+        (ONE kernel launch while every group has one row); the down input is the layer's own intermediate."""
+        (gu, dn), d = layers[i % args.layers], dsteps[i]
+        if shape.fmt == "nf4":
+            return nf4_grouped.ffn_4bit_grouped(d["a"], gu[0], gu[1], dn[0], dn[1], None, d["eids"], group_offsets=d["off"],
+                                                max_rows=d["max_rows"], tables_ready=True)
+        return mxfp4_grouped.ffn_mxfp4_grouped(d["a"], gu[0], gu[1], dn[0], dn[1], None, d["eids"], group_offsets=d["off"],
+                                               max_rows=d["max_rows"], tables_ready=True,
+                                               act="gpt_oss" if shape.name.startswith("gpt_oss") else "silu")
+
+    ffn_ok = shape.gate_up[0] == 2 * shape.down[1]
+
     def capture(what):
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
+        step = layer_ffn if what == "ffn" else (lambda i: layer_resident(i, what))
         with torch.cuda.stream(side):
-            layer_resident(W, what)
+            step(W)
         torch.cuda.current_stream().wait_stream(side)
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
             for i in range(W, W + K):
-                layer_resident(i, what)
+                step(i)
         return g
 
     def timed_replay(g, repeats, min_seconds=0.0):
@@ -381,13 +397,17 @@ def run_gpu(args, shape, rank, world):
         layer_resident(i)
     g_layer = capture("both")
     g_gu = capture("gate_up")
+    g_ffn = capture("ffn") if ffn_ok else None
     g_layer.replay()
     g_gu.replay()
+    if g_ffn is not None:
+        g_ffn.replay()
     torch.cuda.synchronize()
 
     with ClockSampler(dev.index) as clk:
         t_layer = timed_replay(g_layer, args.repeats, min_seconds=0.5)
         t_gu = timed_replay(g_gu, args.repeats)
+        t_ffn = timed_replay(g_ffn, args.repeats) if g_ffn is not None else None
         # end to end with host inputs and a host result: through the host-buffer C entry point (the
         # headline e2e), and through the tensor entry points with torch doing the copies
         e2e_t = time_e2e(layer_e2e_host)
@@ -457,6 +477,12 @@ def run_gpu(args, shape, rank, world):
                   "rows_per_active_expert": rows_per_group, "active_experts": statistics.mean(act)},
         "clocks": clk.summary(), "device_status": status, "repeats_ms": t_layer[:16],
     }
+    if t_ffn is not None:
+        one_launch = all(d["max_rows"] == 1 for d in dsteps[W:])
+        line["ffn"] = {"value": statistics.median(t_ffn) * 1e3 / K, "unit": "us/layer",
+                       "launches_per_layer": 1 if one_launch else 3,
+                       "api": "ffn_4bit_grouped / ffn_mxfp4_grouped on device-resident inputs (gnf4b_ffn_grouped): gate_up, "
+                              "activation and down GEMM in one call -- more work than `value`, which leaves the activation out"}
     if ms_e2e_ffn is not None:
         if world > 1:
             t = torch.tensor([ms_e2e_ffn], device=dev)
@@ -467,7 +493,8 @@ def run_gpu(args, shape, rank, world):
             "h2d_bytes_per_step": statistics.mean(s["a"].numel() * 2 + (2 * len(s["sizes"]) + 2) * 4 for s in steps[W:]),
             "d2h_bytes_per_step": d2h_dev,
             "api": "gnf4b_ffn_grouped_host (nf4_grouped.HostGroupedFfn): gate_up GEMM, SiLU-GLU, down GEMM in one "
-                   "blocking host call per layer; three kernels, the intermediate stays on the device"}
+                   "blocking host call per layer (one fused kernel launch at one row per group); the intermediate stays "
+                   "on the device"}
     if world == 1 and not args.no_cells:
         del dsteps, host_runs, host_ffns
         t0 = time.perf_counter()

@@ -31,6 +31,8 @@ SPLITK_SHIFT = 8
 FLAG_CTA_PAIR = 0x20000           # forward tensor kernel as CTA pairs (cta_group::2) instead of single CTAs
 FLAG_SMEM_OPERANDS = 0x10000      # ablation: forward on the kernel with both MMA operands in shared memory
 FLAG_TABLES_READY = 0x40000       # the group tables were not written by the kernel launched just before
+FLAG_FFN_UNFUSED = 0x100000       # ablation: gnf4b_ffn_grouped as three launches even where it would fuse
+ACT_SILU_GLU, ACT_GPT_OSS_GLU = 0, 1
 FLAG_DECODE_ONE_ROW = 0x80000     # ablation: decode kernel with one weight row per warp in flight, not two
 ST_BAD_EXPERT, ST_BAD_OFFSETS, ST_TIMEOUT = 1, 2, 4
 NOALLOC_SCRATCH_BYTES = 8 << 20
@@ -92,6 +94,14 @@ def _declare(lib):
     lib.gnf4b_ffn_grouped_host.argtypes = [
         C.c_int, vp, C.c_int, i64, vp, i64, i64, vp, i64, i64, vp, i64, i64, vp, i64, i64, C.c_int,
         vp, vp, i32, i32, i64, i64, i64, vp, vp, sz, vp, u32, vp]
+    lib.gnf4b_ffn_grouped.restype = C.c_int
+    lib.gnf4b_ffn_grouped.argtypes = [
+        C.c_int, C.c_int, vp, C.c_int, i64, vp, i64, i64, vp, i64, i64, vp, i64, i64, vp, i64, i64, C.c_int,
+        vp, vp, vp, i32, i32, i64, i64, i64, i32, vp, vp, sz, vp, u32, vp]
+    lib.gnf4b_ffn_workspace_bytes.restype = sz
+    lib.gnf4b_ffn_workspace_bytes.argtypes = [C.c_int, i64, i32, i64, i64, i64, i32, u32]
+    lib.gnf4b_glu_gpt_oss.restype = C.c_int
+    lib.gnf4b_glu_gpt_oss.argtypes = [vp, i64, i64, vp, vp, vp, vp]
     lib.gnf4b_ffn_host_staging_bytes.restype = sz
     lib.gnf4b_ffn_host_staging_bytes.argtypes = [C.c_int, i64, i32, i64, i64, i64, u32]
     lib.gnf4b_host_staging_bytes.restype = sz
@@ -124,7 +134,8 @@ def _declare(lib):
 #: every symbol include/gnf4b.h declares
 EXPORTS = ("gnf4b_abi_version", "gnf4b_strerror", "gnf4b_last_cuda_error", "gnf4b_gemm_grouped",
            "gnf4b_gemm_grouped_noalloc", "gnf4b_gemm_grouped_host", "gnf4b_host_staging_bytes",
-           "gnf4b_ffn_grouped_host", "gnf4b_ffn_host_staging_bytes",
+           "gnf4b_ffn_grouped_host", "gnf4b_ffn_host_staging_bytes", "gnf4b_ffn_grouped", "gnf4b_ffn_workspace_bytes",
+           "gnf4b_glu_gpt_oss",
            "gnf4b_workspace_bytes", "gnf4b_plan_split_k", "gnf4b_build_offsets", "gnf4b_upload_i32", "gnf4b_dequant", "gnf4b_silu_glu", "gnf4b_combine_rows", "gnf4b_ep_plan", "gnf4b_ep_offsets", "gnf4b_route_topk",
            "gnf4b_device_info")
 

@@ -193,6 +193,24 @@ __device__ __forceinline__ uint16_t f32_to_bf16_bits(float x) {
     return __bfloat16_as_ushort(__float2bfloat16_rn(x));
 }
 
+__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+__device__ __forceinline__ float silu_f32(float x) { return x / (1.0f + expf(-x)); }
+
+// The GLU of gpt-oss on one (gate, up) pair of bf16 values: gate clamped from above at 7, up clamped to [-7, 7],
+// (up + 1) * gate * sigmoid(1.702 gate) -- evaluated the way the reference evaluates it, as a chain of bf16 tensor
+// operations (kernel/mxfp4_pipelined.py:453-461): every intermediate is computed in fp32 and rounded to bf16.
+// Returns the bf16-representable result as a float.
+__device__ __forceinline__ float glu_gpt_oss(float gate, float up) {
+    const float g = fminf(gate, 7.0f);
+    const float u = fminf(fmaxf(up, -7.0f), 7.0f);
+    const float t1 = bf16_round(__fmul_rn(g, 1.702f));
+    const float t2 = bf16_round(1.0f / (1.0f + expf(-t1)));
+    const float t3 = bf16_round(__fmul_rn(g, t2));
+    const float t4 = bf16_round(__fadd_rn(u, 1.0f));
+    return bf16_round(__fmul_rn(t4, t3));
+}
+
 // Problem description shared by all GEMM kernels.
 struct GemmArgs {
     const void* x;          // activations / grad rows

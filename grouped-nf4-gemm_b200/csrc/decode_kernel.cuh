@@ -162,6 +162,102 @@ __device__ __forceinline__ float ld_shared_scale(uint32_t row_addr, int idx) {
     return __uint_as_float(e >= 2 ? (e - 1) << 23 : 0x00200000u << e);
 }
 
+// The rows of one ring stage that belong to this warp (w, w + CW, ..., RW of them in flight at a time), each
+// against the RM activation rows in xr: decode, FMA, block scale per unit, warp-shuffle reduce, one bf16 store per
+// (activation row, weight row) by lane 0 at out0[m * out_stride + r] for m < m_valid.  `st` is the shared-window
+// address of the stage: `rows` packed rows of row_bytes, then (from R * row_bytes on) their scale rows.
+template <int FMT, int SDT, int AU, int RM, int RW, int XF, int CW, int XN>
+__device__ __forceinline__ void consume_rows(uint32_t st, int R, int rows, int row_bytes, int scale_row_bytes, int n_units,
+                                             int warp, int lane, uint32_t lane8, const uint32_t (&xr)[RM][XN],
+                                             uint16_t* out0, int64_t out_stride, int m_valid) {
+    for (int r = warp; r < rows; r += CW * RW) {
+        // RW rows of the stage: r, r + CW, ...; one past the end repeats the last valid row (its result is not
+        // stored)
+        uint32_t wrow[RW], srow[RW];
+        float acc[RW][RM];
+#pragma unroll
+        for (int j = 0; j < RW; ++j) {
+            const int rj = min(r + j * CW, rows - 1);
+            wrow[j] = st + (uint32_t)(rj * row_bytes);
+            srow[j] = st + (uint32_t)(R * row_bytes + rj * scale_row_bytes);
+#pragma unroll
+            for (int m = 0; m < RM; ++m) acc[j][m] = 0.f;
+        }
+#pragma unroll
+        for (int q = 0; q < AU; ++q) {
+            const int u = lane + 32 * q;
+            if (u < n_units) {
+                constexpr int kPerUnit = XN / AU, kPerWord = kPerUnit / 4;
+                uint4 wv[RW];
+                float sc[RW];
+                float part[RW][RM][4];
+#pragma unroll
+                for (int j = 0; j < RW; ++j) {
+                    wv[j] = ld_shared_u32x4(wrow[j] + u * 16);
+                    sc[j] = ld_shared_scale<SDT>(srow[j], (FMT == GNF4B_FMT_NF4) ? (u >> 1) : u);
+#pragma unroll
+                    for (int m = 0; m < RM; ++m)
+#pragma unroll
+                        for (int b = 0; b < 4; ++b) part[j][m][b] = 0.f;
+                }
+                // one table lookup per byte serves all activation rows of the pass; word by word and row by
+                // row, so that few looked-up pairs are live at a time
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+#pragma unroll
+                    for (int j = 0; j < RW; ++j) {
+                        const uint32_t word = i == 0 ? wv[j].x : i == 1 ? wv[j].y : i == 2 ? wv[j].z : wv[j].w;
+                        word_fma<RM, XF, XN>(word, lane8, xr, q * kPerUnit + i * kPerWord, part[j]);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < RW; ++j)
+#pragma unroll
+                    for (int m = 0; m < RM; ++m)
+                        acc[j][m] += ((part[j][m][0] + part[j][m][1]) + (part[j][m][2] + part[j][m][3])) * sc[j];
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < RW; ++j) {
+#pragma unroll
+            for (int m = 0; m < RM; ++m) {
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) acc[j][m] += __shfl_xor_sync(0xffffffffu, acc[j][m], o);
+                if (lane == 0 && m < m_valid && r + j * CW < rows)
+                    out0[(int64_t)m * out_stride + r + j * CW] = f32_to_bf16_bits(acc[j][m]);
+            }
+        }
+    }
+}
+
+// The lookup table of word_fma, one 256-byte row per packed byte value, built by CW warps from instruction
+// immediates (no constant memory).  XF < 2: 32 slots of float2, all holding the byte's pair of codebook values, so
+// a lane reading slot == its lane id never conflicts with another lane; a half warp writes one row per step with
+// 16-byte stores.  XF = 2: 32 slots of bf16 pairs in the first 128 bytes of the row.
+template <int FMT, int XF, int CW>
+__device__ __forceinline__ void build_lookup_table(int warp, int lane) {
+    const float mine = code_value_imm<FMT>((uint32_t)lane & 15u);
+    if (XF == 2) {
+        for (int b = warp; b < 256; b += CW) {
+            const float e0 = __shfl_sync(0xffffffffu, mine, (FMT == GNF4B_FMT_NF4) ? (b >> 4) : (b & 15));
+            const float e1 = __shfl_sync(0xffffffffu, mine, (FMT == GNF4B_FMT_NF4) ? (b & 15) : (b >> 4));
+            const uint32_t v = (__float_as_uint(e0) >> 16) | (__float_as_uint(e1) & 0xffff0000u);
+            asm volatile("st.shared.u32 [%0], %1;" ::"r"((uint32_t)kDTabAbs + b * 256 + lane * 4), "r"(v) : "memory");
+        }
+    } else {
+        const int half = lane >> 4, hl = lane & 15;
+#pragma unroll 4
+        for (int b0 = warp * 2; b0 < 256; b0 += CW * 2) {
+            const int b = b0 + half;
+            const float e0 = __shfl_sync(0xffffffffu, mine, (FMT == GNF4B_FMT_NF4) ? (b >> 4) : (b & 15));
+            const float e1 = __shfl_sync(0xffffffffu, mine, (FMT == GNF4B_FMT_NF4) ? (b & 15) : (b >> 4));
+            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"((uint32_t)kDTabAbs + b * 256 + hl * 16),
+                         "f"(e0), "f"(e1), "f"(e0), "f"(e1)
+                         : "memory");
+        }
+    }
+}
+
 struct DGroup {
     int32_t row0, eid, rows;
     bool valid;
@@ -383,33 +479,8 @@ __global__ void __launch_bounds__(decode_threads(RM, AU), 1) decode_gemv_kernel(
     const bool early = a.tables_ready != 0 && item_lo < item_hi;
     DGroupRaw raw0 = {0, 0, 0};
     if (early) raw0 = decode_group_load(a, w.g);
-    {
-        // Lookup table, one 256-byte row per packed byte value, built from instruction immediates (no constant
-        // memory).  XF < 2: 32 slots of float2, all holding the byte's pair of codebook values, so a lane reading
-        // slot == its lane id never conflicts with another lane; a half warp writes one row per step with 16-byte
-        // stores.  XF = 2: 32 slots of bf16 pairs in the first 128 bytes of the row.  Built before pdl_wait(): it
-        // overlaps the tail of the previous kernel.
-        const float mine = code_value_imm<FMT>((uint32_t)lane & 15u);
-        if (XF == 2) {
-            for (int b = warp; b < 256; b += kCW) {
-                const float e0 = __shfl_sync(0xffffffffu, mine, (FMT == GNF4B_FMT_NF4) ? (b >> 4) : (b & 15));
-                const float e1 = __shfl_sync(0xffffffffu, mine, (FMT == GNF4B_FMT_NF4) ? (b & 15) : (b >> 4));
-                const uint32_t v = (__float_as_uint(e0) >> 16) | (__float_as_uint(e1) & 0xffff0000u);
-                asm volatile("st.shared.u32 [%0], %1;" ::"r"((uint32_t)kDTabAbs + b * 256 + lane * 4), "r"(v) : "memory");
-            }
-        } else {
-            const int half = lane >> 4, hl = lane & 15;
-#pragma unroll 4
-            for (int b0 = warp * 2; b0 < 256; b0 += kCW * 2) {
-                const int b = b0 + half;
-                const float e0 = __shfl_sync(0xffffffffu, mine, (FMT == GNF4B_FMT_NF4) ? (b >> 4) : (b & 15));
-                const float e1 = __shfl_sync(0xffffffffu, mine, (FMT == GNF4B_FMT_NF4) ? (b & 15) : (b >> 4));
-                asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"((uint32_t)kDTabAbs + b * 256 + hl * 16),
-                             "f"(e0), "f"(e1), "f"(e0), "f"(e1)
-                             : "memory");
-            }
-        }
-    }
+    // built before pdl_wait(): it overlaps the tail of the previous kernel
+    build_lookup_table<FMT, XF, kCW>(warp, lane);
     if (early) {
         grp = decode_group_check(a, raw0, w.c);
         cur_v = w.v;
@@ -441,67 +512,10 @@ __global__ void __launch_bounds__(decode_threads(RM, AU), 1) decode_gemv_kernel(
         }
         if (!poisoned && !mbar_wait_bounded(full_bar + stage, phase, abort_flag)) poisoned = true;
         if (!poisoned && grp.valid) {
-            const uint32_t st = smem_u32(ring + (size_t)stage * a.slot_bytes);
             const int n0 = tile * R;
-            const int rows = min(R, (int)(a.g.N - n0));
-            for (int r = warp; r < rows; r += kCW * RW) {
-                // RW rows of the stage: r, r + kCW, ...; one past the end repeats the last valid row (its result
-                // is not stored)
-                uint32_t wrow[RW], srow[RW];
-                float acc[RW][RM];
-#pragma unroll
-                for (int j = 0; j < RW; ++j) {
-                    const int rj = min(r + j * kCW, rows - 1);
-                    wrow[j] = st + (uint32_t)(rj * a.row_bytes);
-                    srow[j] = st + (uint32_t)(R * a.row_bytes + rj * a.scale_row_bytes);
-#pragma unroll
-                    for (int m = 0; m < RM; ++m) acc[j][m] = 0.f;
-                }
-#pragma unroll
-                for (int q = 0; q < AU; ++q) {
-                    const int u = lane + 32 * q;
-                    if (u < n_units) {
-                        constexpr int kPerUnit = kXN / AU, kPerWord = kPerUnit / 4;
-                        uint4 wv[RW];
-                        float sc[RW];
-                        float part[RW][RM][4];
-#pragma unroll
-                        for (int j = 0; j < RW; ++j) {
-                            wv[j] = ld_shared_u32x4(wrow[j] + u * 16);
-                            sc[j] = ld_shared_scale<SDT>(srow[j], (FMT == GNF4B_FMT_NF4) ? (u >> 1) : u);
-#pragma unroll
-                            for (int m = 0; m < RM; ++m)
-#pragma unroll
-                                for (int b = 0; b < 4; ++b) part[j][m][b] = 0.f;
-                        }
-                        // one table lookup per byte serves all activation rows of the pass; word by word and row by
-                        // row, so that few looked-up pairs are live at a time
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-#pragma unroll
-                            for (int j = 0; j < RW; ++j) {
-                                const uint32_t word = i == 0 ? wv[j].x : i == 1 ? wv[j].y : i == 2 ? wv[j].z : wv[j].w;
-                                word_fma<RM, XF, kXN>(word, lane8, xr, q * kPerUnit + i * kPerWord, part[j]);
-                            }
-                        }
-#pragma unroll
-                        for (int j = 0; j < RW; ++j)
-#pragma unroll
-                            for (int m = 0; m < RM; ++m)
-                                acc[j][m] += ((part[j][m][0] + part[j][m][1]) + (part[j][m][2] + part[j][m][3])) * sc[j];
-                    }
-                }
-#pragma unroll
-                for (int j = 0; j < RW; ++j) {
-#pragma unroll
-                    for (int m = 0; m < RM; ++m) {
-#pragma unroll
-                        for (int o = 16; o > 0; o >>= 1) acc[j][m] += __shfl_xor_sync(0xffffffffu, acc[j][m], o);
-                        if (lane == 0 && m < grp.rows && r + j * kCW < rows)
-                            out_bf[(int64_t)(grp.row0 + m) * a.g.N + n0 + r + j * kCW] = f32_to_bf16_bits(acc[j][m]);
-                    }
-                }
-            }
+            consume_rows<FMT, SDT, AU, RM, RW, XF, kCW, kXN>(
+                smem_u32(ring + (size_t)stage * a.slot_bytes), R, min(R, (int)(a.g.N - n0)), a.row_bytes,
+                a.scale_row_bytes, n_units, warp, lane, lane8, xr, out_bf + (int64_t)grp.row0 * a.g.N + n0, a.g.N, grp.rows);
         }
         __syncwarp();
         if (!poisoned && lane == 0) mbar_arrive_relaxed(empty_bar + stage);

@@ -7,8 +7,6 @@
 
 namespace gnf4b {
 
-__device__ __forceinline__ float silu_f32(float x) { return x / (1.0f + expf(-x)); }
-
 // out[r, c] = bf16( silu(gate[r, c]) * up[r, c] ), gate = gu[:, :h], up = gu[:, h:], fp32 math.
 // VEC = 8 (h % 8 == 0, 16-byte aligned rows) or 1.
 template <int VEC>
@@ -35,6 +33,25 @@ __global__ void silu_glu_kernel(const uint16_t* __restrict__ gu, int64_t rows, i
             const float gf = bf16_bits_to_float(g[0]), uf = bf16_bits_to_float(g[h]);
             out[r * h + c] = f32_to_bf16_bits(__fmul_rn(silu_f32(gf), uf));
         }
+    }
+}
+
+// out[r, c] = glu_gpt_oss(gu[r, 2c] (+ bias[e, 2c]), gu[r, 2c + 1] (+ bias[e, 2c + 1])), e = row_expert[r]: the
+// activation of gpt-oss between its two expert GEMMs, gate and up interleaved in the columns.  The optional
+// per-expert bias is added first, in bf16 like the reference does (kernel/mxfp4_pipelined.py:441-442).
+__global__ void glu_gpt_oss_kernel(const uint16_t* __restrict__ gu, int64_t rows, int64_t h, const uint16_t* __restrict__ bias,
+                                   const int32_t* __restrict__ row_expert, uint16_t* __restrict__ out) {
+    const int64_t total = rows * h;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / h, c = i - r * h;
+        const uint32_t pair = __ldg(reinterpret_cast<const uint32_t*>(gu + r * 2 * h) + c);
+        float g = __uint_as_float(pair << 16), u = __uint_as_float(pair & 0xffff0000u);
+        if (bias) {
+            const uint32_t bp = __ldg(reinterpret_cast<const uint32_t*>(bias + (int64_t)__ldg(row_expert + r) * 2 * h) + c);
+            g = bf16_round(__fadd_rn(g, __uint_as_float(bp << 16)));
+            u = bf16_round(__fadd_rn(u, __uint_as_float(bp & 0xffff0000u)));
+        }
+        out[i] = f32_to_bf16_bits(glu_gpt_oss(g, u));
     }
 }
 

@@ -15,6 +15,7 @@
 #include "tensor_kernel.cuh"
 #include "tensor_fwd_kernel.cuh"
 #include "ep_kernels.cuh"
+#include "ffn_kernel.cuh"
 
 namespace gnf4b {
 
@@ -261,6 +262,41 @@ static cudaError_t launch_decode_au(const DecodeArgs& da, int au, int rm, int rw
         if (au <= 1) return launch_decode_one<FMT, SDT, 1, 2, 1, X0>(da, grid, smem, st);
         if (au == 2) return launch_decode_one<FMT, SDT, 2, 2, 1, X0>(da, grid, smem, st);
         if (au == 3) return launch_decode_one<FMT, SDT, 3, 2, 1, X0>(da, grid, smem, st);
+    }
+    return cudaErrorInvalidValue;
+}
+
+template <int FMT, int SDT, int AU, int RW, int XF, int ACT>
+static cudaError_t launch_ffn_one(const FfnArgs& fa, int grid, size_t smem, cudaStream_t st) {
+    auto kfn = ffn_decode_kernel<FMT, SDT, AU, RW, XF, ACT>;
+    static int granted[64];
+    cudaError_t e = ensure_smem(kfn, smem, granted);
+    if (e != cudaSuccess) return e;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kFfnThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kfn, fa);
+}
+
+template <int FMT, int SDT, int ACT>
+static cudaError_t launch_ffn_au(const FfnArgs& fa, int au, int rw, int grid, size_t smem, cudaStream_t st) {
+    constexpr int X1 = (FMT == GNF4B_FMT_MXFP4) ? 2 : 1;
+    constexpr int X0 = (FMT == GNF4B_FMT_MXFP4) ? 2 : 0;
+    if (rw == 2) {
+        if (au <= 1) return launch_ffn_one<FMT, SDT, 1, 2, X1, ACT>(fa, grid, smem, st);
+        if (au == 2) return launch_ffn_one<FMT, SDT, 2, 2, X0, ACT>(fa, grid, smem, st);
+        if (au == 3) return launch_ffn_one<FMT, SDT, 3, 2, X0, ACT>(fa, grid, smem, st);
+    } else {
+        if (au <= 1) return launch_ffn_one<FMT, SDT, 1, 1, X1, ACT>(fa, grid, smem, st);
+        if (au == 2) return launch_ffn_one<FMT, SDT, 2, 1, X0, ACT>(fa, grid, smem, st);
+        if (au == 3) return launch_ffn_one<FMT, SDT, 3, 1, X0, ACT>(fa, grid, smem, st);
     }
     return cudaErrorInvalidValue;
 }
@@ -702,35 +738,12 @@ int gnf4b_gemm_grouped_host(int fmt, int op, const void* x_host, int x_dtype, in
     return GNF4B_OK;
 }
 
-// ---- host-buffer expert FFN: gate_up GEMM -> SiLU(gate) * up -> down GEMM, one round trip -----------
-// Staging: [ workspace (larger of the two GEMMs' worst cases) | offsets, ids, status | x | gate_up | h | out ]
+// ---- host-buffer expert FFN: one round trip around gnf4b_ffn_grouped -----------------------------------------
+// Staging: [ workspace of gnf4b_ffn_grouped (worst case over routings) | offsets, ids, status | x | out ]
 struct FfnStaging {
-    size_t tab = 0, x = 0, gu = 0, h = 0, out = 0, total = 0;
-    size_t ws_bytes = 0, tab_bytes = 0, x_bytes = 0, gu_bytes = 0, h_bytes = 0, out_bytes = 0;
+    size_t tab = 0, x = 0, out = 0, total = 0;
+    size_t ws_bytes = 0, tab_bytes = 0, x_bytes = 0, out_bytes = 0;
 };
-
-static int ffn_staging_layout(int fmt, int64_t T, int32_t G, int64_t N_gu, int64_t K_gu, int64_t N_dn, uint32_t flags,
-                              const DevInfo& di, FfnStaging* f) {
-    HostStaging a, b;
-    int rc = host_staging_layout(fmt, GNF4B_OP_FWD, T, G, N_gu, K_gu, flags, di, &a);
-    if (rc) return rc;
-    rc = host_staging_layout(fmt, GNF4B_OP_FWD, T, G, N_dn, N_gu / 2, flags, di, &b);
-    if (rc) return rc;
-    auto up = [](size_t v) { return (size_t)round_up((int64_t)v, 256); };
-    f->ws_bytes = std::max(a.ws_bytes, b.ws_bytes);
-    f->tab_bytes = a.tab_bytes;
-    f->x_bytes = a.x_bytes;
-    f->gu_bytes = a.out_bytes;
-    f->h_bytes = b.x_bytes;
-    f->out_bytes = b.out_bytes;
-    f->tab = up(f->ws_bytes);
-    f->x = f->tab + up(f->tab_bytes);
-    f->gu = f->x + up(f->x_bytes);
-    f->h = f->gu + up(f->gu_bytes);
-    f->out = f->h + up(f->h_bytes);
-    f->total = f->out + up(f->out_bytes);
-    return GNF4B_OK;
-}
 
 static int ffn_check(int fmt, int x_dtype, int s_dtype, int64_t T, int32_t G, int32_t E, int64_t N_gu, int64_t K_gu,
                      int64_t N_dn) {
@@ -739,6 +752,217 @@ static int ffn_check(int fmt, int x_dtype, int s_dtype, int64_t T, int32_t G, in
     if (x_dtype != GNF4B_X_BF16) return GNF4B_EUNSUPPORTED;      // the GLU kernel writes bf16
     if (N_gu % 2) return GNF4B_ESHAPE;
     return check_shape(fmt, GNF4B_OP_FWD, x_dtype, s_dtype, T, G, E, N_dn, N_gu / 2);
+}
+
+int gnf4b_build_offsets(const int32_t* sizes, int32_t G, int32_t* group_offsets, void* cuda_stream) {
+    if (G < 0 || !group_offsets || (G > 0 && !sizes)) return GNF4B_EINVAL;
+    offsets_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(cuda_stream)>>>(sizes, G, group_offsets);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "offsets kernel launch");
+    return GNF4B_OK;
+}
+
+int gnf4b_upload_i32(const int32_t* host_src, int32_t* device_dst, int64_t n, void* cuda_stream) {
+    if (n < 0 || (n > 0 && (!host_src || !device_dst))) return GNF4B_EINVAL;
+    if (n == 0) return GNF4B_OK;
+    cudaError_t e = cudaMemcpyAsync(device_dst, host_src, (size_t)n * 4, cudaMemcpyHostToDevice,
+                                    reinterpret_cast<cudaStream_t>(cuda_stream));
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(group tables)");
+    return GNF4B_OK;
+}
+
+int gnf4b_silu_glu(const void* gate_up, int64_t rows, int64_t h, void* out, void* cuda_stream) {
+    if (rows < 0 || h <= 0 || (rows > 0 && (!gate_up || !out))) return GNF4B_EINVAL;
+    if (rows == 0) return GNF4B_OK;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(cuda_stream);
+    const bool vec = (h % 8) == 0 && ((reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+    const int64_t work = rows * (vec ? h / 8 : h);
+    const int grid = (int)std::min<int64_t>(ceil_div(work, 256), 148 * 16);
+    if (vec)
+        silu_glu_kernel<8><<<grid, 256, 0, st>>>(static_cast<const uint16_t*>(gate_up), rows, h, static_cast<uint16_t*>(out));
+    else
+        silu_glu_kernel<1><<<grid, 256, 0, st>>>(static_cast<const uint16_t*>(gate_up), rows, h, static_cast<uint16_t*>(out));
+    cudaError_t e = cudaPeekAtLastError();
+    return e == cudaSuccess ? GNF4B_OK : cuda_fail(e, "silu_glu launch");
+}
+
+int gnf4b_glu_gpt_oss(const void* gate_up, int64_t rows, int64_t h, const void* bias, const int32_t* row_expert,
+                      void* out, void* cuda_stream) {
+    if (rows < 0 || h <= 0 || (rows > 0 && (!gate_up || !out)) || (bias && !row_expert)) return GNF4B_EINVAL;
+    if (rows == 0) return GNF4B_OK;
+    if ((reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(bias)) & 3) return GNF4B_EINVAL;
+    const int grid = (int)std::min<int64_t>(ceil_div(rows * h, 256), 148 * 16);
+    glu_gpt_oss_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(cuda_stream)>>>(
+        static_cast<const uint16_t*>(gate_up), rows, h, static_cast<const uint16_t*>(bias), row_expert,
+        static_cast<uint16_t*>(out));
+    cudaError_t e = cudaPeekAtLastError();
+    return e == cudaSuccess ? GNF4B_OK : cuda_fail(e, "glu_gpt_oss launch");
+}
+
+// ---- expert FFN on device pointers: one fused launch for one-row groups, three launches otherwise ----------
+// Workspace: [ counters (G + 1) int32 | gate_up bf16 [T, N_gu] | h bf16 [T, N_gu / 2] | GEMM scratch ]
+struct FfnWs {
+    size_t counters = 0, gu = 0, h = 0, gemm = 0, total = 0, gemm_bytes = 0, gemm_counters = 0;
+};
+
+static int ffn_ws_layout(int fmt, int64_t T, int32_t G, int64_t N_gu, int64_t K_gu, int64_t N_dn, int32_t max_rows,
+                         uint32_t flags, const DevInfo& di, FfnWs* w) {
+    auto up = [](size_t v) { return (size_t)round_up((int64_t)v, 256); };
+    size_t gemm = 0, gemm_counters = 0;
+    for (int xdt : {GNF4B_X_BF16}) {
+        Plan a, b;
+        int rc = make_plan(fmt, GNF4B_OP_FWD, xdt, T, G, N_gu, K_gu, max_rows, flags & GNF4B_PATH_MASK, di, &a);
+        if (rc) return rc;
+        rc = make_plan(fmt, GNF4B_OP_FWD, xdt, T, G, N_dn, N_gu / 2, max_rows, flags & GNF4B_PATH_MASK, di, &b);
+        if (rc) return rc;
+        gemm = std::max(gemm, std::max(a.counters_bytes + a.ws_bytes, b.counters_bytes + b.ws_bytes));
+        gemm_counters = std::max(gemm_counters, std::max(a.counters_bytes, b.counters_bytes));
+    }
+    w->counters = 0;
+    w->gu = up((size_t)(G + 1) * 4);
+    w->h = w->gu + up((size_t)T * (size_t)N_gu * 2);
+    w->gemm = w->h + up((size_t)T * (size_t)(N_gu / 2) * 2);
+    w->gemm_bytes = gemm;
+    w->gemm_counters = gemm_counters;
+    w->total = w->gemm + up(gemm);
+    return GNF4B_OK;
+}
+
+size_t gnf4b_ffn_workspace_bytes(int fmt, int64_t T, int32_t G, int64_t N_gu, int64_t K_gu, int64_t N_dn,
+                                 int32_t max_rows, uint32_t flags) {
+    if (ffn_check(fmt, GNF4B_X_BF16, fmt == GNF4B_FMT_NF4 ? GNF4B_S_F32 : GNF4B_S_E8M0, T, G, 1, N_gu, K_gu, N_dn)) return 0;
+    DevInfo di;
+    if (device_info(&di)) return 0;
+    FfnWs w;
+    if (ffn_ws_layout(fmt, T, G, N_gu, K_gu, N_dn, max_rows, flags, di, &w)) return 0;
+    return w.total;
+}
+
+int gnf4b_ffn_grouped(int fmt, int act, const void* x, int x_dtype, int64_t T,
+                      const uint8_t* W_gu, int64_t wgu_stride_e, int64_t wgu_stride_n,
+                      const void* S_gu, int64_t sgu_stride_e, int64_t sgu_stride_n,
+                      const uint8_t* W_dn, int64_t wdn_stride_e, int64_t wdn_stride_n,
+                      const void* S_dn, int64_t sdn_stride_e, int64_t sdn_stride_n, int s_dtype,
+                      const void* bias_gu, const int32_t* group_offsets, const int32_t* expert_ids, int32_t G, int32_t E,
+                      int64_t N_gu, int64_t K_gu, int64_t N_dn, int32_t max_rows, void* out, void* workspace,
+                      size_t workspace_bytes, int32_t* status_word, uint32_t flags, void* cuda_stream) {
+    int rc = ffn_check(fmt, x_dtype, s_dtype, T, G, E, N_gu, K_gu, N_dn);
+    if (rc) return rc;
+    if (act != GNF4B_ACT_SILU_GLU && act != GNF4B_ACT_GPT_OSS_GLU) return GNF4B_EINVAL;
+    if (T == 0 || G == 0) return GNF4B_OK;
+    if (!x || !W_gu || !S_gu || !W_dn || !S_dn || !group_offsets || !expert_ids || !out || !workspace) return GNF4B_EINVAL;
+    if (((uintptr_t)x | (uintptr_t)out | (uintptr_t)workspace | (uintptr_t)bias_gu) & 15) return GNF4B_EINVAL;
+    DevInfo di;
+    rc = device_info(&di);
+    if (rc) return rc;
+    FfnWs w;
+    rc = ffn_ws_layout(fmt, T, G, N_gu, K_gu, N_dn, max_rows, flags, di, &w);
+    if (rc) return rc;
+    if (workspace_bytes < w.total) return GNF4B_EWORKSPACE;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(cuda_stream);
+    unsigned char* base = static_cast<unsigned char*>(workspace);
+    const int64_t H = N_gu / 2;
+
+    // ---- the fused launch: every group one row, short rows, contiguous 16-byte aligned stacks
+    const int elt = (s_dtype == GNF4B_S_F32) ? 4 : (s_dtype == GNF4B_S_BF16 ? 2 : 1);
+    const int64_t blk = (fmt == GNF4B_FMT_NF4) ? 64 : 32;
+    const int64_t rb[2] = {K_gu / 2, H / 2}, srow[2] = {(K_gu / blk) * elt, (H / blk) * elt};
+    auto contiguous = [&](const uint8_t* W, int64_t w_se, int64_t w_sn, const void* S, int64_t s_se, int64_t s_sn, int p) {
+        return w_sn == rb[p] && s_sn * elt == srow[p] && (((uintptr_t)W | (uint64_t)w_se) & 15) == 0 &&
+               (((uintptr_t)S | (uint64_t)(s_se * elt)) & 15) == 0 && ((8 * srow[p]) & 15) == 0;
+    };
+    const int au = (int)ceil_div(std::max(K_gu, H), 1024);
+    const bool fused = max_rows == 1 && !(flags & GNF4B_FLAG_FFN_UNFUSED) && au <= 3 && (N_gu % 8) == 0 && (N_dn % 8) == 0 &&
+                 contiguous(W_gu, wgu_stride_e, wgu_stride_n, S_gu, sgu_stride_e, sgu_stride_n, 0) &&
+                 contiguous(W_dn, wdn_stride_e, wdn_stride_n, S_dn, sdn_stride_e, sdn_stride_n, 1) &&
+                 (act == GNF4B_ACT_SILU_GLU || fmt == GNF4B_FMT_MXFP4);
+    if (fused) {
+        FfnArgs fa;
+        const int64_t room = (int64_t)di.smem_optin - (int64_t)ffn_smem_bytes(0, 0, (int)H);
+        const int64_t per_row = std::max(rb[0] + srow[0], rb[1] + srow[1]);
+        // 32 weight rows per stage (two per warp in flight) when three such stages fit the ring, else 16
+        int R = 32, rw = 2;
+        if (3 * round_up(R * per_row, 128) > room) { R = 16; rw = 1; }
+        fa.slot_bytes = (int32_t)round_up(R * per_row, 128);
+        fa.stages = (int32_t)std::min<int64_t>(kDMaxStages, room / fa.slot_bytes);
+        const int64_t N[2] = {N_gu, N_dn};
+        int64_t items_max = 0;
+        for (int p = 0; p < 2; ++p) items_max = std::max(items_max, (int64_t)G * ceil_div(N[p], R));
+        if (fa.stages >= 3 && items_max < ((int64_t)1 << 31)) {
+            const int grid = (int)std::min<int64_t>(di.sm_count, items_max);
+            const uint8_t* Wp[2] = {W_gu, W_dn};
+            const void* Sp[2] = {S_gu, S_dn};
+            const int64_t wse[2] = {wgu_stride_e, wdn_stride_e}, sse[2] = {sgu_stride_e, sdn_stride_e};
+            for (int p = 0; p < 2; ++p) {
+                FfnPhase& ph = fa.ph[p];
+                ph.W = Wp[p]; ph.S = Sp[p]; ph.w_se = wse[p]; ph.s_se = sse[p];
+                ph.N = (int32_t)N[p];
+                ph.rows_per_stage = R;
+                ph.tiles_per_group = (int32_t)ceil_div(N[p], R);
+                ph.row_bytes = (int32_t)rb[p];
+                ph.scale_row_bytes = (int32_t)srow[p];
+                const int64_t items = (int64_t)G * ph.tiles_per_group;
+                ph.items_per_cta = (int32_t)(items / grid);
+                ph.items_extra = (int32_t)(items % grid);
+            }
+            fa.x = x; fa.off = group_offsets; fa.eids = expert_ids;
+            fa.bias_gu = static_cast<const uint16_t*>(bias_gu);
+            fa.gu = reinterpret_cast<uint16_t*>(base + w.gu);
+            fa.out = static_cast<uint16_t*>(out);
+            fa.counters = reinterpret_cast<int32_t*>(base + w.counters);
+            fa.status = status_word;
+            fa.T = T; fa.G = G; fa.E = E; fa.K_gu = (int32_t)K_gu; fa.H = (int32_t)H;
+            fa.tables_ready = (flags & GNF4B_FLAG_TABLES_READY) ? 1 : 0;
+            const size_t smem = ffn_smem_bytes(fa.slot_bytes, fa.stages, (int)H);
+            cudaError_t e;
+            const bool gpt = act == GNF4B_ACT_GPT_OSS_GLU;
+            if (fmt == GNF4B_FMT_NF4 && s_dtype == GNF4B_S_F32)
+                e = launch_ffn_au<GNF4B_FMT_NF4, GNF4B_S_F32, 0>(fa, au, rw, grid, smem, st);
+            else if (fmt == GNF4B_FMT_NF4)
+                e = launch_ffn_au<GNF4B_FMT_NF4, GNF4B_S_BF16, 0>(fa, au, rw, grid, smem, st);
+            else if (gpt)
+                e = launch_ffn_au<GNF4B_FMT_MXFP4, GNF4B_S_E8M0, 1>(fa, au, rw, grid, smem, st);
+            else
+                e = launch_ffn_au<GNF4B_FMT_MXFP4, GNF4B_S_E8M0, 0>(fa, au, rw, grid, smem, st);
+            if (e != cudaSuccess) return cuda_fail(e, "fused FFN launch");
+            return GNF4B_OK;
+        }
+    }
+
+    // ---- three launches, the intermediates in the workspace
+    if (bias_gu) return GNF4B_EUNSUPPORTED;          // the bias needs the fused kernel's group walk
+    void* gemm_ws = w.gemm_bytes ? base + w.gemm : nullptr;
+    rc = gnf4b_gemm_grouped(fmt, GNF4B_OP_FWD, x, x_dtype, T, W_gu, wgu_stride_e, wgu_stride_n, S_gu, s_dtype, sgu_stride_e,
+                            sgu_stride_n, group_offsets, expert_ids, G, E, N_gu, K_gu, max_rows, base + w.gu, gemm_ws,
+                            w.gemm_bytes, status_word, flags & ~GNF4B_FLAG_FFN_UNFUSED, cuda_stream);
+    if (rc) return rc;
+    rc = act == GNF4B_ACT_SILU_GLU ? gnf4b_silu_glu(base + w.gu, T, H, base + w.h, cuda_stream)
+                                   : gnf4b_glu_gpt_oss(base + w.gu, T, H, nullptr, nullptr, base + w.h, cuda_stream);
+    if (rc) return rc;
+    return gnf4b_gemm_grouped(fmt, GNF4B_OP_FWD, base + w.h, x_dtype, T, W_dn, wdn_stride_e, wdn_stride_n, S_dn, s_dtype,
+                              sdn_stride_e, sdn_stride_n, group_offsets, expert_ids, G, E, N_dn, H, max_rows, out, gemm_ws,
+                              w.gemm_bytes, status_word, flags & ~GNF4B_FLAG_FFN_UNFUSED, cuda_stream);
+}
+
+static int ffn_staging_layout(int fmt, int64_t T, int32_t G, int64_t N_gu, int64_t K_gu, int64_t N_dn, uint32_t flags,
+                              const DevInfo& di, FfnStaging* f) {
+    auto up = [](size_t v) { return (size_t)round_up((int64_t)v, 256); };
+    size_t worst = 0;
+    for (int32_t mr : {1, -1}) {
+        FfnWs w;
+        const int rc = ffn_ws_layout(fmt, T, G, N_gu, K_gu, N_dn, mr, flags, di, &w);
+        if (rc) return rc;
+        worst = std::max(worst, w.total);
+    }
+    f->ws_bytes = worst;
+    f->tab_bytes = (size_t)(2 * (int64_t)G + 2) * 4;
+    f->x_bytes = (size_t)T * (size_t)K_gu * 2;
+    f->out_bytes = (size_t)T * (size_t)N_dn * 2;
+    f->tab = up(f->ws_bytes);
+    f->x = f->tab + up(f->tab_bytes);
+    f->out = f->x + up(f->x_bytes);
+    f->total = f->out + up(f->out_bytes);
+    return GNF4B_OK;
 }
 
 size_t gnf4b_ffn_host_staging_bytes(int fmt, int64_t T, int32_t G, int64_t N_gu, int64_t K_gu, int64_t N_dn,
@@ -781,11 +1005,8 @@ int gnf4b_ffn_grouped_host(int fmt, const void* x_host, int x_dtype, int64_t T,
     rc = ffn_staging_layout(fmt, T, G, N_gu, K_gu, N_dn, flags, di, &f);
     if (rc) return rc;
     if (staging_bytes < f.total) return GNF4B_EWORKSPACE;
-    const int64_t H = N_gu / 2;
-    Plan p_gu, p_dn;
-    rc = make_plan(fmt, GNF4B_OP_FWD, x_dtype, T, G, N_gu, K_gu, max_rows, flags, di, &p_gu);
-    if (rc) return rc;
-    rc = make_plan(fmt, GNF4B_OP_FWD, x_dtype, T, G, N_dn, H, max_rows, flags, di, &p_dn);
+    FfnWs w;
+    rc = ffn_ws_layout(fmt, T, G, N_gu, K_gu, N_dn, max_rows, flags, di, &w);
     if (rc) return rc;
 
     cudaStream_t st = reinterpret_cast<cudaStream_t>(cuda_stream);
@@ -820,23 +1041,15 @@ int gnf4b_ffn_grouped_host(int fmt, const void* x_host, int x_dtype, int64_t T,
         if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(x)");
     }
     auto fail = [&](int code) { cudaStreamSynchronize(st); return code; };   // queued copies read host memory
-    if (p_gu.counters_bytes) {
-        e = cudaMemsetAsync(base, 0, p_gu.counters_bytes, st);
-        if (e != cudaSuccess) return fail(cuda_fail(e, "cudaMemsetAsync(arrival counters)"));
-    }
-    rc = gnf4b_gemm_grouped(fmt, GNF4B_OP_FWD, base + f.x, x_dtype, T, W_gu, wgu_stride_e, wgu_stride_n, S_gu, s_dtype,
-                            sgu_stride_e, sgu_stride_n, d_off, d_ids, G, E, N_gu, K_gu, max_rows, base + f.gu,
-                            f.ws_bytes ? base : nullptr, f.ws_bytes, d_status, flags | GNF4B_FLAG_TABLES_READY, cuda_stream);
-    if (rc) return fail(rc);
-    rc = gnf4b_silu_glu(base + f.gu, T, H, base + f.h, cuda_stream);
-    if (rc) return fail(rc);
-    if (p_dn.counters_bytes) {
-        e = cudaMemsetAsync(base, 0, p_dn.counters_bytes, st);
-        if (e != cudaSuccess) return fail(cuda_fail(e, "cudaMemsetAsync(arrival counters)"));
-    }
-    rc = gnf4b_gemm_grouped(fmt, GNF4B_OP_FWD, base + f.h, x_dtype, T, W_dn, wdn_stride_e, wdn_stride_n, S_dn, s_dtype,
-                            sdn_stride_e, sdn_stride_n, d_off, d_ids, G, E, N_dn, H, max_rows, base + f.out,
-                            f.ws_bytes ? base : nullptr, f.ws_bytes, d_status, flags | GNF4B_FLAG_TABLES_READY, cuda_stream);
+    // what must start at zero: the group counters of the fused launch and the arrival counters of split-K GEMMs
+    e = cudaMemsetAsync(base, 0, w.gu, st);
+    if (e == cudaSuccess && w.gemm_counters) e = cudaMemsetAsync(base + w.gemm, 0, w.gemm_counters, st);
+    if (e != cudaSuccess) return fail(cuda_fail(e, "cudaMemsetAsync(counters)"));
+    // the tables were uploaded by the copy above: ready when the kernels start
+    rc = gnf4b_ffn_grouped(fmt, GNF4B_ACT_SILU_GLU, base + f.x, x_dtype, T, W_gu, wgu_stride_e, wgu_stride_n, S_gu,
+                           sgu_stride_e, sgu_stride_n, W_dn, wdn_stride_e, wdn_stride_n, S_dn, sdn_stride_e, sdn_stride_n,
+                           s_dtype, nullptr, d_off, d_ids, G, E, N_gu, K_gu, N_dn, max_rows, base + f.out, base, w.total,
+                           d_status, flags | GNF4B_FLAG_TABLES_READY, cuda_stream);
     if (rc) return fail(rc);
     e = cudaMemcpyAsync(out_host, base + f.out, f.out_bytes, cudaMemcpyDeviceToHost, st);
     if (e != cudaSuccess) return fail(cuda_fail(e, "cudaMemcpyAsync(out)"));
@@ -847,38 +1060,6 @@ int gnf4b_ffn_grouped_host(int fmt, const void* x_host, int x_dtype, int64_t T,
     e = cudaStreamSynchronize(st);
     if (e != cudaSuccess) return cuda_fail(e, "cudaStreamSynchronize");
     return GNF4B_OK;
-}
-
-int gnf4b_build_offsets(const int32_t* sizes, int32_t G, int32_t* group_offsets, void* cuda_stream) {
-    if (G < 0 || !group_offsets || (G > 0 && !sizes)) return GNF4B_EINVAL;
-    offsets_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(cuda_stream)>>>(sizes, G, group_offsets);
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return cuda_fail(e, "offsets kernel launch");
-    return GNF4B_OK;
-}
-
-int gnf4b_upload_i32(const int32_t* host_src, int32_t* device_dst, int64_t n, void* cuda_stream) {
-    if (n < 0 || (n > 0 && (!host_src || !device_dst))) return GNF4B_EINVAL;
-    if (n == 0) return GNF4B_OK;
-    cudaError_t e = cudaMemcpyAsync(device_dst, host_src, (size_t)n * 4, cudaMemcpyHostToDevice,
-                                    reinterpret_cast<cudaStream_t>(cuda_stream));
-    if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(group tables)");
-    return GNF4B_OK;
-}
-
-int gnf4b_silu_glu(const void* gate_up, int64_t rows, int64_t h, void* out, void* cuda_stream) {
-    if (rows < 0 || h <= 0 || (rows > 0 && (!gate_up || !out))) return GNF4B_EINVAL;
-    if (rows == 0) return GNF4B_OK;
-    cudaStream_t st = reinterpret_cast<cudaStream_t>(cuda_stream);
-    const bool vec = (h % 8) == 0 && ((reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
-    const int64_t work = rows * (vec ? h / 8 : h);
-    const int grid = (int)std::min<int64_t>(ceil_div(work, 256), 148 * 16);
-    if (vec)
-        silu_glu_kernel<8><<<grid, 256, 0, st>>>(static_cast<const uint16_t*>(gate_up), rows, h, static_cast<uint16_t*>(out));
-    else
-        silu_glu_kernel<1><<<grid, 256, 0, st>>>(static_cast<const uint16_t*>(gate_up), rows, h, static_cast<uint16_t*>(out));
-    cudaError_t e = cudaPeekAtLastError();
-    return e == cudaSuccess ? GNF4B_OK : cuda_fail(e, "silu_glu launch");
 }
 
 int gnf4b_combine_rows(const void* rows, int64_t P, const int64_t* pos, const float* weights, int32_t k, int64_t M,

@@ -15,7 +15,7 @@ from __future__ import annotations
 import torch
 
 import _gnf4b
-from nf4_grouped import (_launch, _launch_host, _prefill_block_m, _require_cuda,  # noqa: F401  (re-exported names)
+from nf4_grouped import (_launch, _launch_ffn, _launch_host, _prefill_block_m, _require_cuda,  # noqa: F401  (re-exported names)
                          build_group_tiles)
 
 # e2m1 codebook, index = (sign << 3) | magnitude (ref :34-35)
@@ -54,6 +54,43 @@ def gemm_mxfp4_grouped(a_cat, blocks, scales, sizes, expert_ids,
         raise ValueError(f"a_cat has K={K} but blocks pack K={blocks.shape[2] * 2}")
     return _launch(_gnf4b.FMT_MXFP4, _gnf4b.OP_FWD, a_cat, blocks, scales, sizes, expert_ids, N,
                    group_offsets=group_offsets, max_rows=max_rows, path=path, tables_ready=tables_ready)
+
+
+def ffn_mxfp4_grouped(a_cat, blocks_gu, scales_gu, blocks_dn, scales_dn, sizes, expert_ids, *, act: str = "gpt_oss",
+                      bias_gu=None, group_offsets=None, max_rows=None, tables_ready: bool | None = None,
+                      fused: bool = True):
+    """One MXFP4 expert FFN per row on CUDA tensors: ``act(a @ W_gu[e].T (+ bias_gu[e])) @ W_dn[e].T``.
+    ``act="gpt_oss"``: gate and up interleaved in the gate_up columns, the clamped GLU of gpt-oss evaluated as the
+    reference's chain of bf16 tensor operations (``kernel/mxfp4_pipelined.py:440-445, 453-461``); ``act="silu"``:
+    SiLU(gate) * up over column halves.  ``bias_gu`` is an optional bf16 ``[E, N_gu]``.  Batch-1 decode (every group
+    one row) runs as ONE kernel launch; the down bias and the router-weighted sum stay with the caller (fp32 there)."""
+    if act not in ("gpt_oss", "silu"):
+        raise ValueError("act is 'gpt_oss' or 'silu'")
+    assert blocks_gu.dtype == torch.uint8 and scales_gu.dtype == torch.uint8
+    assert blocks_dn.dtype == torch.uint8 and scales_dn.dtype == torch.uint8
+    _require_cuda(a_cat, "ffn_mxfp4_grouped", "The CPU-checkable equivalent composes mxfp4_pack_ref.dequant_mxfp4 per expert.")
+    return _launch_ffn(_gnf4b.FMT_MXFP4, _gnf4b.ACT_GPT_OSS_GLU if act == "gpt_oss" else _gnf4b.ACT_SILU_GLU, a_cat,
+                       blocks_gu, scales_gu, blocks_dn, scales_dn, sizes, expert_ids, bias_gu=bias_gu,
+                       group_offsets=group_offsets, max_rows=max_rows, tables_ready=tables_ready, fused=fused)
+
+
+def glu_gpt_oss(gate_up, bias=None, row_expert=None):
+    """The activation of gpt-oss between its expert GEMMs as one kernel: ``gate_up [rows, 2h]`` bf16 (gate and up
+    interleaved) -> ``[rows, h]`` bf16; ``bias`` bf16 ``[E, 2h]`` is added first (row r takes ``bias[row_expert[r]]``)."""
+    _require_cuda(gate_up, "glu_gpt_oss", "")
+    gate_up = gate_up.contiguous()
+    rows, two_h = gate_up.shape
+    out = torch.empty(rows, two_h // 2, dtype=torch.bfloat16, device=gate_up.device)
+    if bias is not None:
+        bias = bias.contiguous()
+        row_expert = row_expert.to(torch.int32).contiguous()
+    lib = _gnf4b.load()
+    with torch.cuda.device(gate_up.device):
+        rc = lib.gnf4b_glu_gpt_oss(gate_up.data_ptr(), rows, two_h // 2, bias.data_ptr() if bias is not None else None,
+                                   row_expert.data_ptr() if bias is not None else None, out.data_ptr(),
+                                   torch.cuda.current_stream(gate_up.device).cuda_stream)
+    _gnf4b.check(rc, "gnf4b_glu_gpt_oss")
+    return out
 
 
 def gemm_mxfp4_grouped_host(a_host, blocks, scales, sizes, expert_ids, out=None, *, path: int = 0,

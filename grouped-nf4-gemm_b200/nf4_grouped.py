@@ -634,6 +634,102 @@ def dgrad_4bit_grouped(grad_out, B, absmax, sizes, expert_ids, config=None, *, g
 
 
 # --------------------------------------------------------------------------- #
+# expert FFN on CUDA tensors: gate_up GEMM -> activation -> down GEMM
+# --------------------------------------------------------------------------- #
+_FFN_WS = {}          # (device index, stream) -> zero-initialised uint8 workspace, grown on demand
+
+
+def _launch_ffn(fmt, act, x, W_gu, S_gu, W_dn, S_dn, sizes, expert_ids, *, bias_gu=None, group_offsets=None,
+                max_rows=None, tables_ready=None, fused=True):
+    """One expert FFN per row, ``gnf4b_ffn_grouped``: a single fused launch for one-row groups, three launches
+    otherwise.  ``x [T, K]`` bf16 -> bf16 ``[T, N_dn]``."""
+    dev = x.device
+    if x.dtype != torch.bfloat16:
+        raise TypeError(f"activations must be bfloat16, got {x.dtype}")
+    E, N_gu, half = W_gu.shape
+    K_gu = half * 2
+    N_dn = W_dn.shape[1]
+    T = x.shape[0]
+    if x.shape[1] != K_gu:
+        raise ValueError(f"activations have {x.shape[1]} columns, the gate_up stack contracts over {K_gu}")
+    if W_dn.shape[0] != E or N_gu % 2 or W_dn.shape[2] * 2 != N_gu // 2:
+        raise ValueError(f"down stack {tuple(W_dn.shape)} does not follow gate_up {tuple(W_gu.shape)}")
+    for t in (W_gu, S_gu, W_dn, S_dn):
+        if t.device != dev:
+            raise ValueError("activations, packed weights and scales must live on the same device")
+    if not x.is_contiguous() or x.data_ptr() % 16:
+        x = x.contiguous().clone() if x.data_ptr() % 16 else x.contiguous()
+    if W_gu.stride(2) != 1:
+        W_gu = W_gu.contiguous()
+    if W_dn.stride(2) != 1:
+        W_dn = W_dn.contiguous()
+    if fmt == _gnf4b.FMT_NF4:
+        if S_gu.dtype != S_dn.dtype or S_gu.dtype not in (torch.float32, torch.bfloat16):
+            S_gu, S_dn = S_gu.to(torch.float32), S_dn.to(torch.float32)
+        sdt = _gnf4b.S_F32 if S_gu.dtype == torch.float32 else _gnf4b.S_BF16
+    else:
+        sdt = _gnf4b.S_E8M0
+    if S_gu.stride(2) != 1:
+        S_gu = S_gu.contiguous()
+    if S_dn.stride(2) != 1:
+        S_dn = S_dn.contiguous()
+    if bias_gu is not None:
+        if bias_gu.dtype != torch.bfloat16 or tuple(bias_gu.shape) != (E, N_gu) or bias_gu.device != dev:
+            raise ValueError(f"bias_gu must be a bfloat16 tensor of shape ({E}, {N_gu}) on {dev}")
+        bias_gu = bias_gu.contiguous()
+    out = torch.empty(T, N_dn, dtype=torch.bfloat16, device=dev)
+    if T == 0:
+        return out
+    lib = _gnf4b.load()
+    prev = -1
+    if dev.index is not None and dev.index != torch.cuda.current_device():
+        prev = torch.cuda.current_device()
+        torch.cuda.set_device(dev)
+    try:
+        stream_ptr = _raw_stream(dev)
+        off_t, ids_t, G, max_rows = _group_tables(sizes, expert_ids, T, E, dev, group_offsets, max_rows, stream_ptr)
+        if G == 0:
+            return out
+        off_p = off_t if isinstance(off_t, int) else off_t.data_ptr()
+        ids_p = ids_t if isinstance(ids_t, int) else ids_t.data_ptr()
+        flags = 0 if fused else _gnf4b.FLAG_FFN_UNFUSED
+        if tables_ready is None:
+            tables_ready = group_offsets is None and not (torch.is_tensor(sizes) and sizes.is_cuda) \
+                and not (torch.is_tensor(expert_ids) and expert_ids.is_cuda)
+        if tables_ready:
+            flags |= _gnf4b.FLAG_TABLES_READY
+        need = lib.gnf4b_ffn_workspace_bytes(fmt, T, G, N_gu, K_gu, N_dn, max_rows, flags)
+        key = (dev.index, stream_ptr)
+        ws = _FFN_WS.get(key)
+        if ws is None or ws.numel() < need:
+            # zero-filled once: the kernels leave the counters in it zeroed after every call
+            ws = _FFN_WS[key] = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=dev)
+        rc = lib.gnf4b_ffn_grouped(
+            fmt, act, x.data_ptr(), _gnf4b.X_BF16, T, W_gu.data_ptr(), W_gu.stride(0), W_gu.stride(1),
+            S_gu.data_ptr(), S_gu.stride(0), S_gu.stride(1), W_dn.data_ptr(), W_dn.stride(0), W_dn.stride(1),
+            S_dn.data_ptr(), S_dn.stride(0), S_dn.stride(1), sdt, bias_gu.data_ptr() if bias_gu is not None else None,
+            off_p, ids_p, G, E, N_gu, K_gu, N_dn, max_rows, out.data_ptr(), ws.data_ptr(), ws.numel(),
+            _status_ptr(dev), flags, stream_ptr)
+    finally:
+        if prev >= 0:
+            torch.cuda.set_device(prev)
+    if rc:
+        _gnf4b.check(rc, "gnf4b_ffn_grouped")
+    return out
+
+
+def ffn_4bit_grouped(a_cat, B_gu, absmax_gu, B_dn, absmax_dn, sizes, expert_ids, *, group_offsets=None, max_rows=None,
+                     tables_ready: bool | None = None, fused: bool = True):
+    """One NF4 expert FFN per row on CUDA tensors: ``(silu(gate) * up) @ W_dn[e].T`` with ``[gate | up] = a @ W_gu[e].T``
+    -- the GPU counterpart of the reference's fused CPU FFN (``gnf4_native/cpu_kernels.c:763-986``).  For batch-1
+    decode (every group one row) it is ONE kernel launch; larger groups run as gate_up GEMM, GLU kernel, down GEMM.
+    Bit for bit ``gemm_4bit_grouped -> silu_glu -> gemm_4bit_grouped``.  ``fused=False`` forces the three launches."""
+    _require_cuda(a_cat, "ffn_4bit_grouped", "The CPU-checkable equivalent composes dequant_ref per expert.")
+    return _launch_ffn(_gnf4b.FMT_NF4, _gnf4b.ACT_SILU_GLU, a_cat, B_gu, absmax_gu, B_dn, absmax_dn, sizes, expert_ids,
+                       group_offsets=group_offsets, max_rows=max_rows, tables_ready=tables_ready, fused=fused)
+
+
+# --------------------------------------------------------------------------- #
 # host-buffer entry points (activations, group tables and result in host memory)
 # --------------------------------------------------------------------------- #
 _HOST_STAGING = {}    # (device index, thread id) -> uint8 CUDA tensor, grown on demand (a call blocks, so one

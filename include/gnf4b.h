@@ -56,6 +56,12 @@ extern "C" {
 #define GNF4B_FLAG_DECODE_ONE_ROW 0x80000u /* ablation: decode kernel with one weight row per warp in flight where it
                                             would keep two */
 
+#define GNF4B_FLAG_FFN_UNFUSED    0x100000u /* ablation: gnf4b_ffn_grouped as three launches even where one fused
+                                             launch would be taken */
+/* activations of gnf4b_ffn_grouped */
+#define GNF4B_ACT_SILU_GLU    0   /* SiLU(gate) * up, gate = the first half of the gate_up columns            */
+#define GNF4B_ACT_GPT_OSS_GLU 1   /* gpt-oss: gate / up interleaved, clamped at 7, (up+1) * gate * sigmoid(1.702 gate) */
+
 /* error codes */
 #define GNF4B_OK            0
 #define GNF4B_EINVAL       -1   /* bad enum / null pointer / negative size            */
@@ -218,6 +224,36 @@ int gnf4b_ffn_grouped_host(int fmt, const void* x_host, int x_dtype, int64_t T,
 size_t gnf4b_ffn_host_staging_bytes(int fmt, int64_t T, int32_t G, int64_t N_gu, int64_t K_gu, int64_t N_dn,
                                     uint32_t flags);
 
+/* One expert FFN per row on DEVICE pointers, on the stream, no synchronisation: out = act(x . W_gu[e]^T) . W_dn[e]^T.
+ * The GPU counterpart of the reference's fused CPU FFN gnf4_gemv_nf4_ffn_grouped (gnf4_native/cpu_kernels.c:763-986;
+ * its activation is GNF4B_ACT_SILU_GLU) and, with GNF4B_ACT_GPT_OSS_GLU and bias_gu, of the expert path of
+ * kernel/mxfp4_pipelined.py:440-445, 453-461 up to the down GEMM (the down bias and the router-weighted sum stay
+ * with the caller, in fp32 as there).
+ *
+ * When every group has one row (max_rows == 1: batch-1 decode), both contractions are at most 3072 long and the
+ * stacks are contiguous and 16-byte aligned, it is ONE persistent launch: gate_up GEMV, activation and down GEMV, the
+ * [T, N_gu] intermediate crossing L2 only, the down weights streaming into shared memory while gate_up is still
+ * being computed.  Otherwise (and with GNF4B_FLAG_FFN_UNFUSED) it is the three launches gnf4b_gemm_grouped ->
+ * activation kernel -> gnf4b_gemm_grouped.  Both give the same bits.
+ *
+ *   bias_gu    optional bf16 [E, N_gu] (16-byte aligned), added to the gate_up result in bf16 before the
+ *              activation; fused launch only (GNF4B_EUNSUPPORTED otherwise)
+ *   workspace  at least gnf4b_ffn_workspace_bytes(...) bytes, 256-byte aligned, zero-filled once before its first
+ *              use (the kernels leave it as they need it); holds the intermediates and the group counters of the
+ *              fused launch.  Calls that overlap on the GPU need separate workspaces.
+ * Every device-side wait of the fused launch is bounded: on expiry GNF4B_ST_TIMEOUT is raised and the results are
+ * void, nothing hangs.  GNF4B_ACT_GPT_OSS_GLU needs MXFP4 stacks on the fused path. */
+int gnf4b_ffn_grouped(int fmt, int act, const void* x, int x_dtype, int64_t T,
+                      const uint8_t* W_gu, int64_t wgu_stride_e, int64_t wgu_stride_n,
+                      const void* S_gu, int64_t sgu_stride_e, int64_t sgu_stride_n,
+                      const uint8_t* W_dn, int64_t wdn_stride_e, int64_t wdn_stride_n,
+                      const void* S_dn, int64_t sdn_stride_e, int64_t sdn_stride_n, int s_dtype,
+                      const void* bias_gu, const int32_t* group_offsets, const int32_t* expert_ids, int32_t G, int32_t E,
+                      int64_t N_gu, int64_t K_gu, int64_t N_dn, int32_t max_rows, void* out, void* workspace,
+                      size_t workspace_bytes, int32_t* status_word, uint32_t flags, void* cuda_stream);
+size_t gnf4b_ffn_workspace_bytes(int fmt, int64_t T, int32_t G, int64_t N_gu, int64_t K_gu, int64_t N_dn,
+                                 int32_t max_rows, uint32_t flags);
+
 /* Scratch gnf4b_gemm_grouped needs for the same arguments (0 when none).  Replaces the
  * `ws = torch.empty(sk, T, N)` split-K buffer of kernel/nf4_grouped.py:784. */
 size_t gnf4b_workspace_bytes(int fmt, int op, int64_t T, int32_t G, int64_t N, int64_t K,
@@ -259,6 +295,11 @@ int gnf4b_dequant(int fmt,
  * equal bit for bit to the same loop written with tensor operations.  rows is bf16 [P, H]; a position
  * outside [0, P) is skipped and flagged GNF4B_ST_BAD_OFFSETS in the status word. */
 int gnf4b_silu_glu(const void* gate_up, int64_t rows, int64_t h, void* out, void* cuda_stream);
+/* The activation of gpt-oss between its expert GEMMs (kernel/mxfp4_pipelined.py:453-461): gate_up [rows, 2h] bf16 with
+ * gate and up INTERLEAVED in the columns -> out [rows, h] bf16, every step rounded to bf16 as the reference's tensor
+ * operations do.  bias (optional, bf16 [E, 2h]) is added first, row r taking bias[row_expert[r]]. */
+int gnf4b_glu_gpt_oss(const void* gate_up, int64_t rows, int64_t h, const void* bias, const int32_t* row_expert,
+                      void* out, void* cuda_stream);
 int gnf4b_combine_rows(const void* rows, int64_t P, const int64_t* pos, const float* weights, int32_t k,
                        int64_t M, int64_t H, void* out, int32_t* status_word, void* cuda_stream);
 
