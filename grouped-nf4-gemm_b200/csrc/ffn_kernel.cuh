@@ -179,7 +179,22 @@ __global__ void __launch_bounds__(kFfnThreads, 1) ffn_decode_kernel(const FfnArg
     }
 
     // ---------------------------------------------------------------- consumers
+    // With ready tables the first group of either phase is read before the dependency wait (the loads fly while
+    // the table is built), and a hint brings the first activation row's lines into L2.
+    const bool early = a.tables_ready != 0;
+    FfnGroup first[2];
+#pragma unroll
+    for (int p = 0; p < 2; ++p) {
+        first[p].valid = false;
+        first[p].row0 = 0;
+        first[p].eid = 0;
+        if (early && lo[p] < hi[p]) first[p] = ffn_group(a, lo[p] / a.ph[p].tiles_per_group, false);
+    }
     build_lookup_table<FMT, XF, kFfnCW>(warp, lane);
+    if (early && warp == 0 && first[0].valid) {
+        const uint8_t* xrow = reinterpret_cast<const uint8_t*>(a.x) + (int64_t)first[0].row0 * a.K_gu * 2;
+        for (int o = lane * 128; o < a.K_gu * 2; o += 32 * 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(xrow + o));
+    }
     pdl_wait();
     named_bar_sync(1, kFfnCW * 32);
 
@@ -223,7 +238,12 @@ __global__ void __launch_bounds__(kFfnThreads, 1) ffn_decode_kernel(const FfnArg
         for (int item = lo[p]; item < hi[p]; ++item) {
             if (cur_g != g) {
                 publish();
-                grp = ffn_group(a, g, p == 0 && tile == 0);
+                if (early && item == lo[p]) {
+                    grp = first[p];
+                    if (p == 0 && tile == 0) (void)ffn_group(a, g, true);      // for its flags only
+                } else {
+                    grp = ffn_group(a, g, p == 0 && tile == 0);
+                }
                 cur_g = g;
                 if (p == 0) {
                     // the group's activation row
