@@ -47,9 +47,8 @@ BASELINE_US = {  # reference's published B200 numbers (fused Triton, gate_up + d
     ("qwen3_30b_a3b", 1): 185.0 + 100.0,       # decode_bs1
     ("qwen3_30b_a3b", 2048): 1428.0 + 794.0,   # prefill_s2048
 }
-# DRAM traffic of one gate_up launch (dram__bytes_read.sum + dram__bytes_write.sum, one ncu capture each; the
-# summaries and their commands are profiles/decode_gemv_kernel_qwen3_gate_up_m1.md and
-# profiles/tensor_fwd_kernel_qwen3_gate_up_m4096.md).  Other workloads: not captured, null.
+# DRAM traffic of one gate_up launch (dram__bytes_read.sum + dram__bytes_write.sum, one ncu capture each, summarised
+# with its command under profiles/).  Other workloads: not captured, null.
 NCU_TRAFFIC_BYTES = {
     ("qwen3_30b_a3b", 1): 14.22e6,                # = the algorithmic 14.21 MB: nothing re-read
     ("qwen3_30b_a3b", 4096): 360.8e6 + 85.6e6,    # weights once + activations + scales read, output written
@@ -125,6 +124,8 @@ def algorithmic(shape, proj, rows, active):
 
 def workload_config(shape, tokens, layers, n_gpus=1):
     """The `config` object of the JSON line; the same for both arms of a run."""
+    if n_gpus > 1:
+        layers = max(2, min(layers, 8))        # what the expert-parallel leg keeps resident per rank
     if n_gpus <= 1:
         workload = (f"{shape.name} {shape.fmt} MoE layer, {tokens} tokens per GPU, top-{shape.top_k} of "
                     f"{shape.experts} experts, gate_up {shape.gate_up} + down {shape.down}")
@@ -413,6 +414,18 @@ def run_gpu(args, shape, rank, world):
         e2e_t = time_e2e(layer_e2e_host)
         e2e_dev_t = time_e2e(layer_e2e)
         e2e_ffn_t = time_e2e(layer_e2e_ffn) if host_ffns else None
+        # the same layer the way the reference's own harness times its kernels (and the reference_triton key below):
+        # device-resident activations, host routing lists, eager calls, CUDA events around each layer pass
+        eager_us = []
+        for i in range(W, W + min(K, 60)):
+            (gu, dn), s, d = layers[i % args.layers], steps[i], dsteps[i]
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn(d["a"], gu[0], gu[1], s["sizes"], s["eids"])
+            fn(d["h"], dn[0], dn[1], s["sizes"], s["eids"])
+            e1.record()
+            torch.cuda.synchronize()
+            eager_us.append(e0.elapsed_time(e1) * 1e3)
     status = nf4_grouped.last_status(dev)
 
     ms_layer = statistics.median(t_layer)
@@ -470,6 +483,9 @@ def run_gpu(args, shape, rank, world):
                            "d2h_bytes_per_step": d2h_dev,
                            "api": f"{fn.__name__} on CUDA tensors, torch copies from pinned memory, final result "
                                   "read back"},
+        "eager_api": {"value": statistics.median(eager_us), "unit": "us/layer",
+                      "api": f"{fn.__name__} on device-resident activations with host routing lists, eager calls, CUDA events "
+                             "per layer pass (the method of the reference_triton key)"},
         "gpu_launches": 2 * K,
         "roofline": roof,
         "layer": {"decode_gbs": statistics.mean(by_l) / (us_layer * 1e-6) / 1e9,
@@ -678,12 +694,102 @@ def measure_cells(args, dev, peaks, default_layers):
     return cells
 
 
+# --------------------------------------------------------------------------- the reference's own GPU kernels
+def run_reference_triton(args, shape):
+    """Child-process mode (`--impl reference-triton`): the reference project's Triton kernels, through its public
+    entry points, on this GPU and this workload -- the "beat this" column.  Needs the reference installed under
+    baseline/_ref (git-ignored; `pip install --no-deps --target baseline/_ref <reference checkout>`); this
+    repository's package is NOT importable in this process.  Method of the reference's own harness
+    (bench/phase1/harness.py:915-930): eager calls, CUDA events, warm-up, median."""
+    ref = ROOT / "baseline" / "_ref"
+    if not (ref / "nf4_grouped.py").exists():
+        print(json.dumps({"unavailable": "the reference is not installed under baseline/_ref on this box"}))
+        return 0
+    sys.path[:] = [str(ref)] + [p for p in sys.path if "grouped-nf4-gemm_b200" not in p and p != str(ROOT)]
+    for name in ("nf4_grouped", "mxfp4_grouped", "synth", "_gnf4b"):
+        sys.modules.pop(name, None)
+    try:
+        import mxfp4_grouped as RM
+        import nf4_grouped as RN
+        assert str(ref) in RN.__file__, RN.__file__
+        dev = torch.device("cuda", 0)
+        gen = torch.Generator().manual_seed(5)
+        n_layers, n_steps = 4, 24
+        (n1, k1), (n2, k2) = shape.gate_up, shape.down
+        layers = []
+        for _ in range(n_layers):
+            pair = []
+            for (n, k) in ((n1, k1), (n2, k2)):
+                W = torch.randint(0, 256, (shape.experts, n, k // 2), dtype=torch.uint8, device=dev)
+                if shape.fmt == "nf4":
+                    S = torch.rand(shape.experts, n, k // 64, device=dev) * 0.05 + 0.01
+                else:
+                    S = torch.randint(119, 126, (shape.experts, n, k // 32), dtype=torch.uint8, device=dev)
+                pair.append((W, S))
+            layers.append(pair)
+        steps = []
+        for _ in range(n_steps):
+            logits = torch.randn(args.tokens, shape.experts, generator=gen)
+            idx = torch.argsort(-logits, dim=-1, stable=True)[:, :shape.top_k].reshape(-1)
+            uniq, counts = torch.unique_consecutive(idx[torch.argsort(idx, stable=True)], return_counts=True)
+            rows = int(counts.sum())
+            steps.append((torch.randn(rows, k1, generator=gen).to(torch.bfloat16).to(dev),
+                          torch.randn(rows, k2, generator=gen).to(torch.bfloat16).to(dev), counts.tolist(), uniq.tolist()))
+        fn = RN.gemm_4bit_grouped if shape.fmt == "nf4" else RM.gemm_mxfp4_grouped
+
+        def layer(i, what):
+            a, h, sizes, eids = steps[i % n_steps]
+            (Wg, Sg), (Wd, Sd) = layers[i % n_layers]
+            if what != "down":
+                fn(a, Wg, Sg, sizes, eids)
+            if what != "gate_up":
+                fn(h, Wd, Sd, sizes, eids)
+
+        def timed(what, n):
+            out = []
+            for i in range(n):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                layer(i, what)
+                e1.record()
+                torch.cuda.synchronize()
+                out.append(e0.elapsed_time(e1) * 1e3)
+            return statistics.median(out)
+
+        for i in range(10):
+            layer(i, "both")
+        torch.cuda.synchronize()
+        res = {"value": timed("both", 60), "unit": "us/layer", "gate_up_us": timed("gate_up", 60), "down_us": timed("down", 60),
+               "method": "reference Triton kernels through the reference's public entry points (baseline/_ref), eager calls with "
+                         "host routing lists, CUDA events per layer pass, 10 warm-up passes, median of 60",
+               "triton": __import__("triton").__version__}
+        print(json.dumps(res))
+    except Exception as exc:
+        print(json.dumps({"unavailable": f"{type(exc).__name__}: {str(exc)[:300]}"}))
+    return 0
+
+
+def reference_triton_key(args):
+    """Run the mode above in a child process (its imports must not meet this package's modules of the same names)
+    and return its JSON object."""
+    try:
+        r = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference-triton", "--tokens", str(args.tokens),
+                            "--config", args.config], capture_output=True, text=True, timeout=600)
+        lines = [ln for ln in r.stdout.splitlines() if ln.startswith("{")]
+        if lines:
+            return json.loads(lines[-1])
+        return {"unavailable": f"child exited {r.returncode}: {r.stderr[-200:]}"}
+    except Exception as exc:
+        return {"unavailable": f"{type(exc).__name__}: {str(exc)[:200]}"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-triton"])
+    ap.add_argument("--no-triton", action="store_true", help="skip the reference_triton key (the reference's own GPU kernels)")
     ap.add_argument("--tokens", type=int, default=1, help="tokens per GPU per layer pass (1 = batch-1 decode)")
     ap.add_argument("--config", default="qwen3_30b_a3b", choices=sorted(synth.CONFIGS))
     ap.add_argument("--layers", type=int, default=16)
@@ -702,6 +808,8 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", 1))
     cpu_cut = None if args.tokens * shape.top_k <= 2048 else 2
 
+    if args.impl == "reference-triton":
+        return run_reference_triton(args, shape)
     if args.impl == "reference":
         if rank != 0:
             return 0
@@ -726,6 +834,9 @@ def main():
         torch.distributed.init_process_group("nccl")
     line = run_gpu(args, shape, rank, world) if world == 1 else run_gpu_ep(args, shape, rank, world)
     if rank == 0:
+        if world == 1 and not args.no_triton:
+            torch.cuda.empty_cache()
+            line["reference_triton"] = reference_triton_key(args)
         if world == 1 and not args.no_cpu:
             try:
                 line["cpu_baseline"] = time_cpu(shape, args.tokens, 8, 3, seed=7, max_rows_per_group=cpu_cut)

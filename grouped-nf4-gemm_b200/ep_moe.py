@@ -455,6 +455,35 @@ def bench_ep(args, shape, rank, world, B):
                     phase[n].append(prev.elapsed_time(ev[n][j]) * 1e3)
                     prev = ev[n][j]
             m.timers = None
+    # parity on the real collectives: this rank's result of one step against the same layer computed WITHOUT any
+    # exchange from the gathered expert shards (a one-rank process group), same seeds
+    parity = None
+    try:
+        own = None
+        for r in range(world):
+            grp = dist.new_group([r])
+            if r == rank:
+                own = grp
+        (gu0, dn0) = layers[0]
+        full = []
+        for (Wl, Sl) in (gu0, dn0):
+            parts_w = [torch.empty_like(Wl) for _ in range(world)]
+            parts_s = [torch.empty_like(Sl) for _ in range(world)]
+            dist.all_gather(parts_w, Wl.contiguous())
+            dist.all_gather(parts_s, Sl.contiguous())
+            full.append((torch.cat(parts_w), torch.cat(parts_s)))
+        single = EPGroupedMoE(shape.experts, full[0], full[1], group=own, fmt=shape.fmt)
+        got = mods[0].forward(*dsteps[Wm]).float()
+        want = single.forward(*dsteps[Wm]).float()
+        lim = 2 * 2 ** -8 * want.abs().max()
+        ratio = torch.stack(((got - want).abs().max() / lim.clamp_min(1e-30), want.abs().max()))
+        dist.all_reduce(ratio, op=dist.ReduceOp.MAX)
+        parity = {"max_abs_diff_over_limit": ratio[0].item(), "limit": "2 * 2^-8 * max|reference| per rank",
+                  "ok": bool(ratio[0].item() <= 1.0),
+                  "what": "EP layer output of one step vs the same layer on one rank from the gathered shards, max over ranks"}
+        del single, full
+    except Exception as exc:      # never at the cost of the timing
+        parity = {"ok": None, "error": f"{type(exc).__name__}: {str(exc)[:200]}"}
     t = torch.tensor([statistics.median(t_res), t_e2e, float(statistics.mean(rows))], device=dev)
     tmax = t.clone()
     dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
@@ -489,18 +518,14 @@ def bench_ep(args, shape, rank, world, B):
         "metric": "grouped 4-bit MoE GEMM us/layer", "value": us_layer, "unit": "us/layer", "n_gpus": world,
         "steps": K, "warmup": Wm, "ms_per_step": ms_layer / K, "higher_is_better": False, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16 activations x 4-bit weights, fp32 accumulate", "data": "synthetic",
-        "config": {"workload": f"{shape.name} {shape.fmt} MoE layer, expert-parallel over {world} GPUs "
-                               f"({e_local} experts per GPU), {args.tokens} tokens per GPU, top-{shape.top_k}, "
-                               f"dispatch/combine by NCCL all_to_all",
-                   "tokens": args.tokens, "layers_resident": n_layers, "zipf": zipf,
-                   "l2": "inputs larger than L2 per step: resident layer stacks walked round-robin, fresh routing per step",
-                   "timing": timing},
+        "config": B.workload_config(shape, args.tokens, args.layers, world),
+        "method": {"layers_resident": n_layers, "zipf": zipf, "timing": timing},
         "e2e": {"value": ms_e2e * 1e3 / K, "unit": "us/layer",
                 "h2d_bytes_per_step": args.tokens * (shape.hidden * 2 + shape.top_k * 12),
                 "d2h_bytes_per_step": args.tokens * shape.hidden * 2},
         "gpu_launches": launches_per_layer * K,
         "roofline": roof,
-        "ep": {"phase_us_median": {n: statistics.median(v) for n, v in phase.items()},
+        "ep": {"parity": parity, "phase_us_median": {n: statistics.median(v) for n, v in phase.items()},
                "rows_per_rank_mean": rows_mean, "rows_per_rank_max": tmax[2].item(),
                "imbalance_max_over_mean": tmax[2].item() / max(rows_mean, 1e-9),
                "aggregate_tflops": fl / (us_layer * 1e-6) / 1e12},

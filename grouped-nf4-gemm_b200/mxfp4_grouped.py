@@ -15,7 +15,7 @@ from __future__ import annotations
 import torch
 
 import _gnf4b
-from nf4_grouped import (_launch, _launch_ffn, _launch_host, _prefill_block_m, _require_cuda,  # noqa: F401  (re-exported names)
+from nf4_grouped import (_dispatch, _launch, _launch_ffn, _launch_host, _prefill_block_m, _require_cuda,  # noqa: F401  (re-exported names)
                          build_group_tiles)
 
 # e2m1 codebook, index = (sign << 3) | magnitude (ref :34-35)
@@ -52,8 +52,8 @@ def gemm_mxfp4_grouped(a_cat, blocks, scales, sizes, expert_ids,
                   "mxfp4_pack_ref.dequant_mxfp4(blocks, scales).")
     if blocks.shape[2] * 2 != K:
         raise ValueError(f"a_cat has K={K} but blocks pack K={blocks.shape[2] * 2}")
-    return _launch(_gnf4b.FMT_MXFP4, _gnf4b.OP_FWD, a_cat, blocks, scales, sizes, expert_ids, N,
-                   group_offsets=group_offsets, max_rows=max_rows, path=path, tables_ready=tables_ready)
+    return _dispatch(_gnf4b.FMT_MXFP4, _gnf4b.OP_FWD, a_cat, blocks, scales, sizes, expert_ids, N,
+                     group_offsets=group_offsets, max_rows=max_rows, path=path, tables_ready=tables_ready)
 
 
 def ffn_mxfp4_grouped(a_cat, blocks_gu, scales_gu, blocks_dn, scales_dn, sizes, expert_ids, *, act: str = "gpt_oss",

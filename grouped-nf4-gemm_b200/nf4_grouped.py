@@ -193,14 +193,21 @@ class _IndexRing:
         return self.dev_ptr + lo * 4
 
 
-_RINGS: dict = {}
+_RINGS: dict = {}          # (device index, stream) -> _IndexRing, most recently used last
+_RINGS_MAX = 8             # 1 MiB pinned + 1 MiB device each: a process that cycles through streams keeps only these
 
 
 def _index_ring(dev, stream_ptr):
     key = (dev.index, stream_ptr)
-    r = _RINGS.get(key)
+    r = _RINGS.pop(key, None)
     if r is None:
-        r = _RINGS[key] = _IndexRing(dev)
+        while len(_RINGS) >= _RINGS_MAX:
+            # retire the least recently used ring once nothing can still read it
+            old = _RINGS.pop(next(iter(_RINGS)))
+            with torch.cuda.device(old.dev.device):
+                torch.cuda.synchronize()
+        r = _IndexRing(dev)
+    _RINGS[key] = r
     return r
 
 
@@ -537,6 +544,59 @@ def _launch(fmt, op, x, W, S, sizes, expert_ids, n_out, *, split_k=None, path=_g
     return out
 
 
+# --------------------------------------------------------------------------- #
+# torch.library registration: the grouped GEMM as a custom operator with a fake (meta) kernel, so that callers that
+# trace these entry points (torch.compile, torch.export) get one opaque node instead of a graph break
+# --------------------------------------------------------------------------- #
+try:
+    from typing import List, Optional
+
+    @torch.library.custom_op("gnf4b::grouped_gemm", mutates_args=())
+    def _grouped_gemm_op(x: torch.Tensor, W: torch.Tensor, S: torch.Tensor, group_offsets: Optional[torch.Tensor],
+                         expert_ids_t: Optional[torch.Tensor], sizes: Optional[List[int]], expert_ids: Optional[List[int]],
+                         fmt: int, op: int, n_out: int, max_rows: int, path: int, split_k: int,
+                         tables_ready: bool) -> torch.Tensor:
+        return _launch(fmt, op, x, W, S, sizes, expert_ids_t if expert_ids_t is not None else expert_ids, n_out,
+                       split_k=split_k if split_k > 0 else None, path=path, group_offsets=group_offsets,
+                       max_rows=max_rows if max_rows > 0 else None, tables_ready=tables_ready)
+
+    @_grouped_gemm_op.register_fake
+    def _grouped_gemm_fake(x, W, S, group_offsets, expert_ids_t, sizes, expert_ids, fmt, op, n_out, max_rows, path,
+                           split_k, tables_ready):
+        return x.new_empty((x.shape[0], n_out), dtype=torch.bfloat16)
+
+    _HAVE_OP = True
+except Exception:      # an older torch without torch.library.custom_op: the plain functions still work
+    _HAVE_OP = False
+
+
+def _tracing() -> bool:
+    try:
+        return _HAVE_OP and torch.compiler.is_compiling()
+    except Exception:
+        return False
+
+
+def _dispatch(fmt, op, x, W, S, sizes, expert_ids, n_out, *, split_k=None, path=_gnf4b.PATH_AUTO, group_offsets=None,
+              max_rows=None, tables_ready=None):
+    """_launch directly in eager mode (no dispatcher overhead on the decode path); through the registered operator
+    ``torch.ops.gnf4b.grouped_gemm`` while a compiler is tracing."""
+    if not _tracing():
+        return _launch(fmt, op, x, W, S, sizes, expert_ids, n_out, split_k=split_k, path=path,
+                       group_offsets=group_offsets, max_rows=max_rows, tables_ready=tables_ready)
+    ids_t = expert_ids if torch.is_tensor(expert_ids) else None
+    ids_l = None if ids_t is not None else [int(v) for v in expert_ids]
+    if torch.is_tensor(sizes):
+        sizes = None if group_offsets is not None else [int(v) for v in sizes.tolist()]
+    elif sizes is not None:
+        sizes = [int(v) for v in sizes]
+    if tables_ready is None:
+        tables_ready = group_offsets is None and ids_t is None
+    return torch.ops.gnf4b.grouped_gemm(x, W, S, group_offsets, ids_t, sizes, ids_l, fmt, op, n_out,
+                                        int(max_rows) if max_rows else 0, int(path), int(split_k) if split_k else 0,
+                                        bool(tables_ready))
+
+
 def _require_cuda(t, fn_name: str, hint: str):
     if t.device.type != "cuda":
         raise RuntimeError(
@@ -584,8 +644,8 @@ def gemm_4bit_grouped(a_cat, B, absmax, sizes, expert_ids, block_m: int | None =
         raise ValueError(f"a_cat has K={K} but B packs K={B.shape[2] * 2}")
     if tuple(absmax.shape) != (E, N, K // BLOCKSIZE):
         raise ValueError(f"absmax shape {tuple(absmax.shape)} != {(E, N, K // BLOCKSIZE)}")
-    return _launch(_gnf4b.FMT_NF4, _gnf4b.OP_FWD, a_cat, B, absmax, sizes, expert_ids, N, split_k=split_k,
-                   group_offsets=group_offsets, max_rows=max_rows, path=path, tables_ready=tables_ready)
+    return _dispatch(_gnf4b.FMT_NF4, _gnf4b.OP_FWD, a_cat, B, absmax, sizes, expert_ids, N, split_k=split_k,
+                     group_offsets=group_offsets, max_rows=max_rows, path=path, tables_ready=tables_ready)
 
 
 def dgrad_eligible(grad_out, B, absmax, block_k: int = 64):
@@ -629,8 +689,8 @@ def dgrad_4bit_grouped(grad_out, B, absmax, sizes, expert_ids, config=None, *, g
             "check dgrad_eligible() first rather than catching this.")
     if grad_out.shape[1] != N:
         raise ValueError(f"grad_out has {grad_out.shape[1]} columns but the stack has N={N}")
-    return _launch(_gnf4b.FMT_NF4, _gnf4b.OP_DGRAD, grad_out, B, absmax, sizes, expert_ids, K,
-                   group_offsets=group_offsets, max_rows=max_rows)
+    return _dispatch(_gnf4b.FMT_NF4, _gnf4b.OP_DGRAD, grad_out, B, absmax, sizes, expert_ids, K,
+                     group_offsets=group_offsets, max_rows=max_rows)
 
 
 # --------------------------------------------------------------------------- #

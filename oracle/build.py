@@ -27,7 +27,8 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 REF_DIR = HERE / "_ref"
 ORACLE_SO = HERE / "libgnf4_oracle.so"
-DEFAULT_REF_ROOT = Path(os.environ.get("GNF4_REFERENCE_ROOT", "/root/reference"))
+# the reference checkout: GNF4_REFERENCE_ROOT, else a directory named `reference` beside this repository
+DEFAULT_REF_ROOT = Path(os.environ.get("GNF4_REFERENCE_ROOT") or HERE.parent.parent / "reference")
 
 # name -> -march level; the loader tries them best-first
 REF_VARIANTS = (("avx512", "x86-64-v4"), ("avx2", "x86-64-v3"), ("base", "x86-64"))

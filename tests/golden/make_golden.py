@@ -34,7 +34,9 @@ if os.path.exists("/usr/bin/gcc"):      # the image default CC has no OpenMP spe
 os.environ.setdefault("GNF4_NATIVE_CACHE", "/tmp/gnf4_native_cache")
 sys.dont_write_bytecode = True
 
-REF = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+# the reference checkout: first argument, else GNF4_REFERENCE_ROOT, else a directory named `reference` beside this repository
+REF = Path(sys.argv[1] if len(sys.argv) > 1 else
+           os.environ.get("GNF4_REFERENCE_ROOT") or Path(__file__).resolve().parents[3] / "reference")
 sys.path[:0] = [str(REF / "kernel"), str(REF)]
 OUT = Path(__file__).resolve().parent
 

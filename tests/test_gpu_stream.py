@@ -504,3 +504,23 @@ def test_two_row_decode_keeps_stage_scale_spans_16_byte_aligned(K):
     assert torch.equal(out, general)
     assert rel_fro(out, oracle_fwd64("mxfp4", a, B, S, sizes, ids)) <= REL_FRO_TOL
     assert nf4_grouped.last_status(DEV) == 0
+
+
+def test_entry_points_trace_through_the_registered_operator():
+    """torch.compile (fullgraph: no graph break allowed) over a function that calls the NF4 and MXFP4 entry points
+    with device-side group tables: one opaque gnf4b::grouped_gemm node each, same bits as eager."""
+    gen = torch.Generator().manual_seed(31)
+    B, A = synth.nf4_stack(4, 128, 256, gen, device=DEV, fast=True)
+    Bm, Sm = synth.mxfp4_stack(4, 64, 128, gen, device=DEV, fast=True)
+    a = torch.randn(6, 256, generator=gen).to(torch.bfloat16).to(DEV)
+    off = torch.tensor([0, 2, 3, 6], dtype=torch.int32, device=DEV)
+    ids = torch.tensor([3, 0, 1], dtype=torch.int32, device=DEV)
+
+    def layer(x):
+        y = gemm_4bit_grouped(x, B, A, None, ids, group_offsets=off, max_rows=3)
+        return mxfp4_grouped.gemm_mxfp4_grouped(y, Bm, Sm, [2, 1, 3], [1, 1, 2]) * 2
+
+    want = layer(a)
+    got = torch.compile(layer, backend="aot_eager", fullgraph=True)(a)
+    assert torch.equal(got, want)
+    assert nf4_grouped.last_status(DEV) == 0

@@ -154,3 +154,64 @@ def test_c_abi_rejects_contract_violations_without_a_gpu():
     assert host([2, 2], [0, 4], 4) == (-1, 0)
     assert host([2, 2], [0, -2], 4) == (-1, 0)
     assert host([0, 0], [0, -1], 0) == (0, 0)            # nothing to do: OK without touching the device
+
+
+def test_repack_from_bnb_with_stand_in_state_objects(monkeypatch):
+    """repack_from_bnb (kernel/nf4_grouped.py:74-96 of the reference) on hand-made stand-ins for bitsandbytes'
+    per-expert outputs -- bitsandbytes itself is not installable here: packed bytes land as [E, N, K/2], absmax as
+    fp32 [E, N, K/64], and nested statistics (compress_statistics=True) are de-nested through
+    bitsandbytes.functional.dequantize_blockwise + offset."""
+    import sys
+    import types
+
+    E, N, K = 3, 8, 128
+    gen = torch.Generator().manual_seed(5)
+    packed = [torch.randint(0, 256, (N * K // 2, 1), dtype=torch.uint8, generator=gen) for _ in range(E)]
+    absmax = [torch.rand(N * K // 64, generator=gen) + 0.1 for _ in range(E)]
+
+    class State:
+        def __init__(self, am, nested=False, state2=None, offset=None):
+            self.absmax, self.nested, self.state2, self.offset = am, nested, state2, offset
+
+    # plain statistics
+    B, A = nf4_grouped.repack_from_bnb(packed, [State(a) for a in absmax], N, K)
+    assert B.shape == (E, N, K // 2) and B.dtype == torch.uint8 and A.shape == (E, N, K // 64) and A.dtype == torch.float32
+    for e in range(E):
+        assert torch.equal(B[e].reshape(-1), packed[e].reshape(-1))
+        assert torch.equal(A[e].reshape(-1), absmax[e])
+    # nested statistics: absmax stored as uint8 codes of (absmax - offset), decoded by a second-level quantiser
+    calls = []
+
+    def dequantize_blockwise(q, state2):
+        calls.append(state2)
+        return q.float() * state2["scale"]
+
+    fake = types.ModuleType("bitsandbytes")
+    fake.functional = types.ModuleType("bitsandbytes.functional")
+    fake.functional.dequantize_blockwise = dequantize_blockwise
+    monkeypatch.setitem(sys.modules, "bitsandbytes", fake)
+    monkeypatch.setitem(sys.modules, "bitsandbytes.functional", fake.functional)
+    offset = torch.tensor(0.25)
+    codes = [torch.randint(0, 256, (N * K // 64,), dtype=torch.uint8, generator=gen) for _ in range(E)]
+    states = [State(c, nested=True, state2={"scale": 1.0 / 512 * (e + 1)}, offset=offset) for e, c in enumerate(codes)]
+    B2, A2 = nf4_grouped.repack_from_bnb(packed, states, N, K)
+    assert len(calls) == E and torch.equal(B2, B)
+    for e in range(E):
+        want = (codes[e].float() * (1.0 / 512 * (e + 1)) + 0.25).reshape(N, K // 64)
+        assert torch.equal(A2[e], want)
+    with pytest.raises(AssertionError):
+        nf4_grouped.repack_from_bnb(packed, states, N, 100)        # K must be a multiple of the blocksize
+
+
+def test_custom_operator_is_registered_with_a_fake_kernel():
+    """torch.ops.gnf4b.grouped_gemm exists and its fake kernel gives shape, dtype and device of the result without
+    touching a GPU (what torch.compile / torch.export need to trace through the entry points)."""
+    assert hasattr(torch.ops.gnf4b, "grouped_gemm")
+    x = torch.empty(5, 128, dtype=torch.bfloat16, device="meta")
+    W = torch.empty(4, 64, 64, dtype=torch.uint8, device="meta")
+    S = torch.empty(4, 64, 2, dtype=torch.float32, device="meta")
+    out = torch.ops.gnf4b.grouped_gemm(x, W, S, None, None, [2, 3], [0, 1], 0, 0, 64, 3, 0, 0, True)
+    assert out.shape == (5, 64) and out.dtype == torch.bfloat16 and out.device.type == "meta"
+    go = torch.empty(5, 64, dtype=torch.bfloat16, device="meta")
+    dx = torch.ops.gnf4b.grouped_gemm(go, W, S, None, None, [2, 3], [0, 1], 0, 1, 128, 3, 0, 0, True)
+    assert dx.shape == (5, 128)
