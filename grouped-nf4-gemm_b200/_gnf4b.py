@@ -31,10 +31,12 @@ SPLITK_SHIFT = 8
 FLAG_CTA_PAIR = 0x20000           # forward tensor kernel as CTA pairs (cta_group::2) instead of single CTAs
 FLAG_SMEM_OPERANDS = 0x10000      # ablation: forward on the kernel with both MMA operands in shared memory
 FLAG_TABLES_READY = 0x40000       # the group tables were not written by the kernel launched just before
+FLAG_X_SILU_GLU, FLAG_X_GPT_OSS_GLU = 0x200000, 0x400000   # x is the gate_up output; the GLU is applied on load
 FLAG_FFN_UNFUSED = 0x100000       # ablation: gnf4b_ffn_grouped as three launches even where it would fuse
 ACT_SILU_GLU, ACT_GPT_OSS_GLU = 0, 1
 FLAG_DECODE_ONE_ROW = 0x80000     # ablation: decode kernel with one weight row per warp in flight, not two
 ST_BAD_EXPERT, ST_BAD_OFFSETS, ST_TIMEOUT = 1, 2, 4
+EUNSUPPORTED, ETOOBIG = -5, -6
 NOALLOC_SCRATCH_BYTES = 8 << 20
 
 _lib = None
@@ -126,9 +128,24 @@ def _declare(lib):
     lib.gnf4b_ep_plan.argtypes = [vp, i32, i32, i32, i32, i32, vp, i64, vp, vp, vp, vp, vp]
     lib.gnf4b_ep_offsets.restype = C.c_int
     lib.gnf4b_ep_offsets.argtypes = [vp, i32, i32, i32, vp, vp, vp]
+    lib.gnf4b_ep_peer_layout.restype = C.c_int
+    lib.gnf4b_ep_peer_layout.argtypes = [i32, i32, i32, i64, vp]
+    lib.gnf4b_ep_peer_dispatch.restype = C.c_int
+    lib.gnf4b_ep_peer_dispatch.argtypes = [vp, vp, i32, i32, i32, i32, vp, vp, i32, vp, vp, vp, vp]
+    lib.gnf4b_ep_peer_combine.restype = C.c_int
+    lib.gnf4b_ep_peer_combine.argtypes = [vp, i32, vp, vp, vp, i32, i64, vp, vp, vp]
     lib.gnf4b_device_info.restype = C.c_int
     lib.gnf4b_device_info.argtypes = [vp, vp]
     return lib
+
+
+EP_MAX_WORLD = 16
+
+
+class EpPeerCtx(C.Structure):
+    """gnf4b_ep_peer_ctx of include/gnf4b.h."""
+    _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("e_local", C.c_int32), ("cap_max", C.c_int32),
+                ("H", C.c_int64), ("peers", C.c_void_p * EP_MAX_WORLD)]
 
 
 #: every symbol include/gnf4b.h declares
@@ -137,6 +154,7 @@ EXPORTS = ("gnf4b_abi_version", "gnf4b_strerror", "gnf4b_last_cuda_error", "gnf4
            "gnf4b_ffn_grouped_host", "gnf4b_ffn_host_staging_bytes", "gnf4b_ffn_grouped", "gnf4b_ffn_workspace_bytes",
            "gnf4b_glu_gpt_oss",
            "gnf4b_workspace_bytes", "gnf4b_plan_split_k", "gnf4b_build_offsets", "gnf4b_upload_i32", "gnf4b_dequant", "gnf4b_silu_glu", "gnf4b_combine_rows", "gnf4b_ep_plan", "gnf4b_ep_offsets", "gnf4b_route_topk",
+           "gnf4b_ep_peer_layout", "gnf4b_ep_peer_dispatch", "gnf4b_ep_peer_combine",
            "gnf4b_device_info")
 
 

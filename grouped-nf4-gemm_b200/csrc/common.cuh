@@ -141,6 +141,13 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
 // completed and their writes are visible, so it must precede the first read of anything an earlier
 // kernel may have written and every global write.  pdl_launch_dependents() lets the NEXT kernel start
 // the same way.  Both are no-ops for a kernel launched without the attribute.
+#ifdef GNF4B_EP_TRACE
+__device__ unsigned long long g_ep_trace[8192];
+__device__ unsigned int g_ep_trace_n;
+#define EPT(id) do { if (threadIdx.x == 0 && blockIdx.x == 0) { unsigned i_ = atomicAdd(&g_ep_trace_n, 1u); if (i_ < 4096u) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); g_ep_trace[2 * i_] = (id); g_ep_trace[2 * i_ + 1] = t_; } } } while (0)
+#else
+#define EPT(id) do { } while (0)
+#endif
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 

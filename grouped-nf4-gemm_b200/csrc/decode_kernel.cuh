@@ -61,6 +61,7 @@ struct DecodeArgs {
     int32_t rows_per_pass;      // RM of the kernel instance
     int32_t compact;            // work list holds only (group, chunk) pairs that exist (prefix sum in shared memory)
     int32_t tables_ready;       // group_offsets / expert_ids were NOT written by the kernel launched just before
+    int32_t x_act;              // 0: x [T, K].  1 / 2: x is the gate_up output [T, 2K], SiLU-GLU / gpt-oss GLU applied on load
 };
 
 
@@ -258,6 +259,36 @@ __device__ __forceinline__ void build_lookup_table(int warp, int lane) {
     }
 }
 
+// Eight consecutive activations (columns k0 .. k0 + 7, bf16 pairs in four words) of a row that holds the gate_up
+// output: act 1 = SiLU(gate) * up with gate = columns [0, K), up = [K, 2K) (the arithmetic of silu_glu_kernel);
+// act 2 = the gpt-oss form on interleaved columns (gate 2k, up 2k + 1; glu_gpt_oss_kernel without bias).
+__device__ __forceinline__ uint4 load_glu8(int act, const uint8_t* xrow, int k0, int64_t K) {
+    uint32_t ow[4];
+    if (act == 1) {
+        const uint4 gv = __ldg(reinterpret_cast<const uint4*>(xrow + (int64_t)k0 * 2));
+        const uint4 uv = __ldg(reinterpret_cast<const uint4*>(xrow + (K + k0) * 2));
+        const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float g0 = __uint_as_float(gw[j] << 16), g1 = __uint_as_float(gw[j] & 0xffff0000u);
+            const float u0 = __uint_as_float(uw[j] << 16), u1 = __uint_as_float(uw[j] & 0xffff0000u);
+            ow[j] = (uint32_t)f32_to_bf16_bits(__fmul_rn(silu_f32(g0), u0)) |
+                    ((uint32_t)f32_to_bf16_bits(__fmul_rn(silu_f32(g1), u1)) << 16);
+        }
+    } else {
+        const uint4 p0 = __ldg(reinterpret_cast<const uint4*>(xrow + (int64_t)k0 * 4));
+        const uint4 p1 = __ldg(reinterpret_cast<const uint4*>(xrow + (int64_t)k0 * 4 + 16));
+        const uint32_t pw[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t a0 = pw[2 * j], a1 = pw[2 * j + 1];
+            ow[j] = (uint32_t)f32_to_bf16_bits(glu_gpt_oss(__uint_as_float(a0 << 16), __uint_as_float(a0 & 0xffff0000u))) |
+                    ((uint32_t)f32_to_bf16_bits(glu_gpt_oss(__uint_as_float(a1 << 16), __uint_as_float(a1 & 0xffff0000u))) << 16);
+        }
+    }
+    return make_uint4(ow[0], ow[1], ow[2], ow[3]);
+}
+
 struct DGroup {
     int32_t row0, eid, rows;
     bool valid;
@@ -321,7 +352,48 @@ __device__ __forceinline__ void walk_to(const DecodeArgs& a, const int32_t* vb, 
 // RM: activation rows per pass.  RW: weight rows of a stage that a warp works on at the same time (two
 // independent streams of lookups and FMAs hide the table-read latency that one leaves exposed).  XF: form of the
 // activations in registers and of the lookup table (see word_fma).
-template <int FMT, int SDT, int AU, int RM, int RW, int XF>
+// Compact mode: the prefix sum of the groups' chunk counts in shared memory (s_grp[g + 1] = chunks of groups 0..g).
+// Every thread fetches the tables of its groups (one memory round trip for the whole list, not one per 32 groups),
+// then one warp turns the counts into the prefix sum in place.  Out of line: it runs once, before the kernel's
+// register-heavy part, and must not weigh on that part's register allocation.
+// When the tables may have been written by the kernel launched just before, that kernel has to be waited for first
+// of all; the lookup table, which depends on nothing, is then built here before the wait (and not again later).
+template <int FMT, int XF, int CW>
+__device__ __noinline__ void decode_compact_scan(const DecodeArgs& a, int32_t* s_grp) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, bid = (int)blockIdx.x;
+    if (!a.tables_ready) {
+        if (warp < CW) build_lookup_table<FMT, XF, CW>(warp, lane);
+        pdl_wait();
+    }
+    for (int gi = threadIdx.x; gi < a.g.G; gi += blockDim.x) {
+        const int32_t r0 = __ldg(a.g.off + gi), r1 = __ldg(a.g.off + gi + 1), e = __ldg(a.g.eids + gi);
+        const bool bad = e < 0 || e >= a.g.E || r1 < r0 || r0 < 0 || r1 > a.g.T;
+        const bool bad_off = r1 < r0 || r0 < 0 || r1 > a.g.T;
+        if (bad && r1 != r0 && (bad_off || e != GNF4B_PAD_EXPERT) && a.g.status && bid == 0)
+            atomicOr(a.g.status, bad_off ? GNF4B_ST_BAD_OFFSETS : GNF4B_ST_BAD_EXPERT);
+        s_grp[gi + 1] = bad ? 0 : min((r1 - r0 + a.rows_per_pass - 1) / a.rows_per_pass, a.row_chunks);
+    }
+    __syncthreads();
+    if (warp == 0) {
+        int32_t carry = 0;
+        if (lane == 0) s_grp[0] = 0;
+        for (int base = 0; base < a.g.G; base += 32) {
+            const int gi = base + lane;
+            int32_t n = gi < a.g.G ? s_grp[gi + 1] : 0;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int32_t t = __shfl_up_sync(0xffffffffu, n, o);
+                if (lane >= o) n += t;
+            }
+            if (gi < a.g.G) s_grp[gi + 1] = carry + n;
+            carry += __shfl_sync(0xffffffffu, n, 31);
+        }
+    }
+}
+
+// XA = 1: the instance that can apply the FFN's activation while it loads its activation rows (DecodeArgs.x_act);
+// a separate instance so that the plain one keeps its registers.
+template <int FMT, int SDT, int AU, int RM, int RW, int XF, int XA = 0>
 __global__ void __launch_bounds__(decode_threads(RM, AU), 1) decode_gemv_kernel(const DecodeArgs a) {
     constexpr int kCW = decode_consumer_warps(RM, AU);
     constexpr int kXN = XF == 1 ? AU * 32 : AU * 16;     // registers per activation row
@@ -338,6 +410,7 @@ __global__ void __launch_bounds__(decode_threads(RM, AU), 1) decode_gemv_kernel(
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
+    EPT(60);
     pdl_launch_dependents();
     if (smem_base > (uint32_t)kDTabAbs) {
         // dynamic shared memory starts beyond the table's fixed address (never seen): nothing is computed
@@ -354,6 +427,7 @@ __global__ void __launch_bounds__(decode_threads(RM, AU), 1) decode_gemv_kernel(
     }
     __syncthreads();
 
+
     const int bid = (int)blockIdx.x;
     int64_t item_lo = (int64_t)bid * a.items_per_cta + min(bid, a.items_extra);
     int64_t item_hi = item_lo + a.items_per_cta + (bid < a.items_extra ? 1 : 0);
@@ -361,30 +435,7 @@ __global__ void __launch_bounds__(decode_threads(RM, AU), 1) decode_gemv_kernel(
     if (a.compact) {
         // compact mode (row chunks, or far more groups than rows): build the prefix sum of the groups' chunk counts (one warp, ordered scan),
         // then cut the list of existing items evenly over the CTAs
-        if (!a.tables_ready) pdl_wait();
-        if (warp == 0) {
-            int32_t carry = 0;
-            if (lane == 0) s_grp[0] = 0;
-            for (int base = 0; base < a.g.G; base += 32) {
-                const int gi = base + lane;
-                int32_t n = 0;
-                if (gi < a.g.G) {
-                    const int32_t r0 = __ldg(a.g.off + gi), r1 = __ldg(a.g.off + gi + 1), e = __ldg(a.g.eids + gi);
-                    const bool bad = e < 0 || e >= a.g.E || r1 < r0 || r0 < 0 || r1 > a.g.T;
-                    const bool bad_off = r1 < r0 || r0 < 0 || r1 > a.g.T;
-                    if (bad && r1 != r0 && (bad_off || e != GNF4B_PAD_EXPERT) && a.g.status && bid == 0)
-                        atomicOr(a.g.status, bad_off ? GNF4B_ST_BAD_OFFSETS : GNF4B_ST_BAD_EXPERT);
-                    n = bad ? 0 : min((r1 - r0 + a.rows_per_pass - 1) / a.rows_per_pass, a.row_chunks);
-                }
-#pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    const int32_t t = __shfl_up_sync(0xffffffffu, n, o);
-                    if (lane >= o) n += t;
-                }
-                if (gi < a.g.G) s_grp[gi + 1] = carry + n;
-                carry += __shfl_sync(0xffffffffu, n, 31);
-            }
-        }
+        decode_compact_scan<FMT, XF, kCW>(a, s_grp);
         __syncthreads();
         const int64_t total = (int64_t)vb[a.g.G] * a.tiles_per_group;
         const int64_t per = total / gridDim.x, extra = total % gridDim.x;
@@ -447,19 +498,21 @@ __global__ void __launch_bounds__(decode_threads(RM, AU), 1) decode_gemv_kernel(
     grp.rows = 0;
     uint32_t xr[RM][kXN];     // the group's activation rows: units lane, lane + 32, ... (fp32 bits or bf16 pairs)
 
+    // x_act: the rows of x are gate_up outputs (2K wide) and the activation row is computed while it is loaded
+    const int64_t x_pitch = (XA ? 2 : 1) * a.g.K * 2;
     auto load_a = [&](const DGroup& gr) {
 #pragma unroll
         for (int m = 0; m < RM; ++m) {
-            const uint8_t* xrow = reinterpret_cast<const uint8_t*>(a.g.x) + (int64_t)(gr.row0 + m) * a.g.K * 2;
+            const uint8_t* xrow = reinterpret_cast<const uint8_t*>(a.g.x) + (int64_t)(gr.row0 + m) * x_pitch;
             const bool have = gr.valid && m < gr.rows;
 #pragma unroll
             for (int q = 0; q < AU; ++q) {
                 const int U = lane + 32 * q;
 #pragma unroll
                 for (int v = 0; v < 4; ++v) {
-                    const uint4 raw = (have && U < n_units)
-                                          ? __ldg(reinterpret_cast<const uint4*>(xrow + (int64_t)U * 64 + v * 16))
-                                          : make_uint4(0, 0, 0, 0);
+                    const uint4 raw = !(have && U < n_units) ? make_uint4(0, 0, 0, 0)
+                                      : XA == 0 ? __ldg(reinterpret_cast<const uint4*>(xrow + (int64_t)U * 64 + v * 16))
+                                                : load_glu8(a.x_act, xrow, U * 32 + v * 8, a.g.K);
                     const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
@@ -480,18 +533,20 @@ __global__ void __launch_bounds__(decode_threads(RM, AU), 1) decode_gemv_kernel(
     DGroupRaw raw0 = {0, 0, 0};
     if (early) raw0 = decode_group_load(a, w.g);
     // built before pdl_wait(): it overlaps the tail of the previous kernel
-    build_lookup_table<FMT, XF, kCW>(warp, lane);
+    if (!(a.compact && !a.tables_ready)) build_lookup_table<FMT, XF, kCW>(warp, lane);
     if (early) {
         grp = decode_group_check(a, raw0, w.c);
         cur_v = w.v;
         if (warp == 0 && grp.valid) {       // a hint that brings the activation rows' lines into L2
-            const uint8_t* xrow = reinterpret_cast<const uint8_t*>(a.g.x) + (int64_t)grp.row0 * a.g.K * 2;
-            const int64_t bytes = (int64_t)min(grp.rows, RM) * a.g.K * 2;
+            const uint8_t* xrow = reinterpret_cast<const uint8_t*>(a.g.x) + (int64_t)grp.row0 * x_pitch;
+            const int64_t bytes = (int64_t)min(grp.rows, RM) * x_pitch;
             for (int64_t o = (int64_t)lane * 128; o < bytes; o += 32 * 128)
                 asm volatile("prefetch.global.L2 [%0];" ::"l"(xrow + o));
         }
     }
+    EPT(61);
     pdl_wait();
+    EPT(62);
     if (!early && item_lo < item_hi) {
         grp = decode_group(a, w.g, w.c);
         cur_v = w.v;
@@ -523,6 +578,7 @@ __global__ void __launch_bounds__(decode_threads(RM, AU), 1) decode_gemv_kernel(
         if (++tile == a.tiles_per_group) { tile = 0; walk_to(a, vb, w, w.v + 1); }
     }
     if (poisoned && threadIdx.x == 0 && a.g.status) atomicOr(a.g.status, GNF4B_ST_TIMEOUT);
+    EPT(63);
 }
 
 }  // namespace gnf4b

@@ -13,6 +13,10 @@ template <int VEC>
 __global__ void silu_glu_kernel(const uint16_t* __restrict__ gu, int64_t rows, int64_t h, uint16_t* __restrict__ out) {
     const int64_t per_row = h / VEC;
     const int64_t total = rows * per_row;
+    EPT(50);
+    pdl_launch_dependents();          // launched with programmatic stream serialization: the next kernel may set up now
+    pdl_wait();                       // and this one reads nothing before the kernel that wrote gu has finished
+    EPT(51);
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t r = i / per_row, c = (i - r * per_row) * VEC;
         const uint16_t* g = gu + r * 2 * h + c;
@@ -172,31 +176,6 @@ ep_plan_kernel(const int64_t* __restrict__ idx, int32_t P, int32_t k, int32_t n_
             const int64_t c = i - (int64_t)p * H;
             if (s_slot[p] >= 0) send[s_slot[p] * H + c] = hidden[(int64_t)(p / k) * H + c];
         }
-    }
-}
-
-// Group offsets of a received fixed-capacity buffer: per source rank its e_local expert blocks
-// (recv_counts[s, e] rows) and then the unused capacity as one padding group.  offsets has
-// world * (e_local + 1) + 1 entries.  Counts that do not fit the capacity are clamped and flagged.
-__global__ void ep_offsets_kernel(const int32_t* __restrict__ recv_counts, int32_t world, int32_t e_local, int32_t cap,
-                                  int32_t* __restrict__ offsets, int32_t* status) {
-    if (threadIdx.x != 0 || blockIdx.x != 0) return;
-    int32_t off = 0, g = 0;
-    offsets[0] = 0;
-    for (int s = 0; s < world; ++s) {
-        int32_t used = 0;
-        for (int e = 0; e < e_local; ++e) {
-            int32_t n = recv_counts[s * e_local + e];
-            if (n < 0 || used + n > cap) {
-                if (status) atomicOr(status, GNF4B_ST_BAD_OFFSETS);
-                n = n < 0 ? 0 : cap - used;
-            }
-            used += n;
-            off += n;
-            offsets[++g] = off;
-        }
-        off += cap - used;
-        offsets[++g] = off;
     }
 }
 

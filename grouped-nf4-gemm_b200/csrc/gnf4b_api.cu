@@ -16,6 +16,7 @@
 #include "tensor_fwd_kernel.cuh"
 #include "ep_kernels.cuh"
 #include "ffn_kernel.cuh"
+#include "ep_peer.cuh"
 
 namespace gnf4b {
 
@@ -218,9 +219,26 @@ static cudaError_t launch_stream_au(const StreamArgs& sa, int au, int grid, size
 #undef GNF4B_LAUNCH_AU
 }
 
-template <int FMT, int SDT, int AUV, int RMV, int RW, int XF>
+// Launch with programmatic stream serialization: the kernel may start while its predecessor in the stream is
+// still running and must call pdl_wait() before it touches anything (reads or writes) the predecessor may use.
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_pdl(void (*kfn)(KArgs...), unsigned grid, unsigned block, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(block);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kfn, static_cast<KArgs>(args)...);
+}
+
+template <int FMT, int SDT, int AUV, int RMV, int RW, int XF, int XA = 0>
 static cudaError_t launch_decode_one(const DecodeArgs& da, int grid, size_t smem, cudaStream_t st) {
-    auto kfn = decode_gemv_kernel<FMT, SDT, AUV, RMV, RW, XF>;
+    auto kfn = decode_gemv_kernel<FMT, SDT, AUV, RMV, RW, XF, XA>;
     static int granted[64];
     cudaError_t e = ensure_smem(kfn, smem, granted);
     if (e != cudaSuccess) return e;
@@ -246,6 +264,21 @@ static cudaError_t launch_decode_au(const DecodeArgs& da, int au, int rm, int rw
                                     cudaStream_t st) {
     constexpr int X1 = (FMT == GNF4B_FMT_MXFP4) ? 2 : 1;     // short rows
     constexpr int X0 = (FMT == GNF4B_FMT_MXFP4) ? 2 : 0;     // long rows, two activation rows per pass
+    if (da.x_act) {
+        // activation applied on load: the FFN's second GEMM, whose rows (the intermediate size) are short
+        if (au > 3) return cudaErrorNotSupported;
+        if (rm == 1 && rw == 2) {
+            if (au <= 1) return launch_decode_one<FMT, SDT, 1, 1, 2, X1, 1>(da, grid, smem, st);
+            if (au == 2) return launch_decode_one<FMT, SDT, 2, 1, 2, X1, 1>(da, grid, smem, st);
+            return launch_decode_one<FMT, SDT, 3, 1, 2, X0, 1>(da, grid, smem, st);
+        }
+        if (rm == 2) {
+            if (au <= 1) return launch_decode_one<FMT, SDT, 1, 2, 1, X0, 1>(da, grid, smem, st);
+            if (au == 2) return launch_decode_one<FMT, SDT, 2, 2, 1, X0, 1>(da, grid, smem, st);
+            return launch_decode_one<FMT, SDT, 3, 2, 1, X0, 1>(da, grid, smem, st);
+        }
+        return cudaErrorNotSupported;
+    }
     if (rm == 1 && rw == 2) {
         if (au <= 1) return launch_decode_one<FMT, SDT, 1, 1, 2, X1>(da, grid, smem, st);
         if (au == 2) return launch_decode_one<FMT, SDT, 2, 1, 2, X1>(da, grid, smem, st);
@@ -423,6 +456,12 @@ int gnf4b_gemm_grouped(int fmt, int op, const void* x, int x_dtype, int64_t T, c
     DevInfo di;
     rc = device_info(&di);
     if (rc) return rc;
+    // activation applied while x is loaded: the decode kernel only
+    const int x_act = (flags & GNF4B_FLAG_X_SILU_GLU) ? 1 : ((flags & GNF4B_FLAG_X_GPT_OSS_GLU) ? 2 : 0);
+    if (x_act) {
+        if (op != GNF4B_OP_FWD || x_dtype != GNF4B_X_BF16 || max_rows <= 0 || max_rows > 16) return GNF4B_EUNSUPPORTED;
+        flags = (flags & ~(GNF4B_PATH_MASK | GNF4B_SPLITK_MASK)) | GNF4B_PATH_STREAM | (1u << GNF4B_SPLITK_SHIFT);
+    }
     Plan p;
     rc = make_plan(fmt, op, x_dtype, T, G, N, K, max_rows, flags, di, &p);
     if (rc) return rc;
@@ -526,6 +565,7 @@ int gnf4b_gemm_grouped(int fmt, int op, const void* x, int x_dtype, int64_t T, c
             da.compact = (da.row_chunks > 1 || ((int64_t)G > T && G <= p.g_cache)) ? 1 : 0;
             da.total_items = (int64_t)G * da.row_chunks * da.tiles_per_group;
             da.tables_ready = (flags & GNF4B_FLAG_TABLES_READY) ? 1 : 0;
+            da.x_act = x_act;
             da.stages = (int32_t)std::min<int64_t>(kDMaxStages, ring_room / da.slot_bytes);
             const int dgrid = (int)std::min<int64_t>(di.sm_count, da.total_items);
             da.items_per_cta = (int32_t)(da.total_items / dgrid);
@@ -539,11 +579,13 @@ int gnf4b_gemm_grouped(int fmt, int op, const void* x, int x_dtype, int64_t T, c
                     e = launch_decode_au<GNF4B_FMT_NF4, GNF4B_S_BF16>(da, au_k, rm, rw, dgrid, dsmem, st);
                 else
                     e = launch_decode_au<GNF4B_FMT_MXFP4, GNF4B_S_E8M0>(da, au_k, rm, rw, dgrid, dsmem, st);
+                if (e == cudaErrorNotSupported && x_act) return GNF4B_EUNSUPPORTED;
                 if (e != cudaSuccess) return cuda_fail(e, "decode kernel launch");
                 return GNF4B_OK;
             }
         }
     }
+    if (x_act) return GNF4B_EUNSUPPORTED;       // the streaming kernel reads x as it is
     StreamArgs sa;
     sa.g = g;
     sa.n_tiles = (int32_t)p.n_tiles;
@@ -778,11 +820,10 @@ int gnf4b_silu_glu(const void* gate_up, int64_t rows, int64_t h, void* out, void
     const bool vec = (h % 8) == 0 && ((reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
     const int64_t work = rows * (vec ? h / 8 : h);
     const int grid = (int)std::min<int64_t>(ceil_div(work, 256), 148 * 16);
-    if (vec)
-        silu_glu_kernel<8><<<grid, 256, 0, st>>>(static_cast<const uint16_t*>(gate_up), rows, h, static_cast<uint16_t*>(out));
-    else
-        silu_glu_kernel<1><<<grid, 256, 0, st>>>(static_cast<const uint16_t*>(gate_up), rows, h, static_cast<uint16_t*>(out));
-    cudaError_t e = cudaPeekAtLastError();
+    cudaError_t e = vec ? launch_pdl(silu_glu_kernel<8>, (unsigned)grid, 256u, st, static_cast<const uint16_t*>(gate_up), rows, h,
+                                     static_cast<uint16_t*>(out))
+                        : launch_pdl(silu_glu_kernel<1>, (unsigned)grid, 256u, st, static_cast<const uint16_t*>(gate_up), rows, h,
+                                     static_cast<uint16_t*>(out));
     return e == cudaSuccess ? GNF4B_OK : cuda_fail(e, "silu_glu launch");
 }
 
@@ -1109,10 +1150,71 @@ int gnf4b_ep_plan(const int64_t* idx, int32_t P, int32_t k, int32_t n_experts, i
 int gnf4b_ep_offsets(const int32_t* recv_counts, int32_t world, int32_t e_local, int32_t cap, int32_t* offsets,
                      int32_t* status_word, void* cuda_stream) {
     if (world <= 0 || e_local <= 0 || cap < 0 || !recv_counts || !offsets) return GNF4B_EINVAL;
-    ep_offsets_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(cuda_stream)>>>(recv_counts, world, e_local, cap, offsets,
+    if ((int64_t)world * e_local > kEpPlanMax) return GNF4B_ETOOBIG;
+    ep_offsets_kernel<<<1, kEpOffsetsThreads, 0, reinterpret_cast<cudaStream_t>(cuda_stream)>>>(recv_counts, world, e_local, cap, offsets,
                                                                               status_word);
     cudaError_t e = cudaPeekAtLastError();
     return e == cudaSuccess ? GNF4B_OK : cuda_fail(e, "ep_offsets launch");
+}
+
+static_assert(sizeof(gnf4b_ep_peer_ctx) == sizeof(EpPeerCtx) && GNF4B_EP_MAX_WORLD == kEpPeerMaxWorld,
+              "the public exchange context and the kernels' argument struct are the same bytes");
+
+static int ep_peer_ctx(const gnf4b_ep_peer_ctx* c, int32_t cap, EpPeerCtx* out) {
+    if (!c || c->world <= 0 || c->world > kEpPeerMaxWorld || c->rank < 0 || c->rank >= c->world || c->e_local <= 0 ||
+        c->cap_max <= 0 || c->H <= 0 || (c->H % 8) || cap < 0)
+        return GNF4B_EINVAL;
+    if (cap > c->cap_max || (int64_t)c->world * c->e_local > kEpPlanMax || (int64_t)c->world * cap > kEpPlanMax)
+        return GNF4B_ETOOBIG;
+    for (int r = 0; r < c->world; ++r)
+        if (!c->peers[r] || (reinterpret_cast<uintptr_t>(c->peers[r]) & 255)) return GNF4B_EINVAL;
+    std::memcpy(out, c, sizeof(EpPeerCtx));
+    return GNF4B_OK;
+}
+
+int gnf4b_ep_peer_layout(int32_t world, int32_t e_local, int32_t cap_max, int64_t H, int64_t* out3) {
+    if (world <= 0 || world > kEpPeerMaxWorld || e_local <= 0 || cap_max <= 0 || H <= 0 || (H % 8) || !out3) return GNF4B_EINVAL;
+    const EpPeerLayout L = ep_peer_layout(world, e_local, cap_max, H);
+    out3[0] = L.total;
+    out3[1] = L.recv_rows;
+    out3[2] = L.ret_ll;
+    return GNF4B_OK;
+}
+
+int gnf4b_ep_peer_dispatch(const gnf4b_ep_peer_ctx* ctx, const int64_t* idx, int32_t P, int32_t k, int32_t n_experts,
+                           int32_t cap, const void* hidden, int64_t* slot, int32_t one_row_groups, int32_t* offsets,
+                           int32_t* expert_ids, int32_t* status_word, void* cuda_stream) {
+    EpPeerCtx cx;
+    int rc = ep_peer_ctx(ctx, cap, &cx);
+    if (rc) return rc;
+    if (P < 0 || k <= 0 || n_experts != cx.world * cx.e_local) return GNF4B_EINVAL;
+    if (P > kEpPlanMax || n_experts > kEpPlanMax) return GNF4B_ETOOBIG;
+    if (P > 0 && (!idx || !hidden || !slot)) return GNF4B_EINVAL;
+    if (!offsets || (one_row_groups && !expert_ids)) return GNF4B_EINVAL;
+    if (reinterpret_cast<uintptr_t>(hidden) & 15) return GNF4B_EINVAL;
+    const int32_t n_groups = one_row_groups ? cx.world * cap : cx.e_local;
+    // one pass of 16 bytes per thread where that needs no more than 32 CTAs (each repeats the small plan); about cap
+    // of the world * cap row slots are in use on the receiving side
+    const int64_t rows = std::max<int64_t>(P, cap);
+    const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(32, ceil_div(rows * cx.H * 2, (int64_t)4096)));
+    cudaError_t e = launch_pdl(ep_peer_dispatch_kernel, grid, kEpPeerThreads, reinterpret_cast<cudaStream_t>(cuda_stream), cx,
+                               idx, P, k, n_experts, cap, static_cast<const uint16_t*>(hidden), slot, one_row_groups ? 1 : 0,
+                               n_groups, offsets, expert_ids, status_word);
+    return e == cudaSuccess ? GNF4B_OK : cuda_fail(e, "ep_peer_dispatch launch");
+}
+
+int gnf4b_ep_peer_combine(const gnf4b_ep_peer_ctx* ctx, int32_t cap, const void* y, const int64_t* slot, const float* weights,
+                          int32_t k, int64_t M, void* out, int32_t* status_word, void* cuda_stream) {
+    EpPeerCtx cx;
+    int rc = ep_peer_ctx(ctx, cap, &cx);
+    if (rc) return rc;
+    if (!y || k <= 0 || M < 0 || (M > 0 && (!slot || !weights || !out))) return GNF4B_EINVAL;
+    if ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(y)) & 15) return GNF4B_EINVAL;
+    const int64_t rows = std::max<int64_t>(M, cap);
+    const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(32, ceil_div(rows * cx.H * 2, (int64_t)4096)));
+    cudaError_t e = launch_pdl(ep_peer_combine_kernel, grid, kEpPeerThreads, reinterpret_cast<cudaStream_t>(cuda_stream), cx, cap,
+                               static_cast<const uint16_t*>(y), slot, weights, k, M, static_cast<uint16_t*>(out), status_word);
+    return e == cudaSuccess ? GNF4B_OK : cuda_fail(e, "ep_peer_combine launch");
 }
 
 int gnf4b_dequant(int fmt, const uint8_t* W, int64_t w_stride_e, int64_t w_stride_n, const void* S,
@@ -1136,3 +1238,17 @@ int gnf4b_dequant(int fmt, const uint8_t* W, int64_t w_stride_e, int64_t w_strid
 }
 
 }  // extern "C"
+
+#ifdef GNF4B_EP_TRACE
+extern "C" int gnf4b_ep_trace_read(unsigned long long* host, int max_events) {
+    unsigned int n = 0;
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(&n, gnf4b::g_ep_trace_n, sizeof(n));
+    if ((int)n > max_events) n = max_events;
+    if (n > 4096) n = 4096;
+    cudaMemcpyFromSymbol(host, gnf4b::g_ep_trace, (size_t)n * 16);
+    unsigned int z = 0;
+    cudaMemcpyToSymbol(gnf4b::g_ep_trace_n, &z, sizeof(z));
+    return (int)n;
+}
+#endif

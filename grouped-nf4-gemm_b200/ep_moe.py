@@ -22,12 +22,19 @@ exchange, and the received buffer is multiplied where it lies -- one group per (
 padding group per source for the unused capacity (expert id -1: skipped by the kernels).  Nothing is read
 back to the host, so the layer is a fixed sequence of launches.
 
-The collectives are NCCL over NVLink/NVSwitch on GPUs and gloo in the CPU tests; the GEMM is
+On GPUs of one node the fixed-capacity exchange does not go through a collective library at all
+(``PeerExchange``): each rank's routing kernel stores the rows and their per-expert counts straight into the
+destination ranks' buffers over NVLink (symmetric memory, plain peer stores, one flag per source and
+destination), the result rows come back the same way, and the waits are bounded polls inside the two small kernels
+either side of the GEMMs: five launches per layer and no collective.
+
+Otherwise the collectives are NCCL over NVLink/NVSwitch on GPUs and gloo in the CPU tests; the GEMM is
 injectable (``grouped_fn``) so the exchange logic can be tested on CPU ranks against the
 oracle.  There is no TMA multicast anywhere on this path.
 """
 from __future__ import annotations
 
+import os
 import statistics
 import time
 
@@ -140,6 +147,9 @@ def regroup_index(recv_counts: torch.Tensor, total: int | None = None):
 #: exchange is used; above it the exact-size exchange (one host read per layer) moves fewer bytes
 FIXED_CAPACITY_MAX_BYTES = 4 << 20
 
+#: row slots (world * capacity) up to which the peer-memory exchange makes every received row its own group
+ONE_ROW_MAX_ROWS = 128
+
 #: expert id of a padding group (include/gnf4b.h: GNF4B_PAD_EXPERT)
 PAD_EXPERT = -1
 
@@ -150,12 +160,65 @@ PAD_EXPERT = -1
 BLOCK_GROUPS_MIN_ROWS = 64
 
 
+class PeerExchange:
+    """This rank's exchange buffer (include/gnf4b.h: gnf4b_ep_peer_ctx) and every peer's address of it.
+
+    The buffer comes from torch's symmetric memory (``torch.distributed._symmetric_memory``): one allocation
+    per rank, mapped into every rank of the group by ``rendezvous``; the kernels of the library then use plain
+    stores and loads on the peers' addresses.  Building it is a collective: all ranks of the group construct it
+    at the same point.  One rank alone needs no mapping and takes ordinary device memory."""
+
+    def __init__(self, group, world: int, rank: int, e_local: int, cap_max: int, H: int, device):
+        import ctypes
+        import _gnf4b
+        lib = _gnf4b.load()
+        lay = (ctypes.c_int64 * 3)()
+        _gnf4b.check(lib.gnf4b_ep_peer_layout(world, e_local, cap_max, H, lay), "gnf4b_ep_peer_layout")
+        self.total, self.recv_off, self.ret_off = int(lay[0]), int(lay[1]), int(lay[2])
+        self.world, self.cap_max, self.H = world, cap_max, H
+        if world == 1:
+            self.handle = None
+            self.buf = torch.zeros(self.total, dtype=torch.uint8, device=device)
+            ptrs = [self.buf.data_ptr()]
+        else:
+            import torch.distributed._symmetric_memory as symm
+            pg = group if group is not None else dist.group.WORLD
+            self.buf = symm.empty(self.total, dtype=torch.uint8, device=device)
+            self.buf.zero_()
+            self.handle = symm.rendezvous(self.buf, pg)
+            ptrs = [int(p) for p in self.handle.buffer_ptrs]
+            torch.cuda.synchronize(device)
+            dist.barrier(group)          # every buffer is zeroed before any rank stores into a peer's
+        self.ctx = _gnf4b.EpPeerCtx(world, rank, e_local, cap_max, H)
+        for r in range(world):
+            self.ctx.peers[r] = ptrs[r]
+        self.ref = ctypes.byref(self.ctx)
+
+    _shared = {}
+
+    @classmethod
+    def shared(cls, group, world, rank, e_local, cap_max, H, device):
+        """One buffer per (group, shape, device) for all layers of a process: the layers run one after the other
+        on one stream and every rank uses the buffer in the same order, which is all the exchange needs."""
+        key = (id(group) if group is not None else 0, world, rank, e_local, cap_max, H, str(device))
+        px = cls._shared.get(key)
+        if px is None:
+            px = cls._shared[key] = cls(group, world, rank, e_local, cap_max, H, device)
+        return px
+
+    def recv_rows(self, cap: int) -> torch.Tensor:
+        """The row matrix [world * cap, H] bf16 the arrive kernel unpacks the received rows into."""
+        n = self.world * cap * self.H * 2
+        return self.buf[self.recv_off:self.recv_off + n].view(torch.bfloat16).view(self.world * cap, self.H)
+
+
 class EPGroupedMoE:
     """One expert-parallel MoE layer.  ``gate_up`` / ``down`` are this rank's shards
     ``(W [E/W, N, K/2] u8, S scales)``; ``grouped_fn(a_cat, W, S, sizes, expert_ids)`` is the
     grouped GEMM (the CUDA op by default)."""
 
-    def __init__(self, n_experts: int, gate_up, down, group=None, grouped_fn=None, fmt: str = "nf4"):
+    def __init__(self, n_experts: int, gate_up, down, group=None, grouped_fn=None, fmt: str = "nf4",
+                 peer_exchange: bool | None = None):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -163,6 +226,8 @@ class EPGroupedMoE:
         self.e_local = n_experts // self.world
         assert self.e_local * self.world == n_experts, "experts must divide evenly over the ranks"
         self.gate_up, self.down = gate_up, down
+        self._own_gemm = grouped_fn is None          # the library's GEMM (not an injected one): fused forms apply
+        self._fmt_id = 0 if fmt == "nf4" else 1      # GNF4B_FMT_NF4 / GNF4B_FMT_MXFP4
         if grouped_fn is None:
             if fmt == "nf4":
                 from nf4_grouped import gemm_4bit_grouped as grouped_fn
@@ -171,6 +236,13 @@ class EPGroupedMoE:
         self.grouped_fn = grouped_fn
         self.timers = None           # set to a dict of CUDA-event lists to get a phase breakdown
         self._fixed_eids = None      # expert ids of the fixed-capacity path's groups (built once per device)
+        # small batches on GPUs: rows cross NVLink by the library's own peer stores (PeerExchange) unless this is
+        # False or GNF4B_EP_PEER=0, in which case the same exchange runs as collectives
+        if peer_exchange is None:
+            peer_exchange = os.environ.get("GNF4B_EP_PEER", "1") != "0"
+        self.peer_exchange = bool(peer_exchange) and self.world <= 16
+        self._peer = {}              # (hidden size, device) -> PeerExchange
+        self._local_eids = None
         self.last_rows = 0
 
     # -- helpers ---------------------------------------------------------------
@@ -260,6 +332,8 @@ class EPGroupedMoE:
             self._fixed_eids = torch.tensor((list(range(El)) + [PAD_EXPERT]) * W, dtype=torch.int32, device=dev)
         use_lib = (hidden.is_cuda and hidden.dtype == torch.bfloat16 and hidden.is_contiguous() and cap <= 1024
                    and self.n_experts <= 1024)
+        if use_lib and self.peer_exchange and H % 8 == 0 and W * cap <= 1024:
+            return self._forward_peer(hidden, idx, weights, cap)
         if use_lib:
             import _gnf4b
             import nf4_grouped
@@ -327,6 +401,65 @@ class EPGroupedMoE:
         self._mark("sum")
         return out
 
+
+    def _forward_peer(self, hidden, idx, weights, cap):
+        """The fixed-capacity layer with the rows carried by the library's own kernels over peer memory: dispatch
+        (plan + stores into the destinations' buffers, then bounded wait, rows unpacked expert-major, group tables),
+        the two grouped GEMMs and the activation, combine (stores back, then bounded wait + routing-weight sum).
+        Five launches, no collective, no fence, no host read.  Up to ONE_ROW_MAX_ROWS row
+        slots every received row is its own group (the one-row kernels); beyond, the groups are the local experts."""
+        import _gnf4b
+        import nf4_grouped
+        W, El = self.world, self.e_local
+        dev = hidden.device
+        H = hidden.shape[1]
+        px = self._peer.get((H, dev))
+        if px is None:
+            cap_max = max(1, min(1024 // W, FIXED_CAPACITY_MAX_BYTES // (W * H * hidden.element_size())))
+            with torch.cuda.device(dev):
+                px = self._peer[(H, dev)] = PeerExchange.shared(self.group, W, self.rank, El, cap_max, H, dev)
+        one_row = W * cap <= ONE_ROW_MAX_ROWS
+        n_groups = W * cap if one_row else El
+        lib = _gnf4b.load()
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        status = nf4_grouped._status_word(dev).data_ptr()
+        idx64 = idx.to(torch.int64).contiguous()
+        w32 = weights.to(torch.float32).contiguous()
+        M, k = idx.shape
+        slot = torch.empty(cap, dtype=torch.int64, device=dev)
+        offsets = torch.empty(n_groups + 1, dtype=torch.int32, device=dev)
+        if one_row:
+            eids = torch.empty(n_groups, dtype=torch.int32, device=dev)
+        else:
+            if self._local_eids is None or self._local_eids.device != dev:
+                self._local_eids = torch.arange(El, dtype=torch.int32, device=dev)
+            eids = self._local_eids
+        out = torch.empty(M, H, dtype=hidden.dtype, device=dev)
+        with torch.cuda.device(dev):
+            _gnf4b.check(lib.gnf4b_ep_peer_dispatch(px.ref, idx64.data_ptr(), cap, k, self.n_experts, cap, hidden.data_ptr(),
+                                                    slot.data_ptr(), int(one_row), offsets.data_ptr(), eids.data_ptr(), status,
+                                                    stream), "gnf4b_ep_peer_dispatch")
+        self._mark("dispatch")
+        recv = px.recv_rows(cap)
+        self.last_rows = W * cap
+        max_rows = 1 if one_row else W * M          # an expert can get every token of every rank
+        gu = self.grouped_fn(recv, self.gate_up[0], self.gate_up[1], None, eids, group_offsets=offsets, max_rows=max_rows)
+        self._mark("gate_up")
+        if self._own_gemm:
+            # small groups: the second GEMM applies the activation while it loads the first one's output
+            self._mark("glu")
+            y = nf4_grouped.gemm_after_glu(self._fmt_id, gu, self.down[0], self.down[1], eids, offsets, max_rows)
+        else:
+            h = silu_glu(gu)
+            self._mark("glu")
+            y = self.grouped_fn(h, self.down[0], self.down[1], None, eids, group_offsets=offsets, max_rows=max_rows)
+        self._mark("down")
+        with torch.cuda.device(dev):
+            _gnf4b.check(lib.gnf4b_ep_peer_combine(px.ref, cap, y.data_ptr(), slot.data_ptr(), w32.data_ptr(), k, M,
+                                                   out.data_ptr(), status, stream), "gnf4b_ep_peer_combine")
+        self._mark("combine")
+        self._mark("sum")
+        return out
 
 # --------------------------------------------------------------------------- benchmark leg
 def bench_ep(args, shape, rank, world, B):

@@ -465,8 +465,10 @@ def _group_tables(sizes, expert_ids, T: int, E: int, dev, group_offsets=None, ma
 
 
 def _launch(fmt, op, x, W, S, sizes, expert_ids, n_out, *, split_k=None, path=_gnf4b.PATH_AUTO,
-            group_offsets=None, max_rows=None, tables_ready=None):
-    """One grouped launch.  x [T, C] bf16/fp16, W [E, N, K/2] u8, S scales -> bf16 [T, n_out]."""
+            group_offsets=None, max_rows=None, tables_ready=None, x_glu: int = 0):
+    """One grouped launch.  x [T, C] bf16/fp16, W [E, N, K/2] u8, S scales -> bf16 [T, n_out].
+    ``x_glu`` (FLAG_X_SILU_GLU / FLAG_X_GPT_OSS_GLU): x is the gate_up output [T, 2K]; returns None when the
+    library has no kernel that applies the activation on load for this problem."""
     dev = x.device
     E, N, half = W.shape
     K = half * 2
@@ -513,7 +515,7 @@ def _launch(fmt, op, x, W, S, sizes, expert_ids, n_out, *, split_k=None, path=_g
             return out
         off_p = off_t if isinstance(off_t, int) else off_t.data_ptr()
         ids_p = ids_t if isinstance(ids_t, int) else ids_t.data_ptr()
-        flags = path
+        flags = path | x_glu
         if split_k is not None:
             flags |= max(1, int(split_k)) << _gnf4b.SPLITK_SHIFT
         # Group tables that this call uploaded from host lists travel by a stream-ordered copy, which no kernel
@@ -539,8 +541,32 @@ def _launch(fmt, op, x, W, S, sizes, expert_ids, n_out, *, split_k=None, path=_g
     finally:
         if prev >= 0:
             torch.cuda.set_device(prev)
+    if rc == _gnf4b.EUNSUPPORTED and x_glu:
+        return None
     if rc:
         _gnf4b.check(rc, "gnf4b_gemm_grouped")
+    return out
+
+
+def gemm_after_glu(fmt, gate_up, W, S, expert_ids, group_offsets, max_rows, act: str = "silu"):
+    """The FFN's second GEMM on the OUTPUT of its first: ``gate_up [T, 2K]`` bf16 -> ``[T, N]``, the activation
+    (``"silu"``: SiLU(gate_up[:, :K]) * gate_up[:, K:]; ``"gpt_oss"``: the clamped form on interleaved columns)
+    applied inside the GEMM kernel while it loads its rows, where a kernel for that exists (small groups), else by
+    the activation kernel first.  Same bits either way."""
+    flag = _gnf4b.FLAG_X_SILU_GLU if act == "silu" else _gnf4b.FLAG_X_GPT_OSS_GLU
+    out = None
+    if max_rows and max_rows <= 16 and gate_up.dtype == torch.bfloat16:
+        out = _launch(fmt, _gnf4b.OP_FWD, gate_up, W, S, None, expert_ids, W.shape[1], group_offsets=group_offsets,
+                      max_rows=max_rows, x_glu=flag)
+    if out is None:
+        if act == "silu":
+            import ep_moe
+            h = ep_moe.silu_glu(gate_up)
+        else:
+            import mxfp4_grouped
+            h = mxfp4_grouped.glu_gpt_oss(gate_up)
+        out = _launch(fmt, _gnf4b.OP_FWD, h, W, S, None, expert_ids, W.shape[1], group_offsets=group_offsets,
+                      max_rows=max_rows)
     return out
 
 

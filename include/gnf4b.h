@@ -58,6 +58,13 @@ extern "C" {
 
 #define GNF4B_FLAG_FFN_UNFUSED    0x100000u /* ablation: gnf4b_ffn_grouped as three launches even where one fused
                                              launch would be taken */
+/* x is the gate_up output of the expert FFN, bf16 [T, 2K], and the activation between the two GEMMs is applied while
+ * its rows are loaded: SiLU(x[:, :K]) * x[:, K:] (the arithmetic of gnf4b_silu_glu), or the gpt-oss form on
+ * interleaved columns (gnf4b_glu_gpt_oss without bias).  Saves the activation launch and its pass over memory; same
+ * bits as the two-launch form.  Forward only, on the decode kernel (small groups: max_rows given and <= 16);
+ * GNF4B_EUNSUPPORTED otherwise -- the caller then runs the activation kernel itself. */
+#define GNF4B_FLAG_X_SILU_GLU    0x200000u
+#define GNF4B_FLAG_X_GPT_OSS_GLU 0x400000u
 /* activations of gnf4b_ffn_grouped */
 #define GNF4B_ACT_SILU_GLU    0   /* SiLU(gate) * up, gate = the first half of the gate_up columns            */
 #define GNF4B_ACT_GPT_OSS_GLU 1   /* gpt-oss: gate / up interleaved, clamped at 7, (up+1) * gate * sigmoid(1.702 gate) */
@@ -328,6 +335,49 @@ int gnf4b_ep_plan(const int64_t* idx, int32_t P, int32_t k, int32_t n_experts, i
                   void* cuda_stream);
 int gnf4b_ep_offsets(const int32_t* recv_counts, int32_t world, int32_t e_local, int32_t cap, int32_t* offsets,
                      int32_t* status_word, void* cuda_stream);
+
+/* The same small-batch exchange without a collective library (expert-parallel layer; no reference counterpart):
+ * each rank owns ONE exchange buffer of gnf4b_ep_peer_layout(...)[0] bytes that every other rank of the node can
+ * address (peer access / symmetric memory); ctx.peers[r] is rank r's buffer as THIS process addresses it, 256-byte
+ * aligned, zeroed once before the first step with a barrier of the ranks after the zeroing.  Rows travel as plain
+ * stores to the peer pointer, every 8 bytes carrying 4 bytes of row and the 4-byte number of the step; a reader that
+ * finds the number it expects has the payload beside it, so there is no fence, no flag and no multicast.  Per layer,
+ * on every rank, two launches around the GEMMs on one stream (each may be replayed from a captured graph: the step
+ * numbers live in the buffer).  Each launch first sends and then receives, so no rank waits before it has sent:
+ *
+ *   gnf4b_ep_peer_dispatch  SENDS: the plan of gnf4b_ep_plan (slot[P] as there); rows and per-expert counts written
+ *                           into the destinations' buffers.  RECEIVES: waits for all sources' counts and for the rows
+ *                           they announce, unpacks the rows EXPERT-MAJOR (local experts ascending; inside an expert
+ *                           sources in rank order, a source's rows in the order sent) into the row matrix bf16
+ *                           [world * cap, H] at byte layout[1] of the own buffer, and writes the group tables of the
+ *                           GEMMs over that matrix:
+ *                             one_row_groups = 0: offsets[e_local + 1] (the groups are the local experts 0 .. e_local-1)
+ *                             one_row_groups = 1: every row its own group, offsets[world * cap + 1] (offsets[g] =
+ *                               min(g, rows)) and expert_ids[world * cap] (the row's expert, GNF4B_PAD_EXPERT beyond
+ *                               the rows): few rows, the one-row kernels (max_rows = 1) apply.
+ *   (the grouped GEMMs and the activation on that matrix, result y bf16 [world * cap, H] in the same row order)
+ *   gnf4b_ep_peer_combine   SENDS: every result row of y back to its source's buffer, and to every rank the word
+ *                           that this rank is through with what it received.  RECEIVES: waits for that word from
+ *                           every rank and for the rows it expects, then out[m] = sum_j weights[m, j] *
+ *                           returned[slot[m, j]] with the arithmetic of gnf4b_combine_rows.
+ *
+ * All ranks call with the same cap (<= cap_max, world * cap <= 1024) and H (% 8 == 0).  Every wait is bounded (2 s):
+ * when it runs out GNF4B_ST_TIMEOUT is raised in the status word and the kernel goes on with what is there.  One set
+ * of row slots is enough because the steps interlock: a rank's next dispatch follows its combine, which has heard
+ * from every rank's combine, which follows that rank's dispatch. */
+#define GNF4B_EP_MAX_WORLD 16
+typedef struct gnf4b_ep_peer_ctx {
+    int32_t world, rank, e_local, cap_max;
+    int64_t H;
+    void* peers[GNF4B_EP_MAX_WORLD];
+} gnf4b_ep_peer_ctx;
+/* out3 = {bytes of one rank's buffer, byte offset of the row matrix, byte offset of the returned rows' slots} */
+int gnf4b_ep_peer_layout(int32_t world, int32_t e_local, int32_t cap_max, int64_t H, int64_t* out3);
+int gnf4b_ep_peer_dispatch(const gnf4b_ep_peer_ctx* ctx, const int64_t* idx, int32_t P, int32_t k, int32_t n_experts,
+                           int32_t cap, const void* hidden, int64_t* slot, int32_t one_row_groups, int32_t* offsets,
+                           int32_t* expert_ids, int32_t* status_word, void* cuda_stream);
+int gnf4b_ep_peer_combine(const gnf4b_ep_peer_ctx* ctx, int32_t cap, const void* y, const int64_t* slot,
+                          const float* weights, int32_t k, int64_t M, void* out, int32_t* status_word, void* cuda_stream);
 
 /* Device properties this library plans with (SM count, opt-in shared memory). */
 int gnf4b_device_info(int32_t* sm_count, int32_t* smem_optin_bytes);

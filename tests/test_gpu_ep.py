@@ -32,6 +32,12 @@ def _tokens(rank, E, H, k, M):
     return x, idx, w
 
 
+def _agree(a, b):
+    """The two exchanges hand the GEMM the same rows in different groupings (expert-major against per source), so
+    the planner may pick different kernels: equal to bf16 resolution of the largest value, not to the bit."""
+    return bool(((a.float() - b.float()).abs().max() <= 2 * 2 ** -8 * b.float().abs().max()).item())
+
+
 def _worker(rank, world, port, q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
@@ -47,7 +53,32 @@ def _worker(rank, world, port, q):
         x, idx, w = _tokens(rank, E, H, k, M)
         y = layer.forward(x.to(dev), idx.to(dev), w.to(dev))
         torch.cuda.synchronize()
-        q.put((rank, y.float().cpu().numpy(), nf4_grouped.last_status(dev)))
+        # small batches: the library's own exchange over peer memory against the same layer over NCCL, bit for
+        # bit, on steps with different routing and batch sizes (buffers and flags are reused from step to step)
+        nccl = ep_moe.EPGroupedMoE(E, sh(gu), sh(dn), fmt="nf4", peer_exchange=False)
+        same = True
+        for step, m in enumerate((1, 3, 8, 2, 8, 1, 5, 8, 24, 40, 1)):
+            xs, ids, ws = _tokens(rank + 10 * step, E, H, k, m)
+            a = layer.forward(xs.to(dev), ids.to(dev), ws.to(dev))
+            b = nccl.forward(xs.to(dev), ids.to(dev), ws.to(dev))
+            same = same and _agree(a, b)
+        peer_used = len(layer._peer) == 1 and len(nccl._peer) == 0
+        # the same launches replayed from a CUDA graph: the step number lives on the device
+        xs, ids, ws = (t.to(dev) for t in _tokens(rank + 77, E, H, k, 4))
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            layer.forward(xs, ids, ws)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                yg = layer.forward(xs, ids, ws)
+            for _ in range(3):
+                g.replay()
+        side.synchronize()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        same_graph = _agree(yg, nccl.forward(xs, ids, ws))
+        torch.cuda.synchronize()
+        q.put((rank, y.float().cpu().numpy(), nf4_grouped.last_status(dev), same, peer_used, same_graph))
     finally:
         dist.destroy_process_group()
 
@@ -66,9 +97,12 @@ def test_two_gpu_layer_matches_single_gpu_layer():
         p.start()
     got = {}
     for _ in range(world):
-        r, y, status = q.get(timeout=300)
+        r, y, status, same, peer_used, same_graph = q.get(timeout=300)
         got[r] = y
         assert status == 0
+        assert peer_used, "the small-batch steps did not take the peer-memory exchange"
+        assert same, "peer-memory exchange and NCCL exchange differ beyond bf16 resolution"
+        assert same_graph, "replayed graph of the peer-memory exchange differs"
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
@@ -210,3 +244,70 @@ def test_single_gpu_layer_from_logits_without_host_reads():
             want[m] += w[m, j] * (h.float() @ w2.t()).to(torch.bfloat16).float()
     assert ((y.float() - want).norm() / want.norm()).item() < 1e-2
     assert nf4_grouped.last_status("cuda") == 0
+
+
+def test_peer_exchange_on_one_gpu_equals_the_collective_form_and_replays():
+    """One rank: the four exchange kernels around the GEMMs against the plan / offsets / combine kernels (the form
+    the collectives use), same bits over steps of different sizes; then a captured sequence replayed."""
+    import ep_moe
+    import nf4_grouped
+    import synth
+    E, H, I, k = 16, 256, 128, 4
+    gen = torch.Generator().manual_seed(5)
+    gu = synth.nf4_stack(E, 2 * I, H, gen, device="cuda", scale=0.05)
+    dn = synth.nf4_stack(E, H, I, gen, device="cuda", scale=0.05)
+    peer = ep_moe.EPGroupedMoE(E, gu, dn, fmt="nf4", peer_exchange=True)
+    coll = ep_moe.EPGroupedMoE(E, gu, dn, fmt="nf4", peer_exchange=False)
+    for step, m in enumerate((1, 7, 2, 16, 1, 40, 200, 3)):        # 40 and 200 tokens: groups = the local experts
+        x, idx, w = (t.cuda() for t in _tokens(step, E, H, k, m))
+        assert _agree(peer.forward(x, idx, w), coll.forward(x, idx, w)), step
+    assert len(peer._peer) == 1 and not coll._peer
+    x, idx, w = (t.cuda() for t in _tokens(40, E, H, k, 4))
+    want = coll.forward(x, idx, w)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        peer.forward(x, idx, w)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            y = peer.forward(x, idx, w)
+        for _ in range(3):
+            g.replay()
+    side.synchronize()
+    assert _agree(y, want)
+    assert nf4_grouped.last_status("cuda") == 0
+
+
+def test_peer_exchange_wait_runs_out_and_sets_the_status():
+    """A flag that nothing raises: rank 0 of a two-rank context whose second buffer is a local stand-in that no
+    process writes.  The dispatch kernel's receiving half gives up after its time limit, raises GNF4B_ST_TIMEOUT and returns; the
+    context stays usable."""
+    import ctypes
+    import _gnf4b
+    lib = _gnf4b.load()
+    world, e_local, cap, H = 2, 2, 4, 64
+    lay = (ctypes.c_int64 * 3)()
+    assert lib.gnf4b_ep_peer_layout(world, e_local, cap, H, lay) == 0
+    bufs = [torch.zeros(int(lay[0]), dtype=torch.uint8, device="cuda") for _ in range(world)]
+    ctx = _gnf4b.EpPeerCtx(world, 0, e_local, cap, H)
+    for r in range(world):
+        ctx.peers[r] = bufs[r].data_ptr()
+    idx = torch.tensor([0, 3, 1, 2], dtype=torch.int64, device="cuda")
+    hidden = torch.randn(2, H, device="cuda").to(torch.bfloat16)
+    slot = torch.empty(4, dtype=torch.int64, device="cuda")
+    offsets = torch.zeros(e_local + 1, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    assert lib.gnf4b_ep_peer_dispatch(ctypes.byref(ctx), idx.data_ptr(), 4, 2, world * e_local, cap, hidden.data_ptr(),
+                                      slot.data_ptr(), 0, offsets.data_ptr(), None, status.data_ptr(), st) == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) & _gnf4b.ST_TIMEOUT
+    # rank 0's own rows did arrive: experts 0 and 1 got one row each, unpacked expert-major
+    assert offsets.tolist() == [0, 1, 2]
+    assert slot.tolist() == [0, cap + 1, 1, cap + 0]
+    rows = bufs[0][int(lay[1]):int(lay[1]) + 2 * H * 2].view(torch.bfloat16).view(2, H)
+    assert torch.equal(rows[0], hidden[0]) and torch.equal(rows[1], hidden[1])
+    # too large a capacity is refused before any launch
+    assert lib.gnf4b_ep_peer_dispatch(ctypes.byref(ctx), idx.data_ptr(), 4, 2, world * e_local, cap + 1, hidden.data_ptr(),
+                                      slot.data_ptr(), 0, offsets.data_ptr(), None, status.data_ptr(), st) == -6
+    assert torch.randn(8, device="cuda").sum().isfinite()

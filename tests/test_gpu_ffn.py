@@ -163,3 +163,47 @@ def test_host_ffn_entry_uses_the_fused_launch_and_keeps_its_results():
     comp = gemm_4bit_grouped(ep_moe.silu_glu(gemm_4bit_grouped(a2.to(DEV), Bg, Ag, sizes2, ids2)), Bd, Ad, sizes2, ids2)
     assert torch.equal(out2, comp.cpu())
     _clean()
+
+
+@pytest.mark.parametrize("N_gu,K_gu,N_dn,G,rows", [(1536, 2048, 2048, 8, 1), (512, 256, 256, 5, 2), (4096, 1024, 512, 12, 1),
+                                                   (256, 128, 64, 3, 5)])
+def test_second_gemm_applies_the_activation_on_load(N_gu, K_gu, N_dn, G, rows):
+    """gemm_after_glu: the down GEMM reads the gate_up output and applies SiLU-GLU while it loads its rows.  Same
+    bits as the activation kernel followed by the plain GEMM, for one-row groups and for groups of a few rows."""
+    E = 6
+    (Bg, Ag), (Bd, Ad) = _nf4_pair(E, N_gu, K_gu, N_dn, seed=N_gu + rows)
+    gen = torch.Generator().manual_seed(G)
+    ids = torch.tensor([int(v) for v in torch.randint(0, E, (G,), generator=gen)], dtype=torch.int32, device=DEV)
+    sizes = [int(v) for v in torch.randint(0, rows + 1, (G,), generator=gen)]
+    sizes[0] = rows
+    off = torch.tensor([0] + list(np.cumsum(sizes)), dtype=torch.int32, device=DEV)
+    T = int(sum(sizes))
+    gu = (torch.randn(T, N_gu, generator=gen) * 2).to(torch.bfloat16).to(DEV)
+    got = nf4_grouped.gemm_after_glu(_gnf4b.FMT_NF4, gu, Bd, Ad, ids, off, rows)
+    want = gemm_4bit_grouped(ep_moe.silu_glu(gu), Bd, Ad, None, ids, group_offsets=off, max_rows=rows)
+    assert torch.equal(got, want)
+    # the library did take the fused form (no silent detour through the activation kernel)
+    direct = nf4_grouped._launch(_gnf4b.FMT_NF4, _gnf4b.OP_FWD, gu, Bd, Ad, None, ids, N_dn, group_offsets=off,
+                                 max_rows=rows, x_glu=_gnf4b.FLAG_X_SILU_GLU)
+    assert direct is not None and torch.equal(direct, want)
+    _clean()
+
+
+def test_second_gemm_gpt_oss_activation_on_load():
+    E, N_gu, K, N_dn, G = 4, 5760, 2880, 2880, 4
+    gen = torch.Generator().manual_seed(2)
+    Wd, Sd = synth.mxfp4_stack(E, N_dn, N_gu // 2, gen, device=DEV, e_lo=118, e_hi=122)
+    ids = torch.tensor([3, 0, 2, 3], dtype=torch.int32, device=DEV)
+    off = torch.arange(G + 1, dtype=torch.int32, device=DEV)
+    gu = (torch.randn(G, N_gu, generator=gen) * 3).to(torch.bfloat16).to(DEV)
+    got = nf4_grouped.gemm_after_glu(_gnf4b.FMT_MXFP4, gu, Wd, Sd, ids, off, 1, act="gpt_oss")
+    want = mxfp4_grouped.gemm_mxfp4_grouped(mxfp4_grouped.glu_gpt_oss(gu), Wd, Sd, None, ids, group_offsets=off, max_rows=1)
+    assert torch.equal(got, want)
+    # large groups: no kernel applies the activation on load, the same entry runs the activation kernel first
+    gu2 = (torch.randn(64, N_gu, generator=gen)).to(torch.bfloat16).to(DEV)
+    off2 = torch.tensor([0, 40, 64], dtype=torch.int32, device=DEV)
+    ids2 = torch.tensor([1, 2], dtype=torch.int32, device=DEV)
+    got2 = nf4_grouped.gemm_after_glu(_gnf4b.FMT_MXFP4, gu2, Wd, Sd, ids2, off2, 40, act="gpt_oss")
+    want2 = mxfp4_grouped.gemm_mxfp4_grouped(mxfp4_grouped.glu_gpt_oss(gu2), Wd, Sd, None, ids2, group_offsets=off2, max_rows=40)
+    assert torch.equal(got2, want2)
+    _clean()
