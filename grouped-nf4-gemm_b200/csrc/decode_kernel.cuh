@@ -62,6 +62,7 @@ struct DecodeArgs {
     int32_t compact;            // work list holds only (group, chunk) pairs that exist (prefix sum in shared memory)
     int32_t tables_ready;       // group_offsets / expert_ids were NOT written by the kernel launched just before
     int32_t x_act;              // 0: x [T, K].  1 / 2: x is the gate_up output [T, 2K], SiLU-GLU / gpt-oss GLU applied on load
+    int32_t h_bytes;            // x_act: shared memory behind the group prefix for the activated rows (rows_per_pass * K * 2)
 };
 
 
@@ -358,34 +359,37 @@ __device__ __forceinline__ void walk_to(const DecodeArgs& a, const int32_t* vb, 
 // register-heavy part, and must not weigh on that part's register allocation.
 // When the tables may have been written by the kernel launched just before, that kernel has to be waited for first
 // of all; the lookup table, which depends on nothing, is then built here before the wait (and not again later).
+// (Arguments by value: a reference to the kernel's parameter block would move the whole block to local memory.)
 template <int FMT, int XF, int CW>
-__device__ __noinline__ void decode_compact_scan(const DecodeArgs& a, int32_t* s_grp) {
+__device__ __noinline__ void decode_compact_scan(const int32_t* __restrict__ off, const int32_t* __restrict__ eids, int32_t G,
+                                                 int32_t E, int64_t T, int32_t* status, int32_t rows_per_pass,
+                                                 int32_t row_chunks, int32_t tables_ready, int32_t* s_grp) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, bid = (int)blockIdx.x;
-    if (!a.tables_ready) {
+    if (!tables_ready) {
         if (warp < CW) build_lookup_table<FMT, XF, CW>(warp, lane);
         pdl_wait();
     }
-    for (int gi = threadIdx.x; gi < a.g.G; gi += blockDim.x) {
-        const int32_t r0 = __ldg(a.g.off + gi), r1 = __ldg(a.g.off + gi + 1), e = __ldg(a.g.eids + gi);
-        const bool bad = e < 0 || e >= a.g.E || r1 < r0 || r0 < 0 || r1 > a.g.T;
-        const bool bad_off = r1 < r0 || r0 < 0 || r1 > a.g.T;
-        if (bad && r1 != r0 && (bad_off || e != GNF4B_PAD_EXPERT) && a.g.status && bid == 0)
-            atomicOr(a.g.status, bad_off ? GNF4B_ST_BAD_OFFSETS : GNF4B_ST_BAD_EXPERT);
-        s_grp[gi + 1] = bad ? 0 : min((r1 - r0 + a.rows_per_pass - 1) / a.rows_per_pass, a.row_chunks);
+    for (int gi = threadIdx.x; gi < G; gi += blockDim.x) {
+        const int32_t r0 = __ldg(off + gi), r1 = __ldg(off + gi + 1), e = __ldg(eids + gi);
+        const bool bad = e < 0 || e >= E || r1 < r0 || r0 < 0 || r1 > T;
+        const bool bad_off = r1 < r0 || r0 < 0 || r1 > T;
+        if (bad && r1 != r0 && (bad_off || e != GNF4B_PAD_EXPERT) && status && bid == 0)
+            atomicOr(status, bad_off ? GNF4B_ST_BAD_OFFSETS : GNF4B_ST_BAD_EXPERT);
+        s_grp[gi + 1] = bad ? 0 : min((r1 - r0 + rows_per_pass - 1) / rows_per_pass, row_chunks);
     }
     __syncthreads();
     if (warp == 0) {
         int32_t carry = 0;
         if (lane == 0) s_grp[0] = 0;
-        for (int base = 0; base < a.g.G; base += 32) {
+        for (int base = 0; base < G; base += 32) {
             const int gi = base + lane;
-            int32_t n = gi < a.g.G ? s_grp[gi + 1] : 0;
+            int32_t n = gi < G ? s_grp[gi + 1] : 0;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
                 const int32_t t = __shfl_up_sync(0xffffffffu, n, o);
                 if (lane >= o) n += t;
             }
-            if (gi < a.g.G) s_grp[gi + 1] = carry + n;
+            if (gi < G) s_grp[gi + 1] = carry + n;
             carry += __shfl_sync(0xffffffffu, n, 31);
         }
     }
@@ -435,7 +439,8 @@ __global__ void __launch_bounds__(decode_threads(RM, AU), 1) decode_gemv_kernel(
     if (a.compact) {
         // compact mode (row chunks, or far more groups than rows): build the prefix sum of the groups' chunk counts (one warp, ordered scan),
         // then cut the list of existing items evenly over the CTAs
-        decode_compact_scan<FMT, XF, kCW>(a, s_grp);
+        decode_compact_scan<FMT, XF, kCW>(a.g.off, a.g.eids, a.g.G, a.g.E, a.g.T, a.g.status, a.rows_per_pass, a.row_chunks,
+                                          a.tables_ready, s_grp);
         __syncthreads();
         const int64_t total = (int64_t)vb[a.g.G] * a.tiles_per_group;
         const int64_t per = total / gridDim.x, extra = total % gridDim.x;
@@ -498,12 +503,30 @@ __global__ void __launch_bounds__(decode_threads(RM, AU), 1) decode_gemv_kernel(
     grp.rows = 0;
     uint32_t xr[RM][kXN];     // the group's activation rows: units lane, lane + 32, ... (fp32 bits or bf16 pairs)
 
-    // x_act: the rows of x are gate_up outputs (2K wide) and the activation row is computed while it is loaded
+    // XA: the rows of x are gate_up outputs (2K wide).  The consumer warps compute the group's activated rows ONCE,
+    // together, into shared memory (every warp needs the whole row: computed per warp, the activation would be done
+    // kCW times over), then each takes its lanes' share from there.  All consumer warps walk the same items, so
+    // they reach every group change together and the two barriers are safe.
     const int64_t x_pitch = (XA ? 2 : 1) * a.g.K * 2;
+    uint4* h_s = reinterpret_cast<uint4*>(tail + 256 + (((size_t)(2 * a.g_cache + 1) * 4 + 15) & ~(size_t)15));
     auto load_a = [&](const DGroup& gr) {
+        if (XA) {
+            named_bar_sync(2, kCW * 32);              // the previous group's rows have been taken by every warp
+            const int per_row = (int)(a.g.K >> 3);
+#pragma unroll 1
+            for (int m = 0; m < RM; ++m) {
+                if (!(gr.valid && m < gr.rows)) break;
+                const uint8_t* xrow = reinterpret_cast<const uint8_t*>(a.g.x) + (int64_t)(gr.row0 + m) * x_pitch;
+#pragma unroll 1
+                for (int c8 = (int)threadIdx.x; c8 < per_row; c8 += kCW * 32)
+                    h_s[m * per_row + c8] = load_glu8(a.x_act, xrow, c8 * 8, a.g.K);
+            }
+            named_bar_sync(3, kCW * 32);
+        }
 #pragma unroll
         for (int m = 0; m < RM; ++m) {
-            const uint8_t* xrow = reinterpret_cast<const uint8_t*>(a.g.x) + (int64_t)(gr.row0 + m) * x_pitch;
+            const uint8_t* xrow = XA ? reinterpret_cast<const uint8_t*>(h_s) + (size_t)m * a.g.K * 2
+                                     : reinterpret_cast<const uint8_t*>(a.g.x) + (int64_t)(gr.row0 + m) * x_pitch;
             const bool have = gr.valid && m < gr.rows;
 #pragma unroll
             for (int q = 0; q < AU; ++q) {
@@ -512,7 +535,7 @@ __global__ void __launch_bounds__(decode_threads(RM, AU), 1) decode_gemv_kernel(
                 for (int v = 0; v < 4; ++v) {
                     const uint4 raw = !(have && U < n_units) ? make_uint4(0, 0, 0, 0)
                                       : XA == 0 ? __ldg(reinterpret_cast<const uint4*>(xrow + (int64_t)U * 64 + v * 16))
-                                                : load_glu8(a.x_act, xrow, U * 32 + v * 8, a.g.K);
+                                                : *reinterpret_cast<const uint4*>(xrow + (size_t)U * 64 + v * 16);
                     const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {

@@ -527,7 +527,9 @@ int gnf4b_gemm_grouped(int fmt, int op, const void* x, int x_dtype, int64_t T, c
             const int rw = (rm == 1 && au_k <= 3 && !(flags & GNF4B_FLAG_DECODE_ONE_ROW)) ? 2 : 1;
             DecodeArgs da;
             da.g = g;
-            const int64_t ring_room = (int64_t)di.smem_optin - (int64_t)decode_smem_bytes(0, 0, p.g_cache);
+            // activation on load: room for the group's activated rows behind the group prefix
+            const int64_t h_bytes = x_act ? (int64_t)rm * K * 2 + 16 : 0;
+            const int64_t ring_room = (int64_t)di.smem_optin - (int64_t)decode_smem_bytes(0, 0, p.g_cache) - h_bytes;
             // a stage's scale span must stay 16-byte aligned: rows per stage in multiples of 4 when four scale
             // rows are, else of 8 (`contiguous` guarantees eight are)
             const int r_step = ((4 * srow) % 16 == 0) ? 4 : 8;
@@ -570,7 +572,8 @@ int gnf4b_gemm_grouped(int fmt, int op, const void* x, int x_dtype, int64_t T, c
             const int dgrid = (int)std::min<int64_t>(di.sm_count, da.total_items);
             da.items_per_cta = (int32_t)(da.total_items / dgrid);
             da.items_extra = (int32_t)(da.total_items % dgrid);
-            const size_t dsmem = decode_smem_bytes(da.slot_bytes, std::max(da.stages, 1), da.g_cache);
+            da.h_bytes = (int32_t)h_bytes;
+            const size_t dsmem = decode_smem_bytes(da.slot_bytes, std::max(da.stages, 1), da.g_cache) + (size_t)h_bytes;
             if (da.stages >= 3 && da.total_items < (int64_t)1 << 31) {
                 cudaError_t e;
                 if (fmt == GNF4B_FMT_NF4 && s_dtype == GNF4B_S_F32)
