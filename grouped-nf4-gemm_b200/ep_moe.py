@@ -524,7 +524,7 @@ def bench_ep(args, shape, rank, world, B):
                     run(i, False)
             graph.replay()
             barrier()
-            timing = "K steps (fixed-capacity exchange, no host read) in one CUDA graph incl. the collectives, CUDA events, max over ranks"
+            timing = "K steps (fixed-capacity exchange, no host read) in one CUDA graph incl. the exchanges, CUDA events, max over ranks"
         except Exception as exc:      # capture of the collectives not available: time eagerly
             if os.environ.get("GNF4B_EP_DEBUG"):
                 import traceback
@@ -644,15 +644,20 @@ def bench_ep(args, shape, rank, world, B):
         roof = {"bound": "tensor", "achieved": ach, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": ach / peaks["tflops"]}
     roof.update(traffic=None, kernel="gate_up grouped GEMM (per rank, timed eagerly between events)", us_per_launch=us_gu,
                 peak_source=peaks["source"])
-    # this library's kernels per layer pass: plan, offsets, gate_up, GLU, down, combine on the fixed-capacity path
-    # (torch index kernels and NCCL's are not counted); gate_up, GLU, down, combine on the exact-size path
-    launches_per_layer = 6 if graph is not None else 4
+    # this library's kernels per layer pass.  Fixed-capacity path over peer memory: dispatch, gate_up, down (activation
+    # applied on load), combine; over collectives: plan, offsets, gate_up, GLU, down, combine (torch index kernels and
+    # NCCL's are not counted); exact-size path: gate_up, GLU, down, combine
+    peer = any(m._peer for m in mods)
+    launches_per_layer = (4 if peer else 6) if graph is not None else 4
+    exchange = ("peer memory: rows and counts stored straight into the destination ranks' buffers over NVLink by this "
+                "library's kernels (8-byte words of payload + step number, bounded polls), no collective"
+                if peer else "collectives (all_to_all_single)")
     line = {
         "metric": "grouped 4-bit MoE GEMM us/layer", "value": us_layer, "unit": "us/layer", "n_gpus": world,
         "steps": K, "warmup": Wm, "ms_per_step": ms_layer / K, "higher_is_better": False, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16 activations x 4-bit weights, fp32 accumulate", "data": "synthetic",
         "config": B.workload_config(shape, args.tokens, args.layers, world),
-        "method": {"layers_resident": n_layers, "zipf": zipf, "timing": timing},
+        "method": {"layers_resident": n_layers, "zipf": zipf, "timing": timing, "exchange": exchange},
         "e2e": {"value": ms_e2e * 1e3 / K, "unit": "us/layer",
                 "h2d_bytes_per_step": args.tokens * (shape.hidden * 2 + shape.top_k * 12),
                 "d2h_bytes_per_step": args.tokens * shape.hidden * 2},
