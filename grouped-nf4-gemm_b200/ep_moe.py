@@ -150,6 +150,10 @@ FIXED_CAPACITY_MAX_BYTES = 4 << 20
 #: row slots (world * capacity) up to which the peer-memory exchange makes every received row its own group
 ONE_ROW_MAX_ROWS = 128
 
+#: tokens per rank from which the exact-size layer is pipelined over two halves of the local experts (below, two more
+#: collectives cost more than the overlap brings)
+SPLIT_MIN_TOKENS = 512
+
 #: expert id of a padding group (include/gnf4b.h: GNF4B_PAD_EXPERT)
 PAD_EXPERT = -1
 
@@ -218,7 +222,7 @@ class EPGroupedMoE:
     grouped GEMM (the CUDA op by default)."""
 
     def __init__(self, n_experts: int, gate_up, down, group=None, grouped_fn=None, fmt: str = "nf4",
-                 peer_exchange: bool | None = None):
+                 peer_exchange: bool | None = None, split_experts: bool | None = None):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -242,6 +246,12 @@ class EPGroupedMoE:
             peer_exchange = os.environ.get("GNF4B_EP_PEER", "1") != "0"
         self.peer_exchange = bool(peer_exchange) and self.world <= 16
         self._peer = {}              # (hidden size, device) -> PeerExchange
+        # large batches: the layer pipelined over the two halves of the local experts on two streams, on request
+        # (split_experts=True or GNF4B_EP_SPLIT=1).  Off by default: on 2 GPUs at 4096 tokens per GPU it measured
+        # 1832 against 1597 us/layer -- there the exchange phases are the routing plan's sort and gather kernels and
+        # the host read, not time on NVLink, and two more collectives and smaller GEMMs cost more than the overlap brings
+        self.split_experts = (os.environ.get("GNF4B_EP_SPLIT", "0") == "1") if split_experts is None else bool(split_experts)
+        self._streams = None
         self._local_eids = None
         self.last_rows = 0
 
@@ -268,7 +278,32 @@ class EPGroupedMoE:
         # (a single rank takes it too: routing plan, groups and combine without a host read)
         if W * cap * hidden.shape[1] * hidden.element_size() <= FIXED_CAPACITY_MAX_BYTES:
             return self._forward_fixed(hidden, idx, weights, cap)
-        order, tok, counts = plan_dispatch(idx, self.n_experts, W)
+        halves = 2 if (self.split_experts and W > 1 and El >= 2 and self.timers is None
+                       and hidden.shape[0] >= SPLIT_MIN_TOKENS) else 1
+        return self._forward_exact(hidden, idx, weights, halves)
+
+    def _forward_exact(self, hidden, idx, weights, halves: int = 1):
+        """The exact-size layer.  ``halves`` = 2 pipelines it over the two halves of every rank's local experts on
+        two streams: rows for the lower half are dispatched first, their GEMMs run while the upper half's rows
+        cross NVLink, and the lower half's results travel back under the upper half's GEMMs.  The split is by
+        EXPERT, not by token, because the grouped GEMM's cost at these sizes is per expert (every active expert's
+        4-bit weights are decoded once whatever its rows): token chunks would pay it once per chunk.  One routing
+        plan, one counts exchange and one host read serve both halves, and the returned rows land in one buffer in
+        the order they left, so the weighted sum -- and the result -- is the same as without the split.  The
+        collectives of one communicator run in the order they are issued, the same on every rank:
+        dispatch(0), dispatch(1), combine(0), combine(1)."""
+        W, El = self.world, self.e_local
+        dev = hidden.device
+        H = hidden.shape[1]
+        k = idx.shape[1]
+        flat = idx.reshape(-1).to(torch.int64)
+        cut = El - El // 2 if halves == 2 else El                       # local experts [0, cut) are half 0
+        # stable sort by (half, global expert id) = (half, destination rank, local expert), token order kept
+        key = flat if halves == 1 else flat + ((flat % El) >= cut).to(torch.int64) * self.n_experts
+        order = torch.argsort(key, stable=True)
+        tok = order // k
+        counts = torch.zeros(self.n_experts, dtype=torch.int64, device=dev).scatter_add_(
+            0, flat, torch.ones_like(flat)).reshape(W, El)
         counts32 = counts.to(torch.int32).contiguous()
         recv_counts = torch.empty_like(counts32)
         self._a2a(recv_counts.reshape(-1), counts32.reshape(-1), None, None)
@@ -279,22 +314,62 @@ class EPGroupedMoE:
         # the exchange needs its split sizes on the host: ONE small read per layer brings both count
         # tables, everything else about the layer's shape is derived from them on the host
         host = torch.stack((counts32, recv_counts)).cpu()
-        send_splits, recv_splits = host[0].sum(1).tolist(), host[1].sum(1).tolist()
-        n_recv = sum(recv_splits)
-        recv = torch.empty(n_recv, hidden.shape[1], dtype=hidden.dtype, device=dev)
-        self._a2a(recv, send, recv_splits, send_splits)
+        ret = torch.empty_like(send)
+        self.last_rows = int(host[1].sum())
+        if halves == 1:
+            self._exact_part(send, ret, host, recv_counts, 0, El, H)
+        else:
+            n0 = int(host[0][:, :cut].sum())                            # rows of half 0 in send / ret
+            parts = ((send[:n0], ret[:n0], 0, cut), (send[n0:], ret[n0:], cut, El))
+            if hidden.is_cuda:
+                cur = torch.cuda.current_stream(dev)
+                if self._streams is None:
+                    self._streams = [torch.cuda.Stream(dev) for _ in range(2)]
+                staged = []
+                for st, (sp, rp, lo, hi) in zip(self._streams, parts):      # dispatch(0), dispatch(1)
+                    st.wait_stream(cur)
+                    with torch.cuda.stream(st):
+                        staged.append(self._exact_dispatch(sp, host, lo, hi, H))
+                for st, (sp, rp, lo, hi), stg in zip(self._streams, parts, staged):     # GEMMs + combine per half
+                    with torch.cuda.stream(st):
+                        self._exact_compute_return(stg, rp, host, recv_counts, lo, hi)
+                for st in self._streams:
+                    cur.wait_stream(st)
+                for t in staged:
+                    t["recv"].record_stream(cur)
+            else:           # CPU ranks (tests): the same sequence of exchanges without streams
+                staged = [self._exact_dispatch(sp, host, lo, hi, H) for sp, rp, lo, hi in parts]
+                for (sp, rp, lo, hi), stg in zip(parts, staged):
+                    self._exact_compute_return(stg, rp, host, recv_counts, lo, hi)
+        self._mark("combine")
+        out = combine_rows(ret, pos.reshape(idx.shape), weights)     # the k copies are summed in j order
+        self._mark("sum")
+        return out
+
+    def _exact_dispatch(self, send_part, host, lo, hi, H):
+        """Rows for local experts [lo, hi) of every rank: one all_to_all with the split sizes from the host counts."""
+        send_splits = host[0][:, lo:hi].sum(1).tolist()
+        recv_splits = host[1][:, lo:hi].sum(1).tolist()
+        recv = torch.empty(sum(recv_splits), H, dtype=send_part.dtype, device=send_part.device)
+        self._a2a(recv, send_part, recv_splits, send_splits)
         self._mark("dispatch")
-        if W > 1 and n_recv >= BLOCK_GROUPS_MIN_ROWS * W * El:
+        return dict(recv=recv, send_splits=send_splits, recv_splits=recv_splits)
+
+    def _exact_compute_return(self, stg, ret_part, host, recv_counts, lo, hi):
+        """The grouped GEMMs and the activation on the received rows of local experts [lo, hi), results back."""
+        W, El = self.world, self.e_local
+        recv = stg["recv"]
+        n_recv = recv.shape[0]
+        if W > 1 and n_recv >= BLOCK_GROUPS_MIN_ROWS * W * (hi - lo):
             perm = None                     # groups = the (source, expert) blocks as they arrived
             a_cat = recv
-            sizes_l = host[1].reshape(-1).tolist()
-            eids = list(range(El)) * W
+            sizes_l = host[1][:, lo:hi].reshape(-1).tolist()
+            eids = list(range(lo, hi)) * W
         else:
-            perm, _ = regroup_index(recv_counts, n_recv)
+            perm, _ = regroup_index(recv_counts[:, lo:hi], n_recv)
             a_cat = recv[perm]
-            sizes_l = host[1].sum(0).tolist()
-            eids = list(range(El))
-        self.last_rows = n_recv
+            sizes_l = host[1][:, lo:hi].sum(0).tolist()
+            eids = list(range(lo, hi))
         gu = self.grouped_fn(a_cat, self.gate_up[0], self.gate_up[1], sizes_l, eids)
         self._mark("gate_up")
         h = silu_glu(gu)
@@ -306,13 +381,10 @@ class EPGroupedMoE:
         else:
             back = torch.empty_like(recv)
             back[perm] = y
-        ret = torch.empty_like(send)
-        self._a2a(ret, back, send_splits, recv_splits)
-        self._mark("combine")
-        out = combine_rows(ret, pos.reshape(idx.shape), weights)     # the k copies are summed in j order
-        self._mark("sum")
-        return out
+        self._a2a(ret_part, back, stg["send_splits"], stg["recv_splits"])
 
+    def _exact_part(self, send, ret, host, recv_counts, lo, hi, H):
+        self._exact_compute_return(self._exact_dispatch(send, host, lo, hi, H), ret, host, recv_counts, lo, hi)
 
     def forward_logits(self, hidden: torch.Tensor, logits: torch.Tensor, k: int, mode: int = 0, norm: bool = False):
         """Router included: ``logits [M, E]`` -> top-k ids and weights on the device, then ``forward``."""
@@ -591,6 +663,7 @@ def bench_ep(args, shape, rank, world, B):
     # parity on the real collectives: this rank's result of one step against the same layer computed WITHOUT any
     # exchange from the gathered expert shards (a one-rank process group), same seeds
     parity = None
+    single_us = None
     try:
         own = None
         for r in range(world):
@@ -614,6 +687,34 @@ def bench_ep(args, shape, rank, world, B):
         parity = {"max_abs_diff_over_limit": ratio[0].item(), "limit": "2 * 2^-8 * max|reference| per rank",
                   "ok": bool(ratio[0].item() <= 1.0),
                   "what": "EP layer output of one step vs the same layer on one rank from the gathered shards, max over ranks"}
+        # the same layer WITHOUT any exchange partner (all experts on this GPU, this rank's tokens): what one GPU
+        # needs for the layer code itself, the denominator of the efficiency figure below
+        if graph is not None:
+            mine_us, fine = 0.0, 1.0
+            try:
+                for i in range(Wm, Wm + K):
+                    single.forward(*dsteps[i])
+                g1 = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g1):
+                    for i in range(Wm, Wm + K):
+                        single.forward(*dsteps[i])
+                ts1 = []
+                for _ in range(5):
+                    torch.cuda.synchronize()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    g1.replay()
+                    e1.record()
+                    torch.cuda.synchronize()
+                    ts1.append(e0.elapsed_time(e1) * 1e3 / K)
+                mine_us = statistics.median(ts1)
+                del g1
+            except Exception:
+                fine = 0.0
+                torch.cuda.synchronize()
+            both = torch.tensor([mine_us, -fine], device=dev)       # every rank reaches this reduction
+            dist.all_reduce(both, op=dist.ReduceOp.MAX)
+            single_us = both[0].item() if both[1].item() == -1.0 else None
         del single, full
     except Exception as exc:      # never at the cost of the timing
         parity = {"ok": None, "error": f"{type(exc).__name__}: {str(exc)[:200]}"}
@@ -666,7 +767,11 @@ def bench_ep(args, shape, rank, world, B):
         "ep": {"parity": parity, "phase_us_median": {n: statistics.median(v) for n, v in phase.items()},
                "rows_per_rank_mean": rows_mean, "rows_per_rank_max": tmax[2].item(),
                "imbalance_max_over_mean": tmax[2].item() / max(rows_mean, 1e-9),
-               "aggregate_tflops": fl / (us_layer * 1e-6) / 1e12},
+               "aggregate_tflops": fl / (us_layer * 1e-6) / 1e12,
+               # the layer on ONE GPU that holds all experts and has no partner (one resident layer, K steps in a
+               # graph, max over ranks), and what fraction of the N-GPU layer time that is
+               "single_gpu_layer_us": single_us,
+               "efficiency_vs_single_gpu": (single_us / us_layer) if single_us else None},
         "clocks": clk.summary(), "device_status": nf4_grouped.last_status(dev),
     }
     return line

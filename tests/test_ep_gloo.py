@@ -62,8 +62,10 @@ def _worker(rank, world, port, fmt, out_q, mode="regroup"):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     if mode != "fixed":
         ep_moe.FIXED_CAPACITY_MAX_BYTES = 0       # exact-size exchange (one host read per layer)
-    if mode == "blocks":
+    if mode in ("blocks", "split_blocks"):
         ep_moe.BLOCK_GROUPS_MIN_ROWS = 0          # multiply the (source, expert) blocks where they landed
+    if mode.startswith("split"):
+        ep_moe.SPLIT_MIN_TOKENS = 1               # the layer pipelined over the two halves of the local experts
     try:
         E, H, I, k, M, gu, dn = _problem(fmt)
         el = E // world
@@ -71,7 +73,8 @@ def _worker(rank, world, port, fmt, out_q, mode="regroup"):
         def shard(t):
             return t[0][rank * el:(rank + 1) * el].contiguous(), t[1][rank * el:(rank + 1) * el].contiguous()
 
-        layer = ep_moe.EPGroupedMoE(E, shard(gu), shard(dn), grouped_fn=_oracle_grouped(fmt), fmt=fmt)
+        layer = ep_moe.EPGroupedMoE(E, shard(gu), shard(dn), grouped_fn=_oracle_grouped(fmt), fmt=fmt,
+                                    split_experts=mode.startswith("split"))
         x, idx, w = _tokens(rank, E, H, k, M)
         y = layer.forward(x, idx, w)
         out_q.put((rank, y.view(torch.int16).numpy().copy(), layer.last_rows))
@@ -86,11 +89,12 @@ def _free_port():
 
 
 @pytest.mark.parametrize("fmt,mode", [("nf4", "regroup"), ("mxfp4", "regroup"), ("nf4", "blocks"), ("nf4", "fixed"),
-                                      ("mxfp4", "fixed")])
+                                      ("mxfp4", "fixed"), ("nf4", "split_regroup"), ("nf4", "split_blocks")])
 def test_two_rank_layer_equals_single_process_layer(fmt, mode):
-    """All three ways of exchanging and grouping -- exact-size exchange with rows regrouped expert-major,
-    the same with one group per (source rank, expert) block as the rows arrived, and the fixed-capacity
-    exchange with padding groups and no host read -- must reproduce the single-process layer bit for bit."""
+    """All ways of exchanging and grouping -- exact-size exchange with rows regrouped expert-major, the same with
+    one group per (source rank, expert) block as the rows arrived, both again as two exchanges over the two halves
+    of the local experts, and the fixed-capacity exchange with padding groups and no host read -- must reproduce
+    the single-process layer bit for bit."""
     world = 2
     port = _free_port()
     ctx = mp.get_context("spawn")

@@ -77,8 +77,15 @@ def _worker(rank, world, port, q):
         side.synchronize()
         torch.cuda.current_stream(dev).wait_stream(side)
         same_graph = _agree(yg, nccl.forward(xs, ids, ws))
+        # a large batch (exact-size exchange over NCCL): pipelined over the two halves of the local experts against
+        # the layer in one piece -- the returned rows land in the same places, so the results are the same bits
+        xl, il, wl = (t.to(dev) for t in _tokens(rank + 300, E, H, k, 2600))
+        whole = ep_moe.EPGroupedMoE(E, sh(gu), sh(dn), fmt="nf4", split_experts=False)
+        piped = ep_moe.EPGroupedMoE(E, sh(gu), sh(dn), fmt="nf4", split_experts=True)
+        a, b = piped.forward(xl, il, wl), whole.forward(xl, il, wl)
+        same_chunked = _agree(a, b) and piped._streams is not None and whole._streams is None
         torch.cuda.synchronize()
-        q.put((rank, y.float().cpu().numpy(), nf4_grouped.last_status(dev), same, peer_used, same_graph))
+        q.put((rank, y.float().cpu().numpy(), nf4_grouped.last_status(dev), same, peer_used, same_graph, same_chunked))
     finally:
         dist.destroy_process_group()
 
@@ -97,12 +104,13 @@ def test_two_gpu_layer_matches_single_gpu_layer():
         p.start()
     got = {}
     for _ in range(world):
-        r, y, status, same, peer_used, same_graph = q.get(timeout=300)
+        r, y, status, same, peer_used, same_graph, same_chunked = q.get(timeout=300)
         got[r] = y
         assert status == 0
         assert peer_used, "the small-batch steps did not take the peer-memory exchange"
         assert same, "peer-memory exchange and NCCL exchange differ beyond bf16 resolution"
         assert same_graph, "replayed graph of the peer-memory exchange differs"
+        assert same_chunked, "the large-batch layer pipelined over two halves of the experts differs from the layer in one piece"
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
