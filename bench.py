@@ -20,7 +20,8 @@ One JSON line is printed by rank 0:
 
 ``--impl reference`` times only that CPU path with all host threads, same metric and config.
 With --gpus N > 1 (under torchrun) the layer is expert-parallel: experts are sharded
-across ranks, tokens are dispatched and combined with NCCL all-to-all, M tokens per rank.
+across ranks, M tokens per rank are dispatched and combined over NVLink -- decode-sized batches by
+the library's own kernels storing into the peers' memory, large ones by NCCL all-to-all.
 """
 from __future__ import annotations
 
@@ -132,7 +133,8 @@ def workload_config(shape, tokens, layers, n_gpus=1):
     else:
         workload = (f"{shape.name} {shape.fmt} MoE layer, expert-parallel over {n_gpus} GPUs "
                     f"({shape.experts // n_gpus} experts per GPU), {tokens} tokens per GPU, top-{shape.top_k}, "
-                    f"dispatch/combine by NCCL all_to_all")
+                    f"dispatch and combine over NVLink (decode-sized batches: the library's peer-memory kernels; "
+                    f"large batches: NCCL all_to_all)")
     return {"workload": workload, "tokens": tokens, "layers_resident": layers,
             "l2": f"inputs larger than L2: {layers} layer stacks walked round-robin, fresh routing per step",
             "timing": "K steps in one CUDA graph, median over replays, CUDA events (GPU arm); wall clock per layer pass (CPU arm)"}
@@ -886,9 +888,41 @@ def time_ep_layer_single_gpu(args, shape, layers, dev):
     return statistics.median(ts)
 
 
+#: further cells of the multi-GPU run: (config, tokens per GPU).  The prefill-sized Qwen3 layer and DeepSeek-V3 with
+#: Zipf(1.1) routing at a decode-sized and a mid-sized batch; each a few seconds (few steps, two resident layers).
+EP_CELLS = (("qwen3_30b_a3b", 4096), ("deepseek_v3", 8), ("deepseek_v3", 512))
+
+
 def run_gpu_ep(args, shape, rank, world):
+    import copy
     import ep_moe
-    return ep_moe.bench_ep(args, shape, rank, world, sys.modules[__name__])
+    me = sys.modules[__name__]
+    line = ep_moe.bench_ep(args, shape, rank, world, me)
+    if args.no_cells:
+        return line
+    cells = []
+    t0 = time.perf_counter()
+    for cfg, tok in EP_CELLS:
+        cs = synth.CONFIGS[cfg]
+        if (cs.name == shape.name and tok == args.tokens) or cs.experts % world:
+            continue
+        a2 = copy.copy(args)
+        a2.tokens, a2.steps, a2.warmup, a2.layers, a2.repeats = tok, (4 if tok >= 512 else 8), 3, 2, 2
+        try:
+            l2 = ep_moe.bench_ep(a2, cs, rank, world, me)
+            cells.append({"workload": l2["config"].get("workload"), "tokens_per_gpu": tok, "value": l2["value"],
+                          "unit": l2["unit"], "steps": a2.steps, "timing": l2["method"]["timing"],
+                          "exchange": l2["method"]["exchange"], "zipf": l2["method"]["zipf"],
+                          "phase_us_median": l2["ep"]["phase_us_median"],
+                          "imbalance_max_over_mean": l2["ep"]["imbalance_max_over_mean"],
+                          "aggregate_tflops": l2["ep"]["aggregate_tflops"], "parity": l2["ep"]["parity"],
+                          "roofline": l2["roofline"], "device_status": l2["device_status"]})
+        except Exception as exc:      # a cell never costs the headline
+            cells.append({"workload": f"{cfg} at {tok} tokens per GPU: cell failed", "error": f"{type(exc).__name__}: {str(exc)[:200]}"})
+        torch.cuda.empty_cache()
+    line["cells"] = cells
+    line["cells_seconds"] = time.perf_counter() - t0
+    return line
 
 
 if __name__ == "__main__":
