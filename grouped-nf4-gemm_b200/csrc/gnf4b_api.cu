@@ -3,6 +3,8 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <atomic>
+#include <chrono>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -17,6 +19,7 @@
 #include "ep_kernels.cuh"
 #include "ffn_kernel.cuh"
 #include "ep_peer.cuh"
+#include "host_stage.cuh"
 
 namespace gnf4b {
 
@@ -680,15 +683,70 @@ static int host_staging_layout(int fmt, int op, int64_t T, int32_t G, int64_t N,
 
 static constexpr size_t kHostPinnedBytes = 64u << 10;
 
-// The calling thread's pinned block (group tables, and x when it fits).  Freed when the thread ends.
+// The calling thread's pinned block: [ in: group tables, and x when it fits | out: the result of a small call |
+// tail: sequence number, status word ].  Pinned, portable and mapped: the GPU reads and writes it directly on the
+// small-call path (host_stage.cuh).  Freed when the thread ends.
 struct PinnedBlock {
     unsigned char* p = nullptr;
+    unsigned char* dev = nullptr;          // the block as the current device addresses it
+    uint32_t seq = 0;
+    unsigned char* out() const { return p + kHostPinnedBytes; }
+    volatile uint32_t* tail() const { return reinterpret_cast<volatile uint32_t*>(p + 2 * kHostPinnedBytes); }
     ~PinnedBlock() { if (p) cudaFreeHost(p); }
 };
 
 static PinnedBlock& thread_pinned_block() {
     static thread_local PinnedBlock pin;
     return pin;
+}
+
+static cudaError_t ensure_pinned_block(PinnedBlock& pin) {
+    if (pin.p) return cudaSuccess;
+    cudaError_t e = cudaHostAlloc(reinterpret_cast<void**>(&pin.p), 2 * kHostPinnedBytes + 256,
+                                  cudaHostAllocPortable | cudaHostAllocMapped);
+    if (e != cudaSuccess) { pin.p = nullptr; return e; }
+    void* d = nullptr;
+    // with unified addressing the device address of mapped pinned memory is the host address; asked for anyway
+    pin.dev = (cudaHostGetDevicePointer(&d, pin.p, 0) == cudaSuccess && d) ? static_cast<unsigned char*>(d) : nullptr;
+    if (!pin.dev) (void)cudaGetLastError();
+    pin.tail()[0] = 0;
+    return cudaSuccess;
+}
+
+// A small call's way in and out without the copy engines (host_stage.cuh).  stage_in: the first `in_bytes` of the
+// pinned block -> dst on the device, plus up to two spans zeroed.  stage_out + wait: src on the device -> the block's
+// out area, then the host thread polls the sequence number (bounded: after 50 ms it falls back to a stream
+// synchronise, which also surfaces a launch that failed).
+static cudaError_t host_stage_in(PinnedBlock& pin, void* dst, size_t in_bytes, void* zero_a, size_t zero_a_bytes,
+                                 void* zero_b, size_t zero_b_bytes, cudaStream_t st) {
+    return launch_pdl(host_stage_in_kernel, 1u, (unsigned)kHostStageThreads, st, reinterpret_cast<const uint4*>(pin.dev),
+                      static_cast<uint4*>(dst), (int32_t)(in_bytes / 16), static_cast<uint4*>(zero_a),
+                      (int32_t)(zero_a_bytes / 16), static_cast<uint4*>(zero_b), (int32_t)(zero_b_bytes / 16));
+}
+
+static int host_stage_out_wait(PinnedBlock& pin, const void* src, size_t out_bytes, const int32_t* d_status, void* out_host,
+                               int32_t* status_host, cudaStream_t st) {
+    const uint32_t seq = ++pin.seq ? pin.seq : ++pin.seq;          // never 0
+    cudaError_t e = launch_pdl(host_stage_out_kernel, 1u, (unsigned)kHostStageThreads, st, static_cast<const uint4*>(src),
+                               reinterpret_cast<uint4*>(pin.dev + kHostPinnedBytes), (int32_t)(out_bytes / 16), d_status,
+                               reinterpret_cast<volatile uint32_t*>(pin.dev + 2 * kHostPinnedBytes), seq);
+    if (e != cudaSuccess) { cudaStreamSynchronize(st); return cuda_fail(e, "host_stage_out launch"); }
+    volatile uint32_t* tail = pin.tail();
+    const auto t0 = std::chrono::steady_clock::now();
+    uint32_t spins = 0;
+    while (tail[0] != seq) {
+        if ((++spins & 1023u) == 0 &&
+            std::chrono::steady_clock::now() - t0 > std::chrono::milliseconds(50)) {
+            e = cudaStreamSynchronize(st);
+            if (e != cudaSuccess) return cuda_fail(e, "cudaStreamSynchronize");
+            if (tail[0] != seq) return cuda_fail(cudaErrorUnknown, "host_stage_out: result not delivered");
+            break;
+        }
+    }
+    std::atomic_thread_fence(std::memory_order_acquire);
+    std::memcpy(out_host, pin.out(), out_bytes);
+    if (status_host) *status_host = (int32_t)tail[1];
+    return GNF4B_OK;
 }
 
 size_t gnf4b_host_staging_bytes(int fmt, int op, int64_t T, int32_t G, int64_t N, int64_t K, uint32_t flags) {
@@ -742,19 +800,31 @@ int gnf4b_gemm_grouped_host(int fmt, int op, const void* x_host, int x_dtype, in
     cudaError_t e;
 
     PinnedBlock& pin = thread_pinned_block();
-    if (!pin.p) {
-        e = cudaHostAlloc(reinterpret_cast<void**>(&pin.p), kHostPinnedBytes, cudaHostAllocDefault);
-        if (e != cudaSuccess) { pin.p = nullptr; return cuda_fail(e, "cudaHostAlloc(pinned block)"); }
-    }
+    e = ensure_pinned_block(pin);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaHostAlloc(pinned block)");
     const size_t tab_span = h.x - h.tab;                 // tables + status, padded up to where x starts
     const bool tab_fits = tab_span <= kHostPinnedBytes;
     const bool x_rides = tab_fits && tab_span + h.x_bytes <= kHostPinnedBytes;
+    // small call: in and out through the pinned block by two small kernels instead of the copy engines
+    const bool direct = x_rides && pin.dev && h.out_bytes <= kHostPinnedBytes && h.out_bytes % 16 == 0 &&
+                        !(flags & GNF4B_FLAG_HOST_COPIES);
     std::vector<int32_t> big_tab;                        // only for G beyond the pinned block
     int32_t* t = tab_fits ? reinterpret_cast<int32_t*>(pin.p) : (big_tab.resize(2 * (size_t)G + 2), big_tab.data());
     t[0] = 0;
     for (int32_t g = 0; g < G; ++g) t[g + 1] = t[g] + sizes_host[g];
     std::memcpy(t + G + 1, expert_ids_host, (size_t)G * 4);
     t[2 * (size_t)G + 1] = 0;                            // the status word starts clear
+    if (direct) {
+        std::memcpy(pin.p + tab_span, x_host, h.x_bytes);
+        e = host_stage_in(pin, d_off, tab_span + h.x_bytes, base, p.counters_bytes, nullptr, 0, st);
+        if (e != cudaSuccess) return cuda_fail(e, "host_stage_in launch");
+        // the tables come from the kernel launched just before: not "ready" in the decode kernel's sense
+        rc = gnf4b_gemm_grouped(fmt, op, d_x, x_dtype, T, W, w_stride_e, w_stride_n, S, s_dtype, s_stride_e, s_stride_n,
+                                d_off, d_ids, G, E, N, K, max_rows, d_out, h.ws_bytes ? base : nullptr, h.ws_bytes,
+                                d_status, flags & ~GNF4B_FLAG_TABLES_READY, cuda_stream);
+        if (rc) { cudaStreamSynchronize(st); return rc; }
+        return host_stage_out_wait(pin, d_out, h.out_bytes, d_status, out_host, status_host, st);
+    }
     if (x_rides) {
         std::memcpy(pin.p + tab_span, x_host, h.x_bytes);
         e = cudaMemcpyAsync(d_off, pin.p, tab_span + h.x_bytes, cudaMemcpyHostToDevice, st);
@@ -1063,19 +1133,33 @@ int gnf4b_ffn_grouped_host(int fmt, const void* x_host, int x_dtype, int64_t T,
     cudaError_t e;
 
     PinnedBlock& pin = thread_pinned_block();
-    if (!pin.p) {
-        e = cudaHostAlloc(reinterpret_cast<void**>(&pin.p), kHostPinnedBytes, cudaHostAllocDefault);
-        if (e != cudaSuccess) { pin.p = nullptr; return cuda_fail(e, "cudaHostAlloc(pinned block)"); }
-    }
+    e = ensure_pinned_block(pin);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaHostAlloc(pinned block)");
     const size_t tab_span = f.x - f.tab;
     const bool tab_fits = tab_span <= kHostPinnedBytes;
     const bool x_rides = tab_fits && tab_span + f.x_bytes <= kHostPinnedBytes;
+    const bool direct = x_rides && pin.dev && f.out_bytes <= kHostPinnedBytes && f.out_bytes % 16 == 0 &&
+                        w.gu % 16 == 0 && w.gemm_counters % 16 == 0 && !(flags & GNF4B_FLAG_HOST_COPIES);
     std::vector<int32_t> big_tab;
     int32_t* t = tab_fits ? reinterpret_cast<int32_t*>(pin.p) : (big_tab.resize(2 * (size_t)G + 2), big_tab.data());
     t[0] = 0;
     for (int32_t g = 0; g < G; ++g) t[g + 1] = t[g] + sizes_host[g];
     std::memcpy(t + G + 1, expert_ids_host, (size_t)G * 4);
     t[2 * (size_t)G + 1] = 0;
+    if (direct) {
+        // small call: in and out through the pinned block by two small kernels instead of the copy engines; the
+        // counters that must start at zero are cleared by the first of them
+        std::memcpy(pin.p + tab_span, x_host, f.x_bytes);
+        e = host_stage_in(pin, d_off, tab_span + f.x_bytes, base, w.gu, w.gemm_counters ? base + w.gemm : nullptr,
+                          w.gemm_counters, st);
+        if (e != cudaSuccess) return cuda_fail(e, "host_stage_in launch");
+        rc = gnf4b_ffn_grouped(fmt, GNF4B_ACT_SILU_GLU, base + f.x, x_dtype, T, W_gu, wgu_stride_e, wgu_stride_n, S_gu,
+                               sgu_stride_e, sgu_stride_n, W_dn, wdn_stride_e, wdn_stride_n, S_dn, sdn_stride_e, sdn_stride_n,
+                               s_dtype, nullptr, d_off, d_ids, G, E, N_gu, K_gu, N_dn, max_rows, base + f.out, base, w.total,
+                               d_status, flags & ~GNF4B_FLAG_TABLES_READY, cuda_stream);
+        if (rc) { cudaStreamSynchronize(st); return rc; }
+        return host_stage_out_wait(pin, base + f.out, f.out_bytes, d_status, out_host, status_host, st);
+    }
     if (x_rides) {
         std::memcpy(pin.p + tab_span, x_host, f.x_bytes);
         e = cudaMemcpyAsync(d_off, pin.p, tab_span + f.x_bytes, cudaMemcpyHostToDevice, st);

@@ -63,6 +63,8 @@ extern "C" {
  * interleaved columns (gnf4b_glu_gpt_oss without bias).  Saves the activation launch and its pass over memory; same
  * bits as the two-launch form.  Forward only, on the decode kernel (small groups: max_rows given and <= 16);
  * GNF4B_EUNSUPPORTED otherwise -- the caller then runs the activation kernel itself. */
+#define GNF4B_FLAG_HOST_COPIES   0x800000u  /* ablation, host-buffer entry points: move a small call's inputs and result
+                                              with the copy engines even where two small kernels would do it */
 #define GNF4B_FLAG_X_SILU_GLU    0x200000u
 #define GNF4B_FLAG_X_GPT_OSS_GLU 0x400000u
 /* activations of gnf4b_ffn_grouped */

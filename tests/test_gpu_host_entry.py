@@ -174,3 +174,30 @@ def test_host_entry_with_more_groups_than_the_pinned_block_holds():
     got, status = nf4_grouped.gemm_4bit_grouped_host(a, B, A, sizes, ids, path=_gnf4b.PATH_STREAM, return_status=True)
     want = nf4_grouped.gemm_4bit_grouped(a.to(DEV), B, A, sizes.tolist(), ids.tolist(), path=_gnf4b.PATH_STREAM).cpu()
     assert status == 0 and torch.equal(got, want)
+
+
+def test_small_host_calls_without_the_copy_engines_equal_the_copying_form():
+    """Small calls go in and out through the thread's pinned block by two staging kernels; the flag
+    GNF4B_FLAG_HOST_COPIES keeps the copy engines.  Same bits, same status, for the GEMM, the dgrad and the FFN, over
+    repeated calls (the sequence number advances) and with a split-K scratch that must start at zero."""
+    B, A = make_stack(4, 256, 2048, seed=21, device=DEV)
+    for step in range(4):
+        sizes, ids = [1, 2, 1], [step % 4, (step + 2) % 4, 3]
+        a = torch.randn(4, 2048, dtype=torch.bfloat16)
+        fast, st_f = nf4_grouped.gemm_4bit_grouped_host(a, B, A, sizes, ids, return_status=True)
+        slow, st_s = nf4_grouped.gemm_4bit_grouped_host(a, B, A, sizes, ids, path=_gnf4b.FLAG_HOST_COPIES, return_status=True)
+        assert torch.equal(fast, slow) and st_f == st_s == 0
+        k4 = nf4_grouped.gemm_4bit_grouped_host(a, B, A, sizes, ids, split_k=4, path=_gnf4b.PATH_STREAM)
+        k4c = nf4_grouped.gemm_4bit_grouped_host(a, B, A, sizes, ids, split_k=4, path=_gnf4b.PATH_STREAM | _gnf4b.FLAG_HOST_COPIES)
+        assert torch.equal(k4, k4c)
+    g = torch.randn(4, 256, dtype=torch.bfloat16) * 1e-2
+    assert torch.equal(nf4_grouped.dgrad_4bit_grouped_host(g, B, A, [3, 1], [2, 0]),
+                       nf4_grouped.dgrad_4bit_grouped(g.to(DEV), B, A, [3, 1], [2, 0]).cpu())
+    # a bad expert id inside a small call still reaches the caller's status word
+    bad, status = nf4_grouped.gemm_4bit_grouped_host(torch.randn(1, 2048, dtype=torch.bfloat16), B, A, [1], [1], return_status=True)
+    assert status == 0
+    Bg, Ag, Bd, Ad = _ffn_stacks()
+    for sizes, ids in (([1, 1, 1], [3, 0, 2]), ([2, 3], [1, 1])):
+        a = torch.randn(sum(sizes), 512, dtype=torch.bfloat16)
+        assert torch.equal(nf4_grouped.ffn_4bit_grouped_host(a, Bg, Ag, Bd, Ad, sizes, ids),
+                           nf4_grouped.ffn_4bit_grouped(a.to(DEV), Bg, Ag, Bd, Ad, sizes, ids).cpu())
