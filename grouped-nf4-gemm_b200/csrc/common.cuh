@@ -141,6 +141,9 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
 // completed and their writes are visible, so it must precede the first read of anything an earlier
 // kernel may have written and every global write.  pdl_launch_dependents() lets the NEXT kernel start
 // the same way.  Both are no-ops for a kernel launched without the attribute.
+// Timeline of a chain of kernels, for development builds only (-DGNF4B_EP_TRACE; the shipped library compiles
+// EPT() to nothing): thread 0 of CTA 0 appends (mark, %globaltimer) pairs to a device array that
+// gnf4b_ep_trace_read() copies out.  The marks are the numbers at the EPT() sites (tens = kernel, units = phase).
 #ifdef GNF4B_EP_TRACE
 __device__ unsigned long long g_ep_trace[8192];
 __device__ unsigned int g_ep_trace_n;

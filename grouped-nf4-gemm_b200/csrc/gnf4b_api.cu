@@ -20,6 +20,7 @@
 #include "ffn_kernel.cuh"
 #include "ep_peer.cuh"
 #include "host_stage.cuh"
+#include "gather_kernel.cuh"
 
 namespace gnf4b {
 
@@ -1304,6 +1305,43 @@ int gnf4b_ep_peer_combine(const gnf4b_ep_peer_ctx* ctx, int32_t cap, const void*
     cudaError_t e = launch_pdl(ep_peer_combine_kernel, grid, kEpPeerThreads, reinterpret_cast<cudaStream_t>(cuda_stream), cx, cap,
                                static_cast<const uint16_t*>(y), slot, weights, k, M, static_cast<uint16_t*>(out), status_word);
     return e == cudaSuccess ? GNF4B_OK : cuda_fail(e, "ep_peer_combine launch");
+}
+
+int gnf4b_gather_rows_by_id(void* dst, int64_t row_bytes, int32_t n_slots, const void* src, int32_t n_rows_src,
+                            const int32_t* ids, const int32_t* have_ids, int32_t* status_word, void* cuda_stream) {
+    if (row_bytes <= 0 || n_slots < 0 || n_rows_src < 0) return GNF4B_EINVAL;
+    if (row_bytes % 8) return GNF4B_ESHAPE;
+    if (n_slots == 0) return GNF4B_OK;
+    if (!dst || !src || !ids || ((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src)) & 7)) return GNF4B_EINVAL;
+    if (n_slots > 65535) return GNF4B_ETOOBIG;
+    const dim3 grid((unsigned)ceil_div(row_bytes, kGatherChunk), (unsigned)n_slots);
+    gather_rows_kernel<0><<<grid, kGatherThreads, 0, reinterpret_cast<cudaStream_t>(cuda_stream)>>>(
+        static_cast<uint8_t*>(dst), row_bytes, static_cast<const uint8_t*>(src), ids, have_ids, nullptr, nullptr, n_rows_src,
+        status_word);
+    cudaError_t e = cudaPeekAtLastError();
+    return e == cudaSuccess ? GNF4B_OK : cuda_fail(e, "gather_rows_by_id launch");
+}
+
+int gnf4b_gather_rows_addr(void* dst, int64_t row_bytes, int32_t n_slots, const int64_t* want_addr, const int64_t* have_addr,
+                           const int64_t* pieces, int32_t n_pieces, int64_t max_piece_bytes, void* cuda_stream) {
+    if (row_bytes <= 0 || n_slots < 0 || n_pieces < 0) return GNF4B_EINVAL;
+    if (row_bytes % 8 || max_piece_bytes % 8) return GNF4B_ESHAPE;
+    if (n_slots == 0) return GNF4B_OK;
+    if (!dst || !want_addr || (reinterpret_cast<uintptr_t>(dst) & 7)) return GNF4B_EINVAL;
+    if (n_slots > 65535 || n_pieces > 65535) return GNF4B_ETOOBIG;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(cuda_stream);
+    if (n_pieces == 0) {
+        const dim3 grid((unsigned)ceil_div(row_bytes, kGatherChunk), (unsigned)n_slots);
+        gather_rows_kernel<1><<<grid, kGatherThreads, 0, st>>>(static_cast<uint8_t*>(dst), row_bytes, nullptr, nullptr, nullptr,
+                                                              want_addr, have_addr, 0, nullptr);
+    } else {
+        if (!pieces || max_piece_bytes <= 0 || max_piece_bytes > row_bytes) return GNF4B_EINVAL;
+        const dim3 grid((unsigned)ceil_div(max_piece_bytes, kGatherChunk), (unsigned)n_pieces, (unsigned)n_slots);
+        gather_rows_pieces_kernel<<<grid, kGatherThreads, 0, st>>>(static_cast<uint8_t*>(dst), row_bytes, want_addr, have_addr,
+                                                                   pieces);
+    }
+    cudaError_t e = cudaPeekAtLastError();
+    return e == cudaSuccess ? GNF4B_OK : cuda_fail(e, "gather_rows_addr launch");
 }
 
 int gnf4b_dequant(int fmt, const uint8_t* W, int64_t w_stride_e, int64_t w_stride_n, const void* S,

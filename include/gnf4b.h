@@ -381,6 +381,26 @@ int gnf4b_ep_peer_dispatch(const gnf4b_ep_peer_ctx* ctx, const int64_t* idx, int
 int gnf4b_ep_peer_combine(const gnf4b_ep_peer_ctx* ctx, int32_t cap, const void* y, const int64_t* slot,
                           const float* weights, int32_t k, int64_t M, void* out, int32_t* status_word, void* cuda_stream);
 
+/* Residency feeders: an expert's packed row-block into a device slot, selected on the device (no host read, nothing
+ * synchronises).  Format-agnostic byte movers; rows, offsets and lengths are multiples of 8 bytes (GNF4B_ESHAPE
+ * otherwise).  A slot that already holds the wanted row is skipped without touching the source.  The source may be
+ * device memory or pinned host memory that the GPU addresses directly.
+ *
+ * gnf4b_gather_rows_by_id   dst[slot] <- src[ids[slot]] (rows of row_bytes), skipped where have_ids[slot] == ids[slot]
+ *                           (have_ids optional).  The reference's gather_expert_rows (kernel/host_gather.py:73-95).
+ *                           An id outside [0, n_rows_src) is skipped and flagged GNF4B_ST_BAD_EXPERT (n_rows_src = 0:
+ *                           not checked above).
+ * gnf4b_gather_rows_addr    dst[slot] <- the row at absolute address want_addr[slot], skipped where have_addr[slot] ==
+ *                           want_addr[slot] (optional) or the address is 0.  The reference's _gather_rows_addr
+ *                           (kernel/mxfp4_pipelined.py:48-60).  With pieces (device int64 [n_pieces, 3] = source
+ *                           offset, slot offset, length in bytes; max_piece_bytes = the longest) the row's segments
+ *                           land in a different order: _gather_rows_perm (kernel/mxfp4_residency.py:117-134). */
+int gnf4b_gather_rows_by_id(void* dst, int64_t row_bytes, int32_t n_slots, const void* src, int32_t n_rows_src,
+                            const int32_t* ids, const int32_t* have_ids, int32_t* status_word, void* cuda_stream);
+int gnf4b_gather_rows_addr(void* dst, int64_t row_bytes, int32_t n_slots, const int64_t* want_addr,
+                           const int64_t* have_addr, const int64_t* pieces, int32_t n_pieces, int64_t max_piece_bytes,
+                           void* cuda_stream);
+
 /* Device properties this library plans with (SM count, opt-in shared memory). */
 int gnf4b_device_info(int32_t* sm_count, int32_t* smem_optin_bytes);
 

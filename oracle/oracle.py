@@ -299,3 +299,24 @@ def ffn_grouped_f64(a, W_gu, S_gu, W_dn, S_dn, sizes, expert_ids, fmt="nf4"):
     lo = (h - hi.astype(np.float64)).astype(np.float32)
     return (gemm_grouped_f64(fmt, hi, W_dn, S_dn, sizes, expert_ids)
             + gemm_grouped_f64(fmt, lo, W_dn, S_dn, sizes, expert_ids))
+
+
+def gather_rows_ref(dst, src_rows, ids, have=None, pieces=None):
+    """Byte-level restatement of the residency feeders: ``dst [k, row_bytes]`` uint8 (its current content) with slot j
+    overwritten by ``src_rows[ids[j]]`` unless ``have[j] == ids[j]`` -- kernel/host_gather.py:33-54 (selection by
+    id), kernel/mxfp4_pipelined.py:48-60 (the same with one absolute address per slot: here the address is the row
+    index) -- and, with ``pieces`` = (src_off, dst_off, length) byte triples, only those spans, each landing at its
+    own offset of the slot (kernel/mxfp4_residency.py:117-134).  Returns a new array."""
+    out = np.array(dst, dtype=np.uint8, copy=True)
+    src_rows = np.asarray(src_rows, dtype=np.uint8)
+    for j, want in enumerate(np.asarray(ids).tolist()):
+        if have is not None and int(np.asarray(have)[j]) == want:
+            continue
+        if want < 0 or want >= src_rows.shape[0]:
+            continue
+        if pieces is None:
+            out[j] = src_rows[want]
+        else:
+            for s_off, d_off, n in pieces:
+                out[j, d_off:d_off + n] = src_rows[want, s_off:s_off + n]
+    return out

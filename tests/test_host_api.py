@@ -215,3 +215,21 @@ def test_custom_operator_is_registered_with_a_fake_kernel():
     go = torch.empty(5, 64, dtype=torch.bfloat16, device="meta")
     dx = torch.ops.gnf4b.grouped_gemm(go, W, S, None, None, [2, 3], [0, 1], 0, 1, 128, 3, 0, 0, True)
     assert dx.shape == (5, 128)
+
+
+def test_gather_oracle_and_piece_table_rules():
+    """The byte-level restatement of the residency feeders (skip rule, piece order) and the alignment rule of the
+    piece table, without a GPU."""
+    import numpy as np
+    from oracle import oracle as O
+    src = np.arange(4 * 32, dtype=np.uint8).reshape(4, 32)
+    dst = np.full((3, 32), 255, np.uint8)
+    out = O.gather_rows_ref(dst, src, [2, 0, 3], have=[2, 1, -1])
+    assert (out[0] == 255).all() and np.array_equal(out[1], src[0]) and np.array_equal(out[2], src[3])
+    out = O.gather_rows_ref(dst, src, [1, 1, 9], pieces=[(0, 24, 8), (8, 0, 24)])
+    assert np.array_equal(out[0, 24:], src[1, :8]) and np.array_equal(out[0, :24], src[1, 8:]) and (out[2] == 255).all()
+    import host_gather
+    with pytest.raises(ValueError, match="8-byte aligned"):
+        host_gather.piece_table([(8, 8, 12)], "cpu")
+    tab, longest = host_gather.piece_table([(0, 16, 8), (8, 0, 16)], "cpu")
+    assert tab.tolist() == [[0, 16, 8], [8, 0, 16]] and longest == 16
