@@ -683,11 +683,44 @@ def measure_cells(args, dev, peaks, default_layers):
                           "tokens": tokens, "value": us, "unit": "us/call", "rows": len(tok), "active_experts": len(eids),
                           "roofline": _roofline(shape, proj, len(tok), len(eids), us, peaks, dgrad=True), "max_rel_err": err})
 
+    def gather_cell(name, k):
+        """Residency feeder: the packed rows of k experts' gate_up blocks gathered into device slots by
+        device-resident ids -- from a device pool (HBM-bound: every byte read once and written once) and from pinned
+        host memory (PCIe-bound; the figure is reported, the roofline object is the device pool's)."""
+        import host_gather
+        shape = synth.CONFIGS[name]
+        N, K = shape.gate_up
+        row = N * (K // 2)
+        gen = torch.Generator().manual_seed(3000 + k)
+        n_pool = max(2 * k, min(shape.experts, int(1.0e9 // row)))
+        pool = torch.randint(0, 256, (n_pool, row), dtype=torch.uint8, device=dev)
+        host = torch.randint(0, 256, (min(n_pool, 32), row), dtype=torch.uint8).pin_memory()
+        slots = [torch.empty(k, row, dtype=torch.uint8, device=dev) for _ in range(4)]
+        ids = [torch.randperm(n_pool, generator=gen)[:k].to(torch.int32).to(dev) for _ in range(16)]
+        ids_h = [torch.randperm(host.shape[0], generator=gen)[:k].to(torch.int32).to(dev) for _ in range(16)]
+        us_dev = _graph_us(lambda i: host_gather.gather_expert_rows(slots[i % 4], pool, ids[i]), 16)
+        us_host = _graph_us(lambda i: host_gather.gather_expert_rows(slots[i % 4], host, ids_h[i]), 16)
+        host_gather.gather_expert_rows(slots[0], pool, ids[0])
+        exact = bool(torch.equal(slots[0], pool[ids[0].long()]))
+        moved = 2.0 * k * row                       # read once + written once
+        ach = moved / (us_dev * 1e-6) / 1e9
+        cells.append({"workload": f"{shape.name} residency feeder: {k} experts' packed gate_up rows ({row} bytes each) gathered "
+                                  f"into device slots by device-resident ids",
+                      "tokens": 0, "value": us_dev, "unit": "us/gather", "rows": k, "active_experts": k,
+                      "roofline": {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                   "frac": ach / peaks["hbm_gbs"], "traffic": None, "us_per_launch": us_dev,
+                                   "algorithmic_bytes": moved, "peak_source": peaks["source"],
+                                   "kernel": "gather_rows_kernel, source = device pool"},
+                      "pinned_host_source": {"us": us_host, "gbs": k * row / (us_host * 1e-6) / 1e9,
+                                             "note": "zero-copy reads over PCIe; bytes counted once"},
+                      "max_rel_err": 0.0 if exact else 1.0, "bit_exact": exact})
+
     plan = [lambda: fwd_cell("qwen3_30b_a3b", 0, one_row_groups=64), lambda: fwd_cell("qwen3_30b_a3b", 8),
             lambda: fwd_cell("qwen3_30b_a3b", 64), lambda: fwd_cell("qwen3_30b_a3b", 4096),
             lambda: dgrad_cell("qwen3_30b_a3b", 4096),
             lambda: fwd_cell("gpt_oss_20b", 1), lambda: fwd_cell("gpt_oss_20b", 0, one_row_groups=32),
-            lambda: fwd_cell("gpt_oss_20b", 4096)]
+            lambda: fwd_cell("gpt_oss_20b", 4096), lambda: gather_cell("qwen3_30b_a3b", 8),
+            lambda: gather_cell("deepseek_v3", 8)]
     for job in plan:
         try:
             job()
