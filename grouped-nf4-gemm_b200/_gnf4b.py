@@ -32,6 +32,7 @@ FLAG_CTA_PAIR = 0x20000           # forward tensor kernel as CTA pairs (cta_grou
 FLAG_SMEM_OPERANDS = 0x10000      # ablation: forward on the kernel with both MMA operands in shared memory
 FLAG_TABLES_READY = 0x40000       # the group tables were not written by the kernel launched just before
 FLAG_X_SILU_GLU, FLAG_X_GPT_OSS_GLU = 0x200000, 0x400000   # x is the gate_up output; the GLU is applied on load
+FLAG_SPARSE_GROUPS = 0x1000000    # most groups of the list are empty: deal out only the ones that exist
 FLAG_HOST_COPIES = 0x800000       # ablation: host-buffer entries move small calls with the copy engines
 FLAG_FFN_UNFUSED = 0x100000       # ablation: gnf4b_ffn_grouped as three launches even where it would fuse
 ACT_SILU_GLU, ACT_GPT_OSS_GLU = 0, 1

@@ -570,7 +570,7 @@ int gnf4b_gemm_grouped(int fmt, int op, const void* x, int x_dtype, int64_t T, c
             da.rows_per_pass = rm;
             da.row_chunks = (max_rows + rm - 1) / rm;
             // a list with more groups than rows is mostly empty (or padding) groups: walk only the ones that exist
-            da.compact = (da.row_chunks > 1 || ((int64_t)G > T && G <= p.g_cache)) ? 1 : 0;
+            da.compact = (da.row_chunks > 1 || (((int64_t)G > T || (flags & GNF4B_FLAG_SPARSE_GROUPS)) && G <= p.g_cache)) ? 1 : 0;
             da.total_items = (int64_t)G * da.row_chunks * da.tiles_per_group;
             da.tables_ready = (flags & GNF4B_FLAG_TABLES_READY) ? 1 : 0;
             da.x_act = x_act;

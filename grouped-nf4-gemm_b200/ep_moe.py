@@ -515,12 +515,16 @@ class EPGroupedMoE:
         recv = px.recv_rows(cap)
         self.last_rows = W * cap
         max_rows = 1 if one_row else W * M          # an expert can get every token of every rank
-        gu = self.grouped_fn(recv, self.gate_up[0], self.gate_up[1], None, eids, group_offsets=offsets, max_rows=max_rows)
+        # one-row groups: a list of world * cap groups of which the first few exist -- the kernels deal out only those
+        sparse = {"path": _gnf4b.FLAG_SPARSE_GROUPS} if (one_row and self._own_gemm) else {}
+        gu = self.grouped_fn(recv, self.gate_up[0], self.gate_up[1], None, eids, group_offsets=offsets, max_rows=max_rows,
+                             **sparse)
         self._mark("gate_up")
         if self._own_gemm:
             # small groups: the second GEMM applies the activation while it loads the first one's output
             self._mark("glu")
-            y = nf4_grouped.gemm_after_glu(self._fmt_id, gu, self.down[0], self.down[1], eids, offsets, max_rows)
+            y = nf4_grouped.gemm_after_glu(self._fmt_id, gu, self.down[0], self.down[1], eids, offsets, max_rows,
+                                           path=sparse.get("path", 0))
         else:
             h = silu_glu(gu)
             self._mark("glu")

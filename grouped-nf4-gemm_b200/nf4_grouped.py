@@ -548,7 +548,7 @@ def _launch(fmt, op, x, W, S, sizes, expert_ids, n_out, *, split_k=None, path=_g
     return out
 
 
-def gemm_after_glu(fmt, gate_up, W, S, expert_ids, group_offsets, max_rows, act: str = "silu"):
+def gemm_after_glu(fmt, gate_up, W, S, expert_ids, group_offsets, max_rows, act: str = "silu", path: int = 0):
     """The FFN's second GEMM on the OUTPUT of its first: ``gate_up [T, 2K]`` bf16 -> ``[T, N]``, the activation
     (``"silu"``: SiLU(gate_up[:, :K]) * gate_up[:, K:]; ``"gpt_oss"``: the clamped form on interleaved columns)
     applied inside the GEMM kernel while it loads its rows, where a kernel for that exists (small groups), else by
@@ -557,7 +557,7 @@ def gemm_after_glu(fmt, gate_up, W, S, expert_ids, group_offsets, max_rows, act:
     out = None
     if max_rows and max_rows <= 16 and gate_up.dtype == torch.bfloat16:
         out = _launch(fmt, _gnf4b.OP_FWD, gate_up, W, S, None, expert_ids, W.shape[1], group_offsets=group_offsets,
-                      max_rows=max_rows, x_glu=flag)
+                      max_rows=max_rows, x_glu=flag, path=path)
     if out is None:
         if act == "silu":
             import ep_moe
@@ -566,7 +566,7 @@ def gemm_after_glu(fmt, gate_up, W, S, expert_ids, group_offsets, max_rows, act:
             import mxfp4_grouped
             h = mxfp4_grouped.glu_gpt_oss(gate_up)
         out = _launch(fmt, _gnf4b.OP_FWD, h, W, S, None, expert_ids, W.shape[1], group_offsets=group_offsets,
-                      max_rows=max_rows)
+                      max_rows=max_rows, path=path)
     return out
 
 

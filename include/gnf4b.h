@@ -63,6 +63,9 @@ extern "C" {
  * interleaved columns (gnf4b_glu_gpt_oss without bias).  Saves the activation launch and its pass over memory; same
  * bits as the two-launch form.  Forward only, on the decode kernel (small groups: max_rows given and <= 16);
  * GNF4B_EUNSUPPORTED otherwise -- the caller then runs the activation kernel itself. */
+#define GNF4B_FLAG_SPARSE_GROUPS 0x1000000u /* the caller expects most groups of the list to be empty (a fixed-size list
+                                              with the used groups first, padding behind): the decode kernel then deals
+                                              out only the groups that exist, so that all SMs share them */
 #define GNF4B_FLAG_HOST_COPIES   0x800000u  /* ablation, host-buffer entry points: move a small call's inputs and result
                                               with the copy engines even where two small kernels would do it */
 #define GNF4B_FLAG_X_SILU_GLU    0x200000u
@@ -148,7 +151,8 @@ int gnf4b_gemm_grouped(int fmt, int op,
  *     (gnf4b_workspace_bytes) exceeds GNF4B_NOALLOC_SCRATCH_BYTES; nothing is launched.
  *   - Calls no cudaMalloc / cudaFree and no allocating library routine.
  *   - The first call on each device looks the array's device address up
- *     (cudaGetSymbolAddress, with that device current); make that first call outside any
+ *     (cudaGetSymbolAddress, with that device current), which with lazy module loading may also
+ *     load the module that holds the array; make that first call during warm-up, outside any
  *     CUDA stream capture.
  *   - All calls share the one array and it keeps what the last call left: the part that
  *     must start at zero (the arrival counters) is cleared on `cuda_stream` before every

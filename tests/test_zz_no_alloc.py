@@ -61,6 +61,14 @@ def test_noalloc_entry_point_matches_the_allocating_one_twice_in_a_row():
         assert torch.equal(got, want), f"round {round_}"
         assert rel_fro(got, oracle_fwd64("nf4", a, B, A, [1, 1], [3, 0])) <= REL_FRO_TOL
     assert nf4_grouped.last_status(DEV) == 0
+    # the headline property, around a warmed-up call: no device memory is allocated or freed by it
+    a = torch.randn(2, 2048, device=DEV, dtype=torch.bfloat16)
+    got = torch.empty(2, 256, dtype=torch.bfloat16, device=DEV)
+    torch.cuda.synchronize()
+    free_before, allocated_before = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated()
+    assert _call(lib, "noalloc", a, B, A, off, ids, got, split_k) == 0
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before and torch.cuda.memory_allocated() == allocated_before
 
 
 def test_noalloc_entry_point_refuses_scratch_beyond_its_array():
