@@ -136,6 +136,10 @@ def _declare(lib):
     lib.gnf4b_ep_peer_dispatch.argtypes = [vp, vp, i32, i32, i32, i32, vp, vp, i32, vp, vp, vp, vp]
     lib.gnf4b_ep_peer_combine.restype = C.c_int
     lib.gnf4b_ep_peer_combine.argtypes = [vp, i32, vp, vp, vp, i32, i64, vp, vp, vp]
+    lib.gnf4b_ep_plan_large_scratch_bytes.restype = sz
+    lib.gnf4b_ep_plan_large_scratch_bytes.argtypes = [i64, i32]
+    lib.gnf4b_ep_plan_large.restype = C.c_int
+    lib.gnf4b_ep_plan_large.argtypes = [vp, i64, i32, i32, i32, i32, vp, i64, vp, vp, vp, vp, sz, vp, vp]
     lib.gnf4b_gather_rows_by_id.restype = C.c_int
     lib.gnf4b_gather_rows_by_id.argtypes = [vp, i64, i32, vp, i32, vp, vp, vp, vp]
     lib.gnf4b_gather_rows_addr.restype = C.c_int
@@ -161,7 +165,7 @@ EXPORTS = ("gnf4b_abi_version", "gnf4b_strerror", "gnf4b_last_cuda_error", "gnf4
            "gnf4b_glu_gpt_oss",
            "gnf4b_workspace_bytes", "gnf4b_plan_split_k", "gnf4b_build_offsets", "gnf4b_upload_i32", "gnf4b_dequant", "gnf4b_silu_glu", "gnf4b_combine_rows", "gnf4b_ep_plan", "gnf4b_ep_offsets", "gnf4b_route_topk",
            "gnf4b_ep_peer_layout", "gnf4b_ep_peer_dispatch", "gnf4b_ep_peer_combine",
-           "gnf4b_gather_rows_by_id", "gnf4b_gather_rows_addr",
+           "gnf4b_gather_rows_by_id", "gnf4b_gather_rows_addr", "gnf4b_ep_plan_large", "gnf4b_ep_plan_large_scratch_bytes",
            "gnf4b_device_info")
 
 

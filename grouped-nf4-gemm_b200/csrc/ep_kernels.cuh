@@ -249,3 +249,100 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, int64_t T, i
 }
 
 }  // namespace gnf4b
+
+namespace gnf4b {
+
+// Routing plan of a LARGE batch (any number of pairs): the stable sort of the (token, choice) pairs by
+// (half, global expert id) as a counting sort over several CTAs, and the gather of the pairs' hidden rows into that
+// order.  half = 1 for experts whose local index (id % e_local) is >= cut, so that with cut < e_local every rank's
+// lower experts come first (the layer pipelined over two halves of the local experts); cut = e_local: one half.
+// Three small kernels and one copy:
+//   hist    CTA b counts the bins of its chunk of kEpChunk pairs                       -> hist[b][bin]
+//   starts  one CTA: per bin the pairs of lower bins and of lower CTAs                  -> hist[b][bin] = first position,
+//           per expert the number of pairs                                              -> counts[e]
+//   place   CTA b: position of each of its pairs = first position of (b, bin) + the pair's rank among the
+//           chunk's earlier pairs of the same bin (stable)                              -> pos[p]
+//   rows    send[pos[p], :] = hidden[p / k, :], 16 bytes per thread and step
+// Same order as a stable argsort of the keys; an expert id outside [0, n_experts) is flagged and its pair is placed
+// after all valid pairs (never sent: it is counted by no expert).
+constexpr int kEpChunk = 512;
+constexpr int kEpLargeThreads = 256;
+constexpr int kEpMaxBins = 2048 + 1;          // 2 halves x 1024 experts + the bin of invalid ids
+
+__device__ __forceinline__ int32_t ep_bin(int64_t e, int32_t n_experts, int32_t e_local, int32_t cut) {
+    if (e < 0 || e >= n_experts) return 2 * n_experts;
+    return (int32_t)e + (((int32_t)e % e_local) >= cut ? n_experts : 0);
+}
+
+__global__ void __launch_bounds__(kEpLargeThreads)
+ep_large_hist_kernel(const int64_t* __restrict__ idx, int64_t P, int32_t n_experts, int32_t e_local, int32_t cut,
+                     int32_t* __restrict__ hist, int32_t* status) {
+    __shared__ int32_t s_h[kEpMaxBins];
+    const int n_bins = 2 * n_experts + 1;
+    for (int i = threadIdx.x; i < n_bins; i += kEpLargeThreads) s_h[i] = 0;
+    __syncthreads();
+    const int64_t lo = (int64_t)blockIdx.x * kEpChunk;
+    for (int i = threadIdx.x; i < kEpChunk && lo + i < P; i += kEpLargeThreads) {
+        const int32_t b = ep_bin(__ldg(idx + lo + i), n_experts, e_local, cut);
+        if (b == 2 * n_experts && status) atomicOr(status, GNF4B_ST_BAD_EXPERT);
+        atomicAdd(&s_h[b], 1);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_bins; i += kEpLargeThreads) hist[(int64_t)blockIdx.x * n_bins + i] = s_h[i];
+}
+
+__global__ void __launch_bounds__(1024, 1)
+ep_large_starts_kernel(int32_t* __restrict__ hist, int32_t n_ctas, int32_t n_experts, int32_t* __restrict__ counts) {
+    __shared__ int32_t s_tot[kEpMaxBins];
+    __shared__ int32_t s_start[kEpMaxBins];
+    const int n_bins = 2 * n_experts + 1;
+    for (int b = threadIdx.x; b < n_bins; b += blockDim.x) {
+        int32_t n = 0;
+        for (int c = 0; c < n_ctas; ++c) n += hist[(int64_t)c * n_bins + b];
+        s_tot[b] = n;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int32_t at = 0;
+        for (int b = 0; b < n_bins; ++b) { s_start[b] = at; at += s_tot[b]; }
+    }
+    __syncthreads();
+    for (int b = threadIdx.x; b < n_bins; b += blockDim.x) {
+        int32_t at = s_start[b];
+        for (int c = 0; c < n_ctas; ++c) {
+            const int32_t n = hist[(int64_t)c * n_bins + b];
+            hist[(int64_t)c * n_bins + b] = at;
+            at += n;
+        }
+    }
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) counts[e] = s_tot[e] + s_tot[e + n_experts];
+}
+
+__global__ void __launch_bounds__(kEpLargeThreads)
+ep_large_place_kernel(const int64_t* __restrict__ idx, int64_t P, int32_t n_experts, int32_t e_local, int32_t cut,
+                      const int32_t* __restrict__ hist, int64_t* __restrict__ pos) {
+    __shared__ int32_t s_bin[kEpChunk];
+    const int n_bins = 2 * n_experts + 1;
+    const int64_t lo = (int64_t)blockIdx.x * kEpChunk;
+    const int n = (int)min((int64_t)kEpChunk, P - lo);
+    for (int i = threadIdx.x; i < n; i += kEpLargeThreads) s_bin[i] = ep_bin(__ldg(idx + lo + i), n_experts, e_local, cut);
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += kEpLargeThreads) {
+        const int32_t b = s_bin[i];
+        int32_t rank = 0;
+        for (int q = 0; q < i; ++q) rank += (s_bin[q] == b);
+        pos[lo + i] = (int64_t)__ldg(hist + (int64_t)blockIdx.x * n_bins + b) + rank;
+    }
+}
+
+__global__ void __launch_bounds__(kEpLargeThreads)
+ep_large_rows_kernel(const uint16_t* __restrict__ hidden, int64_t P, int32_t k, int64_t H, const int64_t* __restrict__ pos,
+                     uint16_t* __restrict__ send) {
+    const int64_t per_row = H / 8;
+    for (int64_t i = (int64_t)blockIdx.x * kEpLargeThreads + threadIdx.x; i < P * per_row; i += (int64_t)gridDim.x * kEpLargeThreads) {
+        const int64_t p = i / per_row, c = (i - p * per_row) * 8;
+        *reinterpret_cast<uint4*>(send + __ldg(pos + p) * H + c) = __ldg(reinterpret_cast<const uint4*>(hidden + (p / k) * H + c));
+    }
+}
+
+}  // namespace gnf4b

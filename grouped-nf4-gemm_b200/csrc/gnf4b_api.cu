@@ -1237,6 +1237,39 @@ int gnf4b_ep_plan(const int64_t* idx, int32_t P, int32_t k, int32_t n_experts, i
     return e == cudaSuccess ? GNF4B_OK : cuda_fail(e, "ep_plan launch");
 }
 
+size_t gnf4b_ep_plan_large_scratch_bytes(int64_t P, int32_t n_experts) {
+    if (P <= 0 || n_experts <= 0 || n_experts > 1024) return 0;
+    return (size_t)ceil_div(P, (int64_t)kEpChunk) * (size_t)(2 * n_experts + 1) * 4;
+}
+
+int gnf4b_ep_plan_large(const int64_t* idx, int64_t P, int32_t k, int32_t n_experts, int32_t e_local, int32_t cut,
+                        const void* hidden, int64_t H, int32_t* counts, int64_t* pos, void* send, void* scratch,
+                        size_t scratch_bytes, int32_t* status_word, void* cuda_stream) {
+    if (P < 0 || k <= 0 || n_experts <= 0 || e_local <= 0 || n_experts % e_local || cut < 0 || cut > e_local || H <= 0)
+        return GNF4B_EINVAL;
+    if (n_experts > 1024 || P > ((int64_t)1 << 26)) return GNF4B_ETOOBIG;
+    if (H % 8) return GNF4B_ESHAPE;
+    if (!counts || (P > 0 && (!idx || !hidden || !pos || !send))) return GNF4B_EINVAL;
+    if ((reinterpret_cast<uintptr_t>(hidden) | reinterpret_cast<uintptr_t>(send)) & 15) return GNF4B_EINVAL;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(cuda_stream);
+    if (P == 0) {
+        cudaError_t e0 = cudaMemsetAsync(counts, 0, (size_t)n_experts * 4, st);
+        return e0 == cudaSuccess ? GNF4B_OK : cuda_fail(e0, "cudaMemsetAsync(counts)");
+    }
+    if (!scratch || scratch_bytes < gnf4b_ep_plan_large_scratch_bytes(P, n_experts)) return GNF4B_EWORKSPACE;
+    int32_t* hist = static_cast<int32_t*>(scratch);
+    const int n_ctas = (int)ceil_div(P, (int64_t)kEpChunk);
+    ep_large_hist_kernel<<<n_ctas, kEpLargeThreads, 0, st>>>(idx, P, n_experts, e_local, cut, hist, status_word);
+    ep_large_starts_kernel<<<1, 1024, 0, st>>>(hist, n_ctas, n_experts, counts);
+    ep_large_place_kernel<<<n_ctas, kEpLargeThreads, 0, st>>>(idx, P, n_experts, e_local, cut, hist, pos);
+    const int64_t items = P * (H / 8);
+    const unsigned grid = (unsigned)std::min<int64_t>(ceil_div(items, (int64_t)kEpLargeThreads), 148 * 32);
+    ep_large_rows_kernel<<<grid, kEpLargeThreads, 0, st>>>(static_cast<const uint16_t*>(hidden), P, k, H, pos,
+                                                          static_cast<uint16_t*>(send));
+    cudaError_t e = cudaPeekAtLastError();
+    return e == cudaSuccess ? GNF4B_OK : cuda_fail(e, "ep_plan_large launch");
+}
+
 int gnf4b_ep_offsets(const int32_t* recv_counts, int32_t world, int32_t e_local, int32_t cap, int32_t* offsets,
                      int32_t* status_word, void* cuda_stream) {
     if (world <= 0 || e_local <= 0 || cap < 0 || !recv_counts || !offsets) return GNF4B_EINVAL;

@@ -252,6 +252,7 @@ class EPGroupedMoE:
         # the host read, not time on NVLink, and two more collectives and smaller GEMMs cost more than the overlap brings
         self.split_experts = (os.environ.get("GNF4B_EP_SPLIT", "0") == "1") if split_experts is None else bool(split_experts)
         self._streams = None
+        self._host_counts = None     # pinned landing buffer of the large-batch path's one host read
         self._local_eids = None
         self.last_rows = 0
 
@@ -298,22 +299,51 @@ class EPGroupedMoE:
         k = idx.shape[1]
         flat = idx.reshape(-1).to(torch.int64)
         cut = El - El // 2 if halves == 2 else El                       # local experts [0, cut) are half 0
-        # stable sort by (half, global expert id) = (half, destination rank, local expert), token order kept
-        key = flat if halves == 1 else flat + ((flat % El) >= cut).to(torch.int64) * self.n_experts
-        order = torch.argsort(key, stable=True)
-        tok = order // k
-        counts = torch.zeros(self.n_experts, dtype=torch.int64, device=dev).scatter_add_(
-            0, flat, torch.ones_like(flat)).reshape(W, El)
-        counts32 = counts.to(torch.int32).contiguous()
-        recv_counts = torch.empty_like(counts32)
-        self._a2a(recv_counts.reshape(-1), counts32.reshape(-1), None, None)
-        # work that does not depend on the counts is queued before the host waits for them
-        send = hidden[tok]
-        pos = torch.empty_like(order)        # pair (m, j) sits at sorted position pos[m * k + j]
-        pos[order] = torch.arange(order.numel(), device=dev)
+        both = torch.empty(2, W, El, dtype=torch.int32, device=dev)     # [0] what this rank sends, [1] what it receives
+        counts32, recv_counts = both[0], both[1]
+        use_lib = (hidden.is_cuda and hidden.dtype == torch.bfloat16 and hidden.is_contiguous() and H % 8 == 0
+                   and self.n_experts <= 1024 and self._own_gemm)
+        if use_lib:
+            # the stable sort by (half, global expert id), the per-expert counts and the row gather as four small
+            # kernels of the library (a counting sort; the tensor operations below take ~150 us more at 32768 pairs)
+            import _gnf4b
+            import nf4_grouped
+            lib = _gnf4b.load()
+            P = flat.numel()
+            need = lib.gnf4b_ep_plan_large_scratch_bytes(P, self.n_experts)
+            scratch = torch.empty(max(need, 4), dtype=torch.uint8, device=dev)
+            pos = torch.empty(P, dtype=torch.int64, device=dev)
+            send = torch.empty(P, H, dtype=hidden.dtype, device=dev)
+            with torch.cuda.device(dev):
+                _gnf4b.check(lib.gnf4b_ep_plan_large(flat.data_ptr(), P, k, self.n_experts, El, cut, hidden.data_ptr(), H,
+                                                     counts32.data_ptr(), pos.data_ptr(), send.data_ptr(), scratch.data_ptr(),
+                                                     need, nf4_grouped._status_word(dev).data_ptr(),
+                                                     torch.cuda.current_stream(dev).cuda_stream), "gnf4b_ep_plan_large")
+            self._a2a(recv_counts.reshape(-1), counts32.reshape(-1), None, None)
+        else:
+            # stable sort by (half, global expert id) = (half, destination rank, local expert), token order kept
+            key = flat if halves == 1 else flat + ((flat % El) >= cut).to(torch.int64) * self.n_experts
+            order = torch.argsort(key, stable=True)
+            tok = order // k
+            counts = torch.zeros(self.n_experts, dtype=torch.int64, device=dev).scatter_add_(
+                0, flat, torch.ones_like(flat)).reshape(W, El)
+            counts32.copy_(counts)
+            self._a2a(recv_counts.reshape(-1), counts32.reshape(-1), None, None)
+            # work that does not depend on the counts is queued before the host waits for them
+            send = hidden[tok]
+            pos = torch.empty_like(order)        # pair (m, j) sits at sorted position pos[m * k + j]
+            pos[order] = torch.arange(order.numel(), device=dev)
         # the exchange needs its split sizes on the host: ONE small read per layer brings both count
-        # tables, everything else about the layer's shape is derived from them on the host
-        host = torch.stack((counts32, recv_counts)).cpu()
+        # tables, everything else about the layer's shape is derived from them on the host.  On a GPU the read
+        # lands in a pinned buffer (a copy to pageable memory costs ~150 us more)
+        if hidden.is_cuda:
+            if self._host_counts is None or self._host_counts.shape != both.shape:
+                self._host_counts = torch.empty(both.shape, dtype=torch.int32).pin_memory()
+            self._host_counts.copy_(both, non_blocking=True)
+            torch.cuda.current_stream(dev).synchronize()
+            host = self._host_counts.clone()
+        else:
+            host = both.clone()
         ret = torch.empty_like(send)
         self.last_rows = int(host[1].sum())
         if halves == 1:

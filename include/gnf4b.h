@@ -342,6 +342,19 @@ int gnf4b_ep_plan(const int64_t* idx, int32_t P, int32_t k, int32_t n_experts, i
 int gnf4b_ep_offsets(const int32_t* recv_counts, int32_t world, int32_t e_local, int32_t cap, int32_t* offsets,
                      int32_t* status_word, void* cuda_stream);
 
+/* Routing plan of a LARGE batch (any P up to 2^26 pairs): the stable sort of the pairs by (half, global expert id) as
+ * a counting sort over several CTAs -- the order of a stable argsort of those keys -- and the gather of the pairs'
+ * hidden rows into it.  half = 1 for experts whose local index (id % e_local) is >= cut (cut = e_local: one half);
+ * with two halves every rank's lower experts come first, which lets a caller exchange and multiply them while the
+ * upper half is still in flight.  Outputs: counts[n_experts] (int32 pairs per expert), pos[P] (int64 position of
+ * pair p in the sorted order), send (bf16 [P, H]: send[pos[p]] = hidden[p / k]).  scratch: device memory of
+ * gnf4b_ep_plan_large_scratch_bytes(P, n_experts) bytes, any content.  An id outside [0, n_experts) is flagged
+ * GNF4B_ST_BAD_EXPERT and placed behind all valid pairs. */
+size_t gnf4b_ep_plan_large_scratch_bytes(int64_t P, int32_t n_experts);
+int gnf4b_ep_plan_large(const int64_t* idx, int64_t P, int32_t k, int32_t n_experts, int32_t e_local, int32_t cut,
+                        const void* hidden, int64_t H, int32_t* counts, int64_t* pos, void* send, void* scratch,
+                        size_t scratch_bytes, int32_t* status_word, void* cuda_stream);
+
 /* The same small-batch exchange without a collective library (expert-parallel layer; no reference counterpart):
  * each rank owns ONE exchange buffer of gnf4b_ep_peer_layout(...)[0] bytes that every other rank of the node can
  * address (peer access / symmetric memory); ctx.peers[r] is rank r's buffer as THIS process addresses it, 256-byte

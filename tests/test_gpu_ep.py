@@ -319,3 +319,44 @@ def test_peer_exchange_wait_runs_out_and_sets_the_status():
     assert lib.gnf4b_ep_peer_dispatch(ctypes.byref(ctx), idx.data_ptr(), 4, 2, world * e_local, cap + 1, hidden.data_ptr(),
                                       slot.data_ptr(), 0, offsets.data_ptr(), None, status.data_ptr(), st) == -6
     assert torch.randn(8, device="cuda").sum().isfinite()
+
+
+@pytest.mark.parametrize("M,k,E,El,cut", [(700, 4, 16, 8, 8), (700, 4, 16, 8, 4), (4096, 8, 128, 64, 32), (3, 2, 8, 4, 1),
+                                          (513, 1, 1024, 128, 128)])
+def test_large_batch_plan_equals_the_stable_argsort(M, k, E, El, cut):
+    """gnf4b_ep_plan_large (a counting sort over several CTAs) against the tensor form it replaces: positions of
+    the pairs in the stable order of (half, expert id), per-expert counts, gathered rows -- integer / bit equality."""
+    import _gnf4b
+    import nf4_grouped
+    lib = _gnf4b.load()
+    gen = torch.Generator().manual_seed(M + cut)
+    H = 64
+    idx = torch.randint(0, E, (M, k), generator=gen).cuda()
+    hidden = torch.randn(M, H, generator=gen).to(torch.bfloat16).cuda()
+    flat = idx.reshape(-1)
+    P = flat.numel()
+    key = flat + ((flat % El) >= cut).to(torch.int64) * E
+    order = torch.argsort(key, stable=True)
+    want_pos = torch.empty_like(order)
+    want_pos[order] = torch.arange(P, device="cuda")
+    want_counts = torch.bincount(flat, minlength=E).to(torch.int32)
+    need = lib.gnf4b_ep_plan_large_scratch_bytes(P, E)
+    scratch = torch.full((need,), 0x5A, dtype=torch.uint8, device="cuda")        # any content
+    counts = torch.empty(E, dtype=torch.int32, device="cuda")
+    pos = torch.empty(P, dtype=torch.int64, device="cuda")
+    send = torch.empty(P, H, dtype=torch.bfloat16, device="cuda")
+    rc = lib.gnf4b_ep_plan_large(flat.data_ptr(), P, k, E, El, cut, hidden.data_ptr(), H, counts.data_ptr(), pos.data_ptr(),
+                                 send.data_ptr(), scratch.data_ptr(), need, nf4_grouped._status_word("cuda").data_ptr(),
+                                 torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    assert torch.equal(pos, want_pos) and torch.equal(counts, want_counts)
+    assert torch.equal(send, hidden[order // k])
+    assert nf4_grouped.last_status("cuda") == 0
+    # an id outside the experts: flagged, placed behind every valid pair, counted by no expert
+    flat2 = flat.clone()
+    flat2[0] = E + 3
+    rc = lib.gnf4b_ep_plan_large(flat2.data_ptr(), P, k, E, El, cut, hidden.data_ptr(), H, counts.data_ptr(), pos.data_ptr(),
+                                 send.data_ptr(), scratch.data_ptr(), need, nf4_grouped._status_word("cuda").data_ptr(),
+                                 torch.cuda.current_stream().cuda_stream)
+    assert rc == 0 and int(pos[0]) == P - 1 and int(counts.sum()) == P - 1
+    assert nf4_grouped.last_status("cuda") & _gnf4b.ST_BAD_EXPERT
