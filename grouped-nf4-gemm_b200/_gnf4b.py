@@ -140,6 +140,10 @@ def _declare(lib):
     lib.gnf4b_ep_plan_large_scratch_bytes.argtypes = [i64, i32]
     lib.gnf4b_ep_plan_large.restype = C.c_int
     lib.gnf4b_ep_plan_large.argtypes = [vp, i64, i32, i32, i32, i32, vp, i64, vp, vp, vp, vp, sz, vp, vp]
+    lib.gnf4b_ep_push_blocks.restype = C.c_int
+    lib.gnf4b_ep_push_blocks.argtypes = [i32, vp, vp, vp, vp, i32, vp, vp]
+    lib.gnf4b_ep_wait_flags.restype = C.c_int
+    lib.gnf4b_ep_wait_flags.argtypes = [vp, i32, i32, i32, vp, vp]
     lib.gnf4b_gather_rows_by_id.restype = C.c_int
     lib.gnf4b_gather_rows_by_id.argtypes = [vp, i64, i32, vp, i32, vp, vp, vp, vp]
     lib.gnf4b_gather_rows_addr.restype = C.c_int
@@ -166,6 +170,7 @@ EXPORTS = ("gnf4b_abi_version", "gnf4b_strerror", "gnf4b_last_cuda_error", "gnf4
            "gnf4b_workspace_bytes", "gnf4b_plan_split_k", "gnf4b_build_offsets", "gnf4b_upload_i32", "gnf4b_dequant", "gnf4b_silu_glu", "gnf4b_combine_rows", "gnf4b_ep_plan", "gnf4b_ep_offsets", "gnf4b_route_topk",
            "gnf4b_ep_peer_layout", "gnf4b_ep_peer_dispatch", "gnf4b_ep_peer_combine",
            "gnf4b_gather_rows_by_id", "gnf4b_gather_rows_addr", "gnf4b_ep_plan_large", "gnf4b_ep_plan_large_scratch_bytes",
+           "gnf4b_ep_push_blocks", "gnf4b_ep_wait_flags",
            "gnf4b_device_info")
 
 

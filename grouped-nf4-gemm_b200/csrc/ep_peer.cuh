@@ -530,3 +530,77 @@ ep_peer_combine_kernel(EpPeerCtx cx, int32_t cap, const uint16_t* __restrict__ y
 }
 
 }  // namespace gnf4b
+
+namespace gnf4b {
+
+// Large batches: blocks of rows pushed into the peers' buffers by all SMs with plain 16-byte stores, then one flag per
+// destination behind a system-scope fence (at these sizes the fence is noise); the receiver waits on its flags before
+// its GEMMs read the rows.  The host knows every block's place (it has read the counts of all ranks), so the kernel
+// is a list of up to kEpPeerMaxWorld copies.  Flags carry the caller's step number and only grow.
+struct EpPushArgs {
+    const uint8_t* src[kEpPeerMaxWorld];
+    uint8_t* dst[kEpPeerMaxWorld];
+    int64_t bytes[kEpPeerMaxWorld];            // multiples of 16
+    int32_t* flag[kEpPeerMaxWorld];            // this rank's flag word in every peer's buffer (null: no flag)
+    int32_t* done_counter;                     // this rank only: finished-CTA counter, left at zero
+    int32_t n, step;
+};
+
+constexpr int64_t kEpPushChunk = 64 << 10;     // bytes of one block a CTA takes at a time
+
+__global__ void __launch_bounds__(kEpPeerThreads)
+ep_push_blocks_kernel(const EpPushArgs a) {
+    // chunks of all blocks numbered through; CTA c takes chunks c, c + grid, ...
+    int64_t first[kEpPeerMaxWorld + 1];
+    first[0] = 0;
+    for (int b = 0; b < a.n; ++b) first[b + 1] = first[b] + (a.bytes[b] + kEpPushChunk - 1) / kEpPushChunk;
+    for (int64_t c = blockIdx.x; c < first[a.n]; c += gridDim.x) {
+        int b = 0;
+        while (c >= first[b + 1]) ++b;
+        const int64_t lo = (c - first[b]) * kEpPushChunk, hi = min(a.bytes[b], lo + kEpPushChunk);
+        const uint4* s = reinterpret_cast<const uint4*>(a.src[b] + lo);
+        uint4* d = reinterpret_cast<uint4*>(a.dst[b] + lo);
+        const int64_t n16 = (hi - lo) >> 4;
+        for (int64_t i = threadIdx.x; i < n16; i += (int64_t)kEpPeerThreads * 4) {
+            uint4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (i + (int64_t)u * kEpPeerThreads < n16) v[u] = __ldg(s + i + (int64_t)u * kEpPeerThreads);
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (i + (int64_t)u * kEpPeerThreads < n16) d[i + (int64_t)u * kEpPeerThreads] = v[u];
+        }
+    }
+    // the CTA's stores are ordered before thread 0 by the barrier, its fence orders them before its count; the CTA
+    // that finds all others counted raises the flags
+    __syncthreads();
+    if (threadIdx.x != 0) return;
+    __threadfence_system();
+    if (atomicAdd(a.done_counter, 1) != (int32_t)gridDim.x - 1) return;
+    __threadfence_system();
+    *a.done_counter = 0;
+    for (int b = 0; b < a.n; ++b)
+        if (a.flag[b]) asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(a.flag[b]), "r"(a.step) : "memory");
+}
+
+// Wait until every one of `world` flag words has reached `step` (bounded: limit_ns; GNF4B_ST_TIMEOUT on expiry).
+__global__ void ep_wait_flags_kernel(const int32_t* flags, int32_t world, int32_t step, uint64_t limit_ns, int32_t* status) {
+    if ((int)threadIdx.x >= world) return;
+    const int32_t* f = flags + threadIdx.x;
+    int32_t v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+    uint64_t t0 = 0;
+    for (uint32_t it = 0; (int32_t)(v - step) < 0; ++it) {
+        if (it >= 64) {
+            __nanosleep(200);
+            if (it == 64) t0 = global_timer_ns();
+            else if ((it & 255) == 0 && global_timer_ns() - t0 > limit_ns) {
+                if (status) atomicOr(status, GNF4B_ST_TIMEOUT);
+                break;
+            }
+        }
+        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+    }
+}
+
+}  // namespace gnf4b

@@ -1237,6 +1237,45 @@ int gnf4b_ep_plan(const int64_t* idx, int32_t P, int32_t k, int32_t n_experts, i
     return e == cudaSuccess ? GNF4B_OK : cuda_fail(e, "ep_plan launch");
 }
 
+int gnf4b_ep_push_blocks(int32_t n, const void* const* src, void* const* dst, const int64_t* bytes, int32_t* const* flags,
+                         int32_t step, int32_t* done_counter, void* cuda_stream) {
+    if (n < 0 || n > kEpPeerMaxWorld || !done_counter) return GNF4B_EINVAL;
+    if (n == 0) return GNF4B_OK;
+    if (!src || !dst || !bytes) return GNF4B_EINVAL;
+    EpPushArgs a;
+    std::memset(&a, 0, sizeof(a));
+    int64_t chunks = 0;
+    for (int b = 0; b < n; ++b) {
+        if (bytes[b] < 0 || (bytes[b] % 16)) return GNF4B_ESHAPE;
+        if (bytes[b] > 0 && (!src[b] || !dst[b] || ((reinterpret_cast<uintptr_t>(src[b]) | reinterpret_cast<uintptr_t>(dst[b])) & 15)))
+            return GNF4B_EINVAL;
+        a.src[b] = static_cast<const uint8_t*>(src[b]);
+        a.dst[b] = static_cast<uint8_t*>(dst[b]);
+        a.bytes[b] = bytes[b];
+        a.flag[b] = flags ? flags[b] : nullptr;
+        chunks += ceil_div(bytes[b], kEpPushChunk);
+    }
+    a.n = n;
+    a.step = step;
+    a.done_counter = done_counter;
+    DevInfo di;
+    int rc = device_info(&di);
+    if (rc) return rc;
+    const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(chunks, 2 * (int64_t)di.sm_count));
+    ep_push_blocks_kernel<<<grid, kEpPeerThreads, 0, reinterpret_cast<cudaStream_t>(cuda_stream)>>>(a);
+    cudaError_t e = cudaPeekAtLastError();
+    return e == cudaSuccess ? GNF4B_OK : cuda_fail(e, "ep_push_blocks launch");
+}
+
+int gnf4b_ep_wait_flags(const int32_t* flags, int32_t world, int32_t step, int32_t timeout_ms, int32_t* status_word,
+                        void* cuda_stream) {
+    if (!flags || world <= 0 || world > kEpPeerMaxWorld || timeout_ms <= 0) return GNF4B_EINVAL;
+    ep_wait_flags_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(cuda_stream)>>>(flags, world, step,
+                                                                                   (uint64_t)timeout_ms * 1000000ull, status_word);
+    cudaError_t e = cudaPeekAtLastError();
+    return e == cudaSuccess ? GNF4B_OK : cuda_fail(e, "ep_wait_flags launch");
+}
+
 size_t gnf4b_ep_plan_large_scratch_bytes(int64_t P, int32_t n_experts) {
     if (P <= 0 || n_experts <= 0 || n_experts > 1024) return 0;
     return (size_t)ceil_div(P, (int64_t)kEpChunk) * (size_t)(2 * n_experts + 1) * 4;

@@ -216,6 +216,48 @@ class PeerExchange:
         return self.buf[self.recv_off:self.recv_off + n].view(torch.bfloat16).view(self.world * cap, self.H)
 
 
+class LargePeerExchange:
+    """Symmetric buffers of the large-batch exchange: [flags of dispatch | flags of combine | counter | received rows
+    (cap_recv x H) | returned rows (cap_ret x H)], one per rank, mapped into every rank.  Built collectively."""
+
+    def __init__(self, group, world, rank, cap_recv, cap_ret, H, device):
+        import torch.distributed._symmetric_memory as symm
+        self.world, self.rank, self.H = world, rank, H
+        self.cap_recv, self.cap_ret = int(cap_recv), int(cap_ret)
+        self.flags_dispatch_off, self.flags_combine_off, self.done_off = 0, 64, 128
+        self.recv_off = 256
+        self.ret_off = self.recv_off + (self.cap_recv * H * 2 + 255) // 256 * 256
+        total = self.ret_off + (self.cap_ret * H * 2 + 255) // 256 * 256
+        pg = group if group is not None else dist.group.WORLD
+        self.buf = symm.empty(total, dtype=torch.uint8, device=device)
+        self.buf[:256].zero_()
+        self.handle = symm.rendezvous(self.buf, pg)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        torch.cuda.synchronize(device)
+        dist.barrier(group)              # every header is zeroed before any rank raises a flag in it
+        self.step = 0
+        self.timeout_ms = 10000
+
+    _shared = {}
+
+    @classmethod
+    def shared(cls, group, world, rank, cap_recv, cap_ret, H, device):
+        """One set of buffers per (group, capacity, device) for all layers of a process (they run one after the other
+        on one stream, and every rank uses the buffers in the same order)."""
+        key = (id(group) if group is not None else 0, world, rank, int(cap_recv), int(cap_ret), H, str(device))
+        px = cls._shared.get(key)
+        if px is None:
+            px = cls._shared[key] = cls(group, world, rank, cap_recv, cap_ret, H, device)
+        return px
+
+    def next_step(self) -> int:
+        self.step += 1
+        return self.step
+
+    def view(self, off, rows, H):
+        return self.buf[off:off + rows * H * 2].view(torch.bfloat16).view(rows, H)
+
+
 class EPGroupedMoE:
     """One expert-parallel MoE layer.  ``gate_up`` / ``down`` are this rank's shards
     ``(W [E/W, N, K/2] u8, S scales)``; ``grouped_fn(a_cat, W, S, sizes, expert_ids)`` is the
@@ -253,6 +295,11 @@ class EPGroupedMoE:
         self.split_experts = (os.environ.get("GNF4B_EP_SPLIT", "0") == "1") if split_experts is None else bool(split_experts)
         self._streams = None
         self._host_counts = None     # pinned landing buffer of the large-batch path's one host read
+        self._host_all = None
+        # large batches over the library's own stores into symmetric buffers (GNF4B_EP_PEER_LARGE=0: NCCL all-to-all)
+        self.peer_large = os.environ.get("GNF4B_EP_PEER_LARGE", "1") != "0"
+        self._peer_large_buf = {}
+        self._peer_recv_counts = None
         self._local_eids = None
         self.last_rows = 0
 
@@ -319,7 +366,15 @@ class EPGroupedMoE:
                                                      counts32.data_ptr(), pos.data_ptr(), send.data_ptr(), scratch.data_ptr(),
                                                      need, nf4_grouped._status_word(dev).data_ptr(),
                                                      torch.cuda.current_stream(dev).cuda_stream), "gnf4b_ep_plan_large")
-            self._a2a(recv_counts.reshape(-1), counts32.reshape(-1), None, None)
+            if self.peer_exchange and self.peer_large and halves == 1 and W > 1:
+                out = self._exact_peer(hidden, idx, weights, counts32, pos, send)
+                if out is not None:
+                    return out
+                # (capacity of the symmetric buffers exceeded: this step goes over NCCL; recv_counts was filled)
+                recv_counts = self._peer_recv_counts
+                both = torch.stack((counts32, recv_counts))
+            else:
+                self._a2a(recv_counts.reshape(-1), counts32.reshape(-1), None, None)
         else:
             # stable sort by (half, global expert id) = (half, destination rank, local expert), token order kept
             key = flat if halves == 1 else flat + ((flat % El) >= cut).to(torch.int64) * self.n_experts
@@ -376,6 +431,83 @@ class EPGroupedMoE:
         self._mark("sum")
         return out
 
+    def _exact_peer(self, hidden, idx, weights, counts32, pos, send):
+        """The exact-size layer with the rows moved by the library's own stores into symmetric buffers
+        (gnf4b_ep_push_blocks / gnf4b_ep_wait_flags) instead of NCCL's all-to-all, which reaches about a third of
+        a peer copy's bandwidth at these sizes.  Every rank gathers ALL ranks' per-(destination, expert) counts
+        (one small all_gather, then the layer's one host read), so each knows where its blocks start in every
+        peer's receive buffer and where every peer's results start in its own return buffer.  Returns None when the
+        rows of this step do not fit the buffers (every rank sees the same table and decides the same)."""
+        import ctypes
+        import _gnf4b
+        import nf4_grouped
+        W, El, rank = self.world, self.e_local, self.rank
+        dev = hidden.device
+        H = hidden.shape[1]
+        P = send.shape[0]
+        all_counts = torch.empty(W, W, El, dtype=torch.int32, device=dev)            # [source, destination, expert]
+        dist.all_gather_into_tensor(all_counts.reshape(-1), counts32.reshape(-1), group=self.group)
+        if self._host_all is None or self._host_all.shape != all_counts.shape:
+            self._host_all = torch.empty(all_counts.shape, dtype=torch.int32).pin_memory()
+        self._host_all.copy_(all_counts, non_blocking=True)
+        torch.cuda.current_stream(dev).synchronize()
+        tab = self._host_all.clone()
+        tot = tab.sum(-1, dtype=torch.int64)                                         # rows [source, destination]
+        self._peer_recv_counts = all_counts[:, rank, :].contiguous()
+        px = self._peer_large_buf.get((H, dev))
+        if px is None:
+            rows = int(tot.sum(1).max())            # the most pairs any rank holds: the same number on every rank
+            px = self._peer_large_buf[(H, dev)] = LargePeerExchange.shared(self.group, W, rank, 2 * rows, rows, H, dev)
+        n_recv_all = tot.sum(0)
+        if int(n_recv_all.max()) > px.cap_recv or int(tot.sum(1).max()) > px.cap_ret:
+            return None
+        lib = _gnf4b.load()
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        status = nf4_grouped._status_word(dev).data_ptr()
+        row = H * 2
+        send_tot, recv_tot = tot[rank].tolist(), tot[:, rank].tolist()
+        send_start = [0] * W
+        recv_start = [0] * W
+        for r in range(1, W):
+            send_start[r] = send_start[r - 1] + send_tot[r - 1]
+            recv_start[r] = recv_start[r - 1] + recv_tot[r - 1]
+        n_recv = sum(recv_tot)
+        start_in_dest = [int(tot[:rank, d].sum()) for d in range(W)]               # my block in d's receive buffer
+        ret_start_in_src = [int(tot[s, :rank].sum()) for s in range(W)]            # my results in s's return buffer
+        step = px.next_step()
+        vp = ctypes.c_void_p
+
+        def push(srcs, dsts, sizes, flag_off):
+            a_src = (vp * W)(*srcs)
+            a_dst = (vp * W)(*dsts)
+            a_len = (ctypes.c_int64 * W)(*sizes)
+            a_flag = (vp * W)(*[px.ptrs[r] + flag_off + rank * 4 for r in range(W)])
+            _gnf4b.check(lib.gnf4b_ep_push_blocks(W, a_src, a_dst, a_len, a_flag, step, px.ptrs[rank] + px.done_off, stream),
+                         "gnf4b_ep_push_blocks")
+
+        with torch.cuda.device(dev):
+            push([send.data_ptr() + send_start[d] * row for d in range(W)],
+                 [px.ptrs[d] + px.recv_off + start_in_dest[d] * row for d in range(W)],
+                 [send_tot[d] * row for d in range(W)], px.flags_dispatch_off)
+            _gnf4b.check(lib.gnf4b_ep_wait_flags(px.ptrs[rank] + px.flags_dispatch_off, W, step, px.timeout_ms, status, stream),
+                         "gnf4b_ep_wait_flags")
+        self._mark("dispatch")
+        recv = px.view(px.recv_off, n_recv, H)
+        stg = dict(recv=recv)
+        host = torch.stack((tab[rank], tab[:, rank]))
+        self.last_rows = n_recv
+        back = self._exact_compute(stg, host, self._peer_recv_counts, 0, El)
+        with torch.cuda.device(dev):
+            push([back.data_ptr() + recv_start[s] * row for s in range(W)],
+                 [px.ptrs[s] + px.ret_off + ret_start_in_src[s] * row for s in range(W)],
+                 [recv_tot[s] * row for s in range(W)], px.flags_combine_off)
+            _gnf4b.check(lib.gnf4b_ep_wait_flags(px.ptrs[rank] + px.flags_combine_off, W, step, px.timeout_ms, status, stream),
+                         "gnf4b_ep_wait_flags")
+        self._mark("combine")
+        out = combine_rows(px.view(px.ret_off, P, H), pos.reshape(idx.shape), weights)
+        self._mark("sum")
+        return out
+
     def _exact_dispatch(self, send_part, host, lo, hi, H):
         """Rows for local experts [lo, hi) of every rank: one all_to_all with the split sizes from the host counts."""
         send_splits = host[0][:, lo:hi].sum(1).tolist()
@@ -387,6 +519,12 @@ class EPGroupedMoE:
 
     def _exact_compute_return(self, stg, ret_part, host, recv_counts, lo, hi):
         """The grouped GEMMs and the activation on the received rows of local experts [lo, hi), results back."""
+        back = self._exact_compute(stg, host, recv_counts, lo, hi)
+        self._a2a(ret_part, back, stg["send_splits"], stg["recv_splits"])
+
+    def _exact_compute(self, stg, host, recv_counts, lo, hi):
+        """The grouped GEMMs and the activation on the received rows of local experts [lo, hi); returns the result
+        rows in the order the rows arrived."""
         W, El = self.world, self.e_local
         recv = stg["recv"]
         n_recv = recv.shape[0]
@@ -407,11 +545,12 @@ class EPGroupedMoE:
         y = self.grouped_fn(h, self.down[0], self.down[1], sizes_l, eids)
         self._mark("down")
         if perm is None:
-            back = y
-        else:
-            back = torch.empty_like(recv)
-            back[perm] = y
-        self._a2a(ret_part, back, stg["send_splits"], stg["recv_splits"])
+            return y
+        # back[perm[i]] = y[i] as a gather through the inverse permutation (an index_put of whole rows is several
+        # times slower than a gather)
+        inv = torch.empty_like(perm)
+        inv[perm] = torch.arange(perm.numel(), device=perm.device)
+        return y[inv]
 
     def _exact_part(self, send, ret, host, recv_counts, lo, hi, H):
         self._exact_compute_return(self._exact_dispatch(send, host, lo, hi, H), ret, host, recv_counts, lo, hi)

@@ -355,6 +355,19 @@ int gnf4b_ep_plan_large(const int64_t* idx, int64_t P, int32_t k, int32_t n_expe
                         const void* hidden, int64_t H, int32_t* counts, int64_t* pos, void* send, void* scratch,
                         size_t scratch_bytes, int32_t* status_word, void* cuda_stream);
 
+/* Large-batch exchange without a collective library: up to GNF4B_EP_MAX_WORLD blocks of rows (src[b] -> dst[b], bytes[b]
+ * a multiple of 16, dst typically a peer's symmetric buffer) copied by all SMs with plain 16-byte stores; when the last
+ * CTA is through, behind a system-scope fence, flags[b] (this rank's flag word in peer b's buffer; may be null) is set
+ * to `step`.  done_counter: a device int32 of this rank that is zero before the first call (left at zero).  The
+ * receiver queues gnf4b_ep_wait_flags(its flag words, world, step) before the kernels that read the rows: a bounded
+ * wait (timeout_ms; GNF4B_ST_TIMEOUT in the status word on expiry) until every flag has reached `step` (flags only
+ * grow).  The caller sees to it that a block's destination is free: in ep_moe a rank pushes step n + 1 only after its
+ * combine of step n has heard from every rank. */
+int gnf4b_ep_push_blocks(int32_t n, const void* const* src, void* const* dst, const int64_t* bytes, int32_t* const* flags,
+                         int32_t step, int32_t* done_counter, void* cuda_stream);
+int gnf4b_ep_wait_flags(const int32_t* flags, int32_t world, int32_t step, int32_t timeout_ms, int32_t* status_word,
+                        void* cuda_stream);
+
 /* The same small-batch exchange without a collective library (expert-parallel layer; no reference counterpart):
  * each rank owns ONE exchange buffer of gnf4b_ep_peer_layout(...)[0] bytes that every other rank of the node can
  * address (peer access / symmetric memory); ctx.peers[r] is rank r's buffer as THIS process addresses it, 256-byte

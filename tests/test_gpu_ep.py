@@ -84,6 +84,18 @@ def _worker(rank, world, port, q):
         piped = ep_moe.EPGroupedMoE(E, sh(gu), sh(dn), fmt="nf4", split_experts=True)
         a, b = piped.forward(xl, il, wl), whole.forward(xl, il, wl)
         same_chunked = _agree(a, b) and piped._streams is not None and whole._streams is None
+        # the same large batch with the rows moved by the library's own stores into symmetric buffers (the default)
+        # against NCCL's all-to-all: the GEMMs see the same rows in the same order, so the same bits; twice (the
+        # buffers and flags are reused), then a larger step that does not fit the buffers and goes over NCCL
+        os.environ["GNF4B_EP_PEER_LARGE"] = "0"
+        over_nccl = ep_moe.EPGroupedMoE(E, sh(gu), sh(dn), fmt="nf4", split_experts=False)
+        os.environ["GNF4B_EP_PEER_LARGE"] = "1"
+        for rep in range(2):
+            xr, ir, wr = (t.to(dev) for t in _tokens(rank + 400 + rep, E, H, k, 2600))
+            same_chunked = same_chunked and torch.equal(whole.forward(xr, ir, wr), over_nccl.forward(xr, ir, wr))
+        same_chunked = same_chunked and len(whole._peer_large_buf) == 1 and not over_nccl._peer_large_buf
+        xb, ib, wb = (t.to(dev) for t in _tokens(rank + 500, E, H, k, 2600 * 3))
+        same_chunked = same_chunked and torch.equal(whole.forward(xb, ib, wb), over_nccl.forward(xb, ib, wb))
         torch.cuda.synchronize()
         q.put((rank, y.float().cpu().numpy(), nf4_grouped.last_status(dev), same, peer_used, same_graph, same_chunked))
     finally:
