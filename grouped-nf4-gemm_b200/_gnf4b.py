@@ -141,7 +141,7 @@ def _declare(lib):
     lib.gnf4b_ep_plan_large.restype = C.c_int
     lib.gnf4b_ep_plan_large.argtypes = [vp, i64, i32, i32, i32, i32, vp, i64, vp, vp, vp, vp, sz, vp, vp]
     lib.gnf4b_ep_push_blocks.restype = C.c_int
-    lib.gnf4b_ep_push_blocks.argtypes = [i32, vp, vp, vp, vp, i32, vp, vp]
+    lib.gnf4b_ep_push_blocks.argtypes = [i32, vp, vp, vp, vp, i32, i32, vp, vp]
     lib.gnf4b_ep_wait_flags.restype = C.c_int
     lib.gnf4b_ep_wait_flags.argtypes = [vp, i32, i32, i32, vp, vp]
     lib.gnf4b_gather_rows_by_id.restype = C.c_int

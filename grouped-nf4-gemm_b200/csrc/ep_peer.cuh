@@ -543,21 +543,23 @@ struct EpPushArgs {
     int64_t bytes[kEpPeerMaxWorld];            // multiples of 16
     int32_t* flag[kEpPeerMaxWorld];            // this rank's flag word in every peer's buffer (null: no flag)
     int32_t* done_counter;                     // this rank only: finished-CTA counter, left at zero
-    int32_t n, step;
+    int32_t n, step, rot;
 };
 
 constexpr int64_t kEpPushChunk = 64 << 10;     // bytes of one block a CTA takes at a time
 
 __global__ void __launch_bounds__(kEpPeerThreads)
 ep_push_blocks_kernel(const EpPushArgs a) {
-    // chunks of all blocks numbered through; CTA c takes chunks c, c + grid, ...
-    int64_t first[kEpPeerMaxWorld + 1];
-    first[0] = 0;
-    for (int b = 0; b < a.n; ++b) first[b + 1] = first[b] + (a.bytes[b] + kEpPushChunk - 1) / kEpPushChunk;
-    for (int64_t c = blockIdx.x; c < first[a.n]; c += gridDim.x) {
-        int b = 0;
-        while (c >= first[b + 1]) ++b;
-        const int64_t lo = (c - first[b]) * kEpPushChunk, hi = min(a.bytes[b], lo + kEpPushChunk);
+    // Chunks are taken round by round over the blocks -- chunk r of every block before chunk r + 1 of any -- and the
+    // round starts at block `rot` (the caller's rank): a rank then writes to all its peers at once, and no two ranks
+    // start on the same peer.  (Block after block, every rank would first pour into peer 0's links, then peer 1's.)
+    int64_t rounds = 0;
+    for (int b = 0; b < a.n; ++b) rounds = max(rounds, (a.bytes[b] + kEpPushChunk - 1) / kEpPushChunk);
+    for (int64_t c = blockIdx.x; c < rounds * a.n; c += gridDim.x) {
+        const int64_t r = c / a.n;
+        const int b = (int)((c - r * a.n + a.rot) % a.n);
+        const int64_t lo = r * kEpPushChunk, hi = min(a.bytes[b], lo + kEpPushChunk);
+        if (lo >= hi) continue;
         const uint4* s = reinterpret_cast<const uint4*>(a.src[b] + lo);
         uint4* d = reinterpret_cast<uint4*>(a.dst[b] + lo);
         const int64_t n16 = (hi - lo) >> 4;

@@ -1238,7 +1238,7 @@ int gnf4b_ep_plan(const int64_t* idx, int32_t P, int32_t k, int32_t n_experts, i
 }
 
 int gnf4b_ep_push_blocks(int32_t n, const void* const* src, void* const* dst, const int64_t* bytes, int32_t* const* flags,
-                         int32_t step, int32_t* done_counter, void* cuda_stream) {
+                         int32_t step, int32_t first_block, int32_t* done_counter, void* cuda_stream) {
     if (n < 0 || n > kEpPeerMaxWorld || !done_counter) return GNF4B_EINVAL;
     if (n == 0) return GNF4B_OK;
     if (!src || !dst || !bytes) return GNF4B_EINVAL;
@@ -1257,6 +1257,7 @@ int gnf4b_ep_push_blocks(int32_t n, const void* const* src, void* const* dst, co
     }
     a.n = n;
     a.step = step;
+    a.rot = ((first_block % n) + n) % n;
     a.done_counter = done_counter;
     DevInfo di;
     int rc = device_info(&di);

@@ -452,7 +452,8 @@ class EPGroupedMoE:
         self._host_all.copy_(all_counts, non_blocking=True)
         torch.cuda.current_stream(dev).synchronize()
         tab = self._host_all.clone()
-        tot = tab.sum(-1, dtype=torch.int64)                                         # rows [source, destination]
+        # (numpy for the few dozen integers: the GPU waits while the host does this arithmetic)
+        tot = tab.numpy().sum(-1, dtype="int64")                                     # rows [source, destination]
         self._peer_recv_counts = all_counts[:, rank, :].contiguous()
         px = self._peer_large_buf.get((H, dev))
         if px is None:
@@ -466,14 +467,11 @@ class EPGroupedMoE:
         status = nf4_grouped._status_word(dev).data_ptr()
         row = H * 2
         send_tot, recv_tot = tot[rank].tolist(), tot[:, rank].tolist()
-        send_start = [0] * W
-        recv_start = [0] * W
-        for r in range(1, W):
-            send_start[r] = send_start[r - 1] + send_tot[r - 1]
-            recv_start[r] = recv_start[r - 1] + recv_tot[r - 1]
+        send_start = (tot[rank].cumsum() - tot[rank]).tolist()
+        recv_start = (tot[:, rank].cumsum() - tot[:, rank]).tolist()
         n_recv = sum(recv_tot)
-        start_in_dest = [int(tot[:rank, d].sum()) for d in range(W)]               # my block in d's receive buffer
-        ret_start_in_src = [int(tot[s, :rank].sum()) for s in range(W)]            # my results in s's return buffer
+        start_in_dest = tot[:rank].sum(0).tolist()                                 # my block in d's receive buffer
+        ret_start_in_src = tot[:, :rank].sum(1).tolist()                           # my results in s's return buffer
         step = px.next_step()
         vp = ctypes.c_void_p
 
@@ -482,7 +480,7 @@ class EPGroupedMoE:
             a_dst = (vp * W)(*dsts)
             a_len = (ctypes.c_int64 * W)(*sizes)
             a_flag = (vp * W)(*[px.ptrs[r] + flag_off + rank * 4 for r in range(W)])
-            _gnf4b.check(lib.gnf4b_ep_push_blocks(W, a_src, a_dst, a_len, a_flag, step, px.ptrs[rank] + px.done_off, stream),
+            _gnf4b.check(lib.gnf4b_ep_push_blocks(W, a_src, a_dst, a_len, a_flag, step, rank, px.ptrs[rank] + px.done_off, stream),
                          "gnf4b_ep_push_blocks")
 
         with torch.cuda.device(dev):

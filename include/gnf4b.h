@@ -358,13 +358,15 @@ int gnf4b_ep_plan_large(const int64_t* idx, int64_t P, int32_t k, int32_t n_expe
 /* Large-batch exchange without a collective library: up to GNF4B_EP_MAX_WORLD blocks of rows (src[b] -> dst[b], bytes[b]
  * a multiple of 16, dst typically a peer's symmetric buffer) copied by all SMs with plain 16-byte stores; when the last
  * CTA is through, behind a system-scope fence, flags[b] (this rank's flag word in peer b's buffer; may be null) is set
- * to `step`.  done_counter: a device int32 of this rank that is zero before the first call (left at zero).  The
+ * to `step`.  The blocks are taken 64 KiB at a time round by round, starting each round at block first_block (pass the
+ * rank: a rank then writes to all peers at once and no two ranks start on the same peer).  done_counter: a device int32
+ * of this rank that is zero before the first call (left at zero).  The
  * receiver queues gnf4b_ep_wait_flags(its flag words, world, step) before the kernels that read the rows: a bounded
  * wait (timeout_ms; GNF4B_ST_TIMEOUT in the status word on expiry) until every flag has reached `step` (flags only
  * grow).  The caller sees to it that a block's destination is free: in ep_moe a rank pushes step n + 1 only after its
  * combine of step n has heard from every rank. */
 int gnf4b_ep_push_blocks(int32_t n, const void* const* src, void* const* dst, const int64_t* bytes, int32_t* const* flags,
-                         int32_t step, int32_t* done_counter, void* cuda_stream);
+                         int32_t step, int32_t first_block, int32_t* done_counter, void* cuda_stream);
 int gnf4b_ep_wait_flags(const int32_t* flags, int32_t world, int32_t step, int32_t timeout_ms, int32_t* status_word,
                         void* cuda_stream);
 
