@@ -20,8 +20,8 @@ One JSON line is printed by rank 0:
 
 ``--impl reference`` times only that CPU path with all host threads, same metric and config.
 With --gpus N > 1 (under torchrun) the layer is expert-parallel: experts are sharded
-across ranks, M tokens per rank are dispatched and combined over NVLink -- decode-sized batches by
-the library's own kernels storing into the peers' memory, large ones by NCCL all-to-all.
+across ranks, M tokens per rank are dispatched and combined over NVLink by the library's own
+kernels storing into the peers' memory (NCCL all-to-all is the fallback).
 """
 from __future__ import annotations
 
@@ -133,8 +133,7 @@ def workload_config(shape, tokens, layers, n_gpus=1):
     else:
         workload = (f"{shape.name} {shape.fmt} MoE layer, expert-parallel over {n_gpus} GPUs "
                     f"({shape.experts // n_gpus} experts per GPU), {tokens} tokens per GPU, top-{shape.top_k}, "
-                    f"dispatch and combine over NVLink (decode-sized batches: the library's peer-memory kernels; "
-                    f"large batches: NCCL all_to_all)")
+                    f"dispatch and combine over NVLink by the library's own stores into peer memory")
     return {"workload": workload, "tokens": tokens, "layers_resident": layers,
             "l2": f"inputs larger than L2: {layers} layer stacks walked round-robin, fresh routing per step",
             "timing": "K steps in one CUDA graph, median over replays, CUDA events (GPU arm); wall clock per layer pass (CPU arm)"}

@@ -921,9 +921,13 @@ def bench_ep(args, shape, rank, world, B):
     # NCCL's are not counted); exact-size path: gate_up, GLU, down, combine
     peer = any(m._peer for m in mods)
     launches_per_layer = (4 if peer else 6) if graph is not None else 4
+    peer_large = any(m._peer_large_buf for m in mods)
     exchange = ("peer memory: rows and counts stored straight into the destination ranks' buffers over NVLink by this "
                 "library's kernels (8-byte words of payload + step number, bounded polls), no collective"
-                if peer else "collectives (all_to_all_single)")
+                if peer else
+                "peer memory: blocks of rows stored into the destination ranks' symmetric buffers by this library's "
+                "kernels (flags behind a fence, bounded waits); counts by one small all_gather and one host read"
+                if peer_large else "collectives (all_to_all_single)")
     line = {
         "metric": "grouped 4-bit MoE GEMM us/layer", "value": us_layer, "unit": "us/layer", "n_gpus": world,
         "steps": K, "warmup": Wm, "ms_per_step": ms_layer / K, "higher_is_better": False, "scaling": "weak",
