@@ -26,7 +26,9 @@ On GPUs of one node the fixed-capacity exchange does not go through a collective
 (``PeerExchange``): each rank's routing kernel stores the rows and their per-expert counts straight into the
 destination ranks' buffers over NVLink (symmetric memory, plain peer stores, one flag per source and
 destination), the result rows come back the same way, and the waits are bounded polls inside the two small kernels
-either side of the GEMMs: five launches per layer and no collective.
+either side of the GEMMs: four launches per layer and no collective.  Large batches move their rows the same way
+in bulk (``LargePeerExchange``: every rank gathers all ranks' counts, one host read, then blocks of rows are stored
+into the peers' buffers by all SMs with one flag per destination); NCCL's all-to-all is the fallback.
 
 Otherwise the collectives are NCCL over NVLink/NVSwitch on GPUs and gloo in the CPU tests; the GEMM is
 injectable (``grouped_fn``) so the exchange logic can be tested on CPU ranks against the
@@ -645,7 +647,7 @@ class EPGroupedMoE:
         """The fixed-capacity layer with the rows carried by the library's own kernels over peer memory: dispatch
         (plan + stores into the destinations' buffers, then bounded wait, rows unpacked expert-major, group tables),
         the two grouped GEMMs and the activation, combine (stores back, then bounded wait + routing-weight sum).
-        Five launches, no collective, no fence, no host read.  Up to ONE_ROW_MAX_ROWS row
+        Four launches (the activation is applied by the second GEMM), no collective, no fence, no host read.  Up to ONE_ROW_MAX_ROWS row
         slots every received row is its own group (the one-row kernels); beyond, the groups are the local experts."""
         import _gnf4b
         import nf4_grouped
