@@ -38,6 +38,15 @@ __host__ __device__ constexpr int decode_consumer_warps(int rm, int au) {
     return au > 3 ? 6 : (rm == 1 ? 16 : (au <= 2 ? 12 : 8));
 }
 __host__ __device__ constexpr int decode_threads(int rm, int au) { return (decode_consumer_warps(rm, au) + 1) * 32; }
+// Long rows (K > 3072), chained pairs: a weight row is shared by TWO warps -- the first takes the lower half of the
+// row's 1024-element units and hands its per-lane partial sums to the second through shared memory, which goes on
+// from them with the upper half, reduces and stores.  The per-lane order of additions is the one a single warp
+// would use, so the bits do not change, but a warp holds only half of the activation row in registers: twelve
+// consumer warps (six pairs, one row per pair and stage) instead of six.
+constexpr int kDChainPairs = 6;
+constexpr int kDChainWarps = 2 * kDChainPairs;
+constexpr int kDChainRowsMax = 2 * kDChainPairs;                 // rows of a ring stage: one or two per pair
+constexpr int kDChainPartialBytes = kDChainRowsMax * 32 * 4;     // per ring stage: one partial sum per lane and row
 constexpr int kDMaxStages = 8;
 
 // The lookup table sits at a FIXED address of the CTA's shared-memory window (dynamic shared memory
@@ -232,6 +241,53 @@ __device__ __forceinline__ void consume_rows(uint32_t st, int R, int rows, int r
     }
 }
 
+// Chained pairs (see kDChainPairs): the rows of one ring stage, row r by pair r % kDChainPairs.  Warp 2p is the
+// first half of pair p (units q_base = 0 ..), warp 2p + 1 the second (units AU ..): it waits for part_bar (one arrival
+// per first-half warp and ring pass) before it reads the partial sums.  AU = units per warp.  Returns false when
+// that wait ran out.
+template <int FMT, int SDT, int AU, int XF, int XN>
+__device__ __forceinline__ bool consume_rows_chain(uint32_t st, int R, int rows, int row_bytes, int scale_row_bytes, int n_units,
+                                                   int warp, int lane, uint32_t lane8, const uint32_t (&xr)[1][XN],
+                                                   uint16_t* out0, float* partial, uint64_t* part_bar, uint32_t phase,
+                                                   volatile int* abort_flag) {
+    const int pair = warp >> 1, second = warp & 1;
+    const int q_base = second * AU;
+    if (second && !mbar_wait_bounded(part_bar, phase, abort_flag)) return false;
+    for (int r = pair; r < rows; r += kDChainPairs) {
+        const uint32_t wrow = st + (uint32_t)(r * row_bytes);
+        const uint32_t srow = st + (uint32_t)(R * row_bytes + r * scale_row_bytes);
+        float acc = second ? partial[r * 32 + lane] : 0.f;
+#pragma unroll
+        for (int q = 0; q < AU; ++q) {
+            const int u = lane + 32 * (q + q_base);
+            if (u < n_units) {
+                constexpr int kPerUnit = XN / AU, kPerWord = kPerUnit / 4;
+                const uint4 wv = ld_shared_u32x4(wrow + u * 16);
+                const float sc = ld_shared_scale<SDT>(srow, (FMT == GNF4B_FMT_NF4) ? (u >> 1) : u);
+                float part[1][4] = {{0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const uint32_t word = i == 0 ? wv.x : i == 1 ? wv.y : i == 2 ? wv.z : wv.w;
+                    word_fma<1, XF, XN>(word, lane8, xr, q * kPerUnit + i * kPerWord, part);
+                }
+                acc += ((part[0][0] + part[0][1]) + (part[0][2] + part[0][3])) * sc;
+            }
+        }
+        if (!second) {
+            partial[r * 32 + lane] = acc;
+        } else {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (lane == 0) out0[r] = f32_to_bf16_bits(acc);
+        }
+    }
+    if (!second) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(part_bar);        // release: this warp's partial sums of the stage are written
+    }
+    return true;
+}
+
 // The lookup table of word_fma, one 256-byte row per packed byte value, built by CW warps from instruction
 // immediates (no constant memory).  XF < 2: 32 slots of float2, all holding the byte's pair of codebook values, so
 // a lane reading slot == its lane id never conflicts with another lane; a half warp writes one row per step with
@@ -397,9 +453,10 @@ __device__ __noinline__ void decode_compact_scan(const int32_t* __restrict__ off
 
 // XA = 1: the instance that can apply the FFN's activation while it loads its activation rows (DecodeArgs.x_act);
 // a separate instance so that the plain one keeps its registers.
-template <int FMT, int SDT, int AU, int RM, int RW, int XF, int XA = 0>
-__global__ void __launch_bounds__(decode_threads(RM, AU), 1) decode_gemv_kernel(const DecodeArgs a) {
-    constexpr int kCW = decode_consumer_warps(RM, AU);
+// CH = 1: long rows as chained pairs; AU is then the units per WARP (half of the row's), RM = RW = 1.
+template <int FMT, int SDT, int AU, int RM, int RW, int XF, int XA = 0, int CH = 0>
+__global__ void __launch_bounds__(CH ? (kDChainWarps + 1) * 32 : decode_threads(RM, AU), 1) decode_gemv_kernel(const DecodeArgs a) {
+    constexpr int kCW = CH ? kDChainWarps : decode_consumer_warps(RM, AU);
     constexpr int kXN = XF == 1 ? AU * 32 : AU * 16;     // registers per activation row
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t smem_base = smem_u32(smem);
@@ -409,6 +466,7 @@ __global__ void __launch_bounds__(decode_threads(RM, AU), 1) decode_gemv_kernel(
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(tail);
     uint64_t* empty_bar = full_bar + kDMaxStages;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_bar + kDMaxStages);
+    uint64_t* part_bar = empty_bar + kDMaxStages + 1;       // CH: "first halves written", one per ring stage
     int32_t* s_grp = reinterpret_cast<int32_t*>(tail + 256);
 
     const int warp = threadIdx.x >> 5;
@@ -425,6 +483,7 @@ __global__ void __launch_bounds__(decode_threads(RM, AU), 1) decode_gemv_kernel(
         for (int s = 0; s < a.stages; ++s) {
             mbar_init(full_bar + s, 1);
             mbar_init(empty_bar + s, kCW);
+            if (CH) mbar_init(part_bar + s, kDChainPairs);
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -530,7 +589,7 @@ __global__ void __launch_bounds__(decode_threads(RM, AU), 1) decode_gemv_kernel(
             const bool have = gr.valid && m < gr.rows;
 #pragma unroll
             for (int q = 0; q < AU; ++q) {
-                const int U = lane + 32 * q;
+                const int U = lane + 32 * (q + (CH ? (warp & 1) * AU : 0));
 #pragma unroll
                 for (int v = 0; v < 4; ++v) {
                     const uint4 raw = !(have && U < n_units) ? make_uint4(0, 0, 0, 0)
@@ -589,7 +648,18 @@ __global__ void __launch_bounds__(decode_threads(RM, AU), 1) decode_gemv_kernel(
             load_a(grp);
         }
         if (!poisoned && !mbar_wait_bounded(full_bar + stage, phase, abort_flag)) poisoned = true;
-        if (!poisoned && grp.valid) {
+        if constexpr (CH != 0) {
+            if (!poisoned) {
+                // (every stage, also of an empty group: the pairs' hand-over barrier counts ring passes)
+                const int n0 = tile * R;
+                float* partial = reinterpret_cast<float*>(h_s) + (size_t)stage * (kDChainPartialBytes / 4);
+                if (!consume_rows_chain<FMT, SDT, AU, XF, kXN>(
+                        smem_u32(ring + (size_t)stage * a.slot_bytes), R, grp.valid ? min(R, (int)(a.g.N - n0)) : 0, a.row_bytes,
+                        a.scale_row_bytes, n_units, warp, lane, lane8, xr, out_bf + (int64_t)grp.row0 * a.g.N + n0, partial,
+                        part_bar + stage, phase, abort_flag))
+                    poisoned = true;
+            }
+        } else if (!poisoned && grp.valid) {     // NOLINT(readability-misleading-indentation): the plain instances
             const int n0 = tile * R;
             consume_rows<FMT, SDT, AU, RM, RW, XF, kCW, kXN>(
                 smem_u32(ring + (size_t)stage * a.slot_bytes), R, min(R, (int)(a.g.N - n0)), a.row_bytes,

@@ -242,15 +242,15 @@ static cudaError_t launch_pdl(void (*kfn)(KArgs...), unsigned grid, unsigned blo
     return cudaLaunchKernelEx(&cfg, kfn, static_cast<KArgs>(args)...);
 }
 
-template <int FMT, int SDT, int AUV, int RMV, int RW, int XF, int XA = 0>
+template <int FMT, int SDT, int AUV, int RMV, int RW, int XF, int XA = 0, int CH = 0>
 static cudaError_t launch_decode_one(const DecodeArgs& da, int grid, size_t smem, cudaStream_t st) {
-    auto kfn = decode_gemv_kernel<FMT, SDT, AUV, RMV, RW, XF, XA>;
+    auto kfn = decode_gemv_kernel<FMT, SDT, AUV, RMV, RW, XF, XA, CH>;
     static int granted[64];
     cudaError_t e = ensure_smem(kfn, smem, granted);
     if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(decode_threads(RMV, AUV));
+    cfg.blockDim = dim3(CH ? (kDChainWarps + 1) * 32 : decode_threads(RMV, AUV));
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -294,8 +294,10 @@ static cudaError_t launch_decode_au(const DecodeArgs& da, int au, int rm, int rw
         if (au <= 1) return launch_decode_one<FMT, SDT, 1, 1, 1, X1>(da, grid, smem, st);
         if (au == 2) return launch_decode_one<FMT, SDT, 2, 1, 1, X1>(da, grid, smem, st);
         if (au == 3) return launch_decode_one<FMT, SDT, 3, 1, 1, X0>(da, grid, smem, st);
-        if (au <= 5) return launch_decode_one<FMT, SDT, 5, 1, 1, X0>(da, grid, smem, st);
-        if (au <= 7) return launch_decode_one<FMT, SDT, 7, 1, 1, X0>(da, grid, smem, st);
+        // long rows: chained pairs of warps, each warp half of the row's units
+        if (au <= 4) return launch_decode_one<FMT, SDT, 2, 1, 1, X0, 0, 1>(da, grid, smem, st);
+        if (au <= 6) return launch_decode_one<FMT, SDT, 3, 1, 1, X0, 0, 1>(da, grid, smem, st);
+        if (au <= 7) return launch_decode_one<FMT, SDT, 4, 1, 1, X0, 0, 1>(da, grid, smem, st);
     }
     if (rm == 2) {
         if (au <= 1) return launch_decode_one<FMT, SDT, 1, 2, 1, X0>(da, grid, smem, st);
@@ -534,7 +536,8 @@ int gnf4b_gemm_grouped(int fmt, int op, const void* x, int x_dtype, int64_t T, c
             DecodeArgs da;
             da.g = g;
             // activation on load: room for the group's activated rows behind the group prefix
-            const int64_t h_bytes = x_act ? (int64_t)rm * K * 2 + 16 : 0;
+            // (long rows: the partial sums the chained pairs hand over, one set per ring stage, sit there instead)
+            const int64_t h_bytes = x_act ? (int64_t)rm * K * 2 + 16 : (au_k > 3 ? (int64_t)kDMaxStages * kDChainPartialBytes + 16 : 0);
             const int64_t ring_room = (int64_t)di.smem_optin - (int64_t)decode_smem_bytes(0, 0, p.g_cache) - h_bytes;
             // a stage's scale span must stay 16-byte aligned: rows per stage in multiples of 4 when four scale
             // rows are, else of 8 (`contiguous` guarantees eight are)
@@ -542,6 +545,12 @@ int gnf4b_gemm_grouped(int fmt, int op, const void* x, int x_dtype, int64_t T, c
             int best_r;
             if (au_k > 3) {
                 best_r = cw;                       // long_ok checked this granularity
+                // two rows per pair and stage (half the hand-overs per byte) where twelve rows keep every span of a
+                // stage -- the last, shorter one of a group too -- 16-byte aligned, and three such stages fit the ring
+                if ((12 * srow) % 16 == 0 && (N % 12 == 0 || ((N % 12) * srow) % 16 == 0) &&
+                    3 * (int64_t)12 * (row_bytes + srow) + 1024 <= ring_room &&
+                    !(flags & GNF4B_FLAG_DECODE_ONE_ROW))
+                    best_r = 2 * cw;
             } else {
                 // rows per stage: up to 32 KiB of weight rows (at least rw per warp when three such stages fit the
                 // ring), a whole number of rows per warp with rw = 2, and among the candidates the one that gives the
