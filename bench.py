@@ -718,7 +718,8 @@ def measure_cells(args, dev, peaks, default_layers):
             lambda: fwd_cell("qwen3_30b_a3b", 64), lambda: fwd_cell("qwen3_30b_a3b", 4096),
             lambda: dgrad_cell("qwen3_30b_a3b", 4096),
             lambda: fwd_cell("gpt_oss_20b", 1), lambda: fwd_cell("gpt_oss_20b", 0, one_row_groups=32),
-            lambda: fwd_cell("gpt_oss_20b", 4096), lambda: gather_cell("qwen3_30b_a3b", 8),
+            lambda: fwd_cell("gpt_oss_20b", 4096), lambda: fwd_cell("deepseek_v3", 0, one_row_groups=32),
+            lambda: gather_cell("qwen3_30b_a3b", 8),
             lambda: gather_cell("deepseek_v3", 8)]
     for job in plan:
         try:
