@@ -926,7 +926,8 @@ def bench_ep(args, shape, rank, world, B):
     # applied on load), combine; over collectives: plan, offsets, gate_up, GLU, down, combine (torch index kernels and
     # NCCL's are not counted); exact-size path: gate_up, GLU, down, combine
     peer = any(m._peer for m in mods)
-    launches_per_layer = (4 if peer else 6) if graph is not None else 4
+    # (large batches over peer memory: 4 plan kernels, push + wait each way, gate_up, GLU, down, combine = 12)
+    launches_per_layer = (4 if peer else 6) if graph is not None else (12 if any(m._peer_large_buf for m in mods) else 4)
     peer_large = any(m._peer_large_buf for m in mods)
     exchange = ("peer memory: rows and counts stored straight into the destination ranks' buffers over NVLink by this "
                 "library's kernels (8-byte words of payload + step number, bounded polls), no collective"
