@@ -233,3 +233,30 @@ def test_gather_oracle_and_piece_table_rules():
         host_gather.piece_table([(8, 8, 12)], "cpu")
     tab, longest = host_gather.piece_table([(0, 16, 8), (8, 0, 16)], "cpu")
     assert tab.tolist() == [[0, 16, 8], [8, 0, 16]] and longest == 16
+
+
+def test_exchange_and_feeder_entry_points_check_their_arguments_on_the_host():
+    """Layout arithmetic and argument checks of the entry points added around the GEMM (no launch is reached)."""
+    import ctypes
+    import _gnf4b
+    lib = _gnf4b.load()
+    lay = (ctypes.c_int64 * 3)()
+    assert lib.gnf4b_ep_peer_layout(8, 16, 8, 2048, lay) == 0
+    total, rows_off, ret_off = int(lay[0]), int(lay[1]), int(lay[2])
+    row_bytes = 8 * 8 * 2048 * 2
+    assert rows_off % 256 == 0 and ret_off % 256 == 0
+    assert ret_off >= rows_off + 3 * row_bytes and total >= ret_off + 2 * row_bytes      # plain rows, then two 8-byte-per-4 areas
+    assert lib.gnf4b_ep_peer_layout(17, 16, 8, 2048, lay) == -1                          # more ranks than the context holds
+    assert lib.gnf4b_ep_peer_layout(8, 16, 8, 2050, lay) == -1                           # H not a multiple of 8
+    assert lib.gnf4b_ep_plan_large_scratch_bytes(32768, 128) == (32768 // 512) * 257 * 4
+    assert lib.gnf4b_ep_plan_large_scratch_bytes(1, 2048) == 0                           # more experts than the kernels' bins
+    # feeders: rows are 8-byte words
+    assert lib.gnf4b_gather_rows_by_id(None, 12, 2, None, 4, None, None, None, None) == -2
+    assert lib.gnf4b_gather_rows_by_id(None, 16, 0, None, 4, None, None, None, None) == 0   # nothing to do
+    assert lib.gnf4b_gather_rows_by_id(None, 16, 2, None, 4, None, None, None, None) == -1  # null pointers
+    assert lib.gnf4b_gather_rows_addr(None, 16, 2, None, None, None, 0, 0, None) == -1
+    assert lib.gnf4b_gather_rows_addr(None, 16, 2, None, None, None, 0, 12, None) == -2
+    # push: at most 16 blocks, byte counts multiples of 16
+    assert lib.gnf4b_ep_push_blocks(17, None, None, None, None, 1, 0, None, None) == -1
+    ctx = _gnf4b.EpPeerCtx(2, 0, 4, 8, 64)
+    assert lib.gnf4b_ep_peer_dispatch(ctypes.byref(ctx), None, 0, 2, 8, 4, None, None, 0, None, None, None, None) == -1   # no buffers
