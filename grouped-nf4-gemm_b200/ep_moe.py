@@ -324,7 +324,9 @@ class EPGroupedMoE:
 
     # -- the layer ---------------------------------------------------------------
     def forward(self, hidden: torch.Tensor, idx: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
-        """hidden [M, H] bf16, idx [M, k] global expert ids, weights [M, k] fp32 -> [M, H] bf16."""
+        """hidden [M, H] bf16, idx [M, k] global expert ids, weights [M, k] fp32 -> [M, H] bf16.
+        A collective call: every rank of the group calls it with the same M and k (the choice between the
+        fixed-capacity and the exact-size exchange, and the capacity itself, follow from them)."""
         W, El = self.world, self.e_local
         dev = hidden.device
         self._mark("start")
