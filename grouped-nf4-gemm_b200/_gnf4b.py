@@ -37,6 +37,7 @@ FLAG_HOST_COPIES = 0x800000       # ablation: host-buffer entries move small cal
 FLAG_FFN_UNFUSED = 0x100000       # ablation: gnf4b_ffn_grouped as three launches even where it would fuse
 ACT_SILU_GLU, ACT_GPT_OSS_GLU = 0, 1
 FLAG_DECODE_ONE_ROW = 0x80000     # ablation: decode kernel with one weight row per warp in flight, not two
+FLAG_DECODE_BF16_ROWS = 0x2000000  # ablation: decode kernel with two activation rows as bf16 pairs, not fp32
 ST_BAD_EXPERT, ST_BAD_OFFSETS, ST_TIMEOUT = 1, 2, 4
 EUNSUPPORTED, ETOOBIG = -5, -6
 NOALLOC_SCRATCH_BYTES = 8 << 20

@@ -129,12 +129,14 @@ static int make_plan(int fmt, int op, int x_dtype, int64_t T, int32_t G, int64_t
         // rows at about 2.0 TB/s (1.6 TB/s for rows shorter than 2048 columns); the tensor kernel pays a
         // fixed MMA-issue cost per (128-row tile, 64-column stage) whatever the rows: 5.6 ns (NF4, two MMAs
         // per k-step) or 3.85 ns (MXFP4) with all SMs busy.  Measured on B200: Qwen3 gate_up crosses at a
-        // mean of 4.3 rows (model 3.9), Qwen3 down at 3.2 (3.1), gpt-oss gate_up at 2.4 (2.5).  Rows longer
+        // mean of 4.3 rows (model 3.9), Qwen3 down at 3.5 (3.5), gpt-oss gate_up at 2.4 (2.5).  Rows longer
         // than 3072 columns are streamed once per row, not per pair: fixed 1.5.
         double cross = 1.5;
         if (K <= 3072) {
             const double scale_bytes = (fmt == GNF4B_FMT_NF4) ? (double)(K / 64) * 4.0 : (double)(K / 32);
-            const double t_pass = (double)N * ((double)(K / 2) + scale_bytes) / (K >= 2048 ? 2.0e6 : 1.6e6);   // us
+            // (NF4 rows of up to 1024 columns keep both rows of a pass as fp32: 1.85 TB/s)
+            const double rate = K >= 2048 ? 2.0e6 : ((fmt == GNF4B_FMT_NF4 && K <= 1024) ? 1.85e6 : 1.6e6);
+            const double t_pass = (double)N * ((double)(K / 2) + scale_bytes) / rate;   // us
             const double t_tensor = (double)ceil_div(N, 128) * (double)ceil_div(K, 64) * (fmt == GNF4B_FMT_NF4 ? 5.6e-3 : 3.85e-3);
             cross = std::min(4.0, std::max(2.0, 2.0 * (t_tensor / t_pass - 0.5)));
         }
@@ -266,7 +268,7 @@ static cudaError_t launch_decode_one(const DecodeArgs& da, int grid, size_t smem
 // (AU <= 2), bf16 pairs beyond; MXFP4, whose codebook is exact in bf16, always takes the bf16-pair table with the
 // mixed-precision FMA.
 template <int FMT, int SDT>
-static cudaError_t launch_decode_au(const DecodeArgs& da, int au, int rm, int rw, int grid, size_t smem,
+static cudaError_t launch_decode_au(const DecodeArgs& da, int au, int rm, int rw, bool bf16_rows, int grid, size_t smem,
                                     cudaStream_t st) {
     constexpr int X1 = (FMT == GNF4B_FMT_MXFP4) ? 2 : 1;     // short rows
     constexpr int X0 = (FMT == GNF4B_FMT_MXFP4) ? 2 : 0;     // long rows, two activation rows per pass
@@ -300,7 +302,15 @@ static cudaError_t launch_decode_au(const DecodeArgs& da, int au, int rm, int rw
         if (au <= 7) return launch_decode_one<FMT, SDT, 4, 1, 1, X0, 0, 1>(da, grid, smem, st);
     }
     if (rm == 2) {
-        if (au <= 1) return launch_decode_one<FMT, SDT, 1, 2, 1, X0>(da, grid, smem, st);
+        // rows of up to 1024 columns: both activation rows fit 64 registers of a lane as fp32, and an element then
+        // costs its lookup and one FMA per row, without the two widening instructions per row of the bf16-pair form
+        // (Qwen3 down, 768 columns: 15 % faster).  Longer rows keep bf16 pairs: splitting a row over two chained warps
+        // so that each holds half of both rows as fp32 measured 8 % slower than the pairs at 2048 columns, and four
+        // rows per pass (eight or seven warps, 128 registers of activations) twice as slow per pass as two.
+        if (au <= 1) {
+            if (bf16_rows) return launch_decode_one<FMT, SDT, 1, 2, 1, X0>(da, grid, smem, st);
+            return launch_decode_one<FMT, SDT, 1, 2, 1, X1>(da, grid, smem, st);
+        }
         if (au == 2) return launch_decode_one<FMT, SDT, 2, 2, 1, X0>(da, grid, smem, st);
         if (au == 3) return launch_decode_one<FMT, SDT, 3, 2, 1, X0>(da, grid, smem, st);
     }
@@ -592,11 +602,11 @@ int gnf4b_gemm_grouped(int fmt, int op, const void* x, int x_dtype, int64_t T, c
             if (da.stages >= 3 && da.total_items < (int64_t)1 << 31) {
                 cudaError_t e;
                 if (fmt == GNF4B_FMT_NF4 && s_dtype == GNF4B_S_F32)
-                    e = launch_decode_au<GNF4B_FMT_NF4, GNF4B_S_F32>(da, au_k, rm, rw, dgrid, dsmem, st);
+                    e = launch_decode_au<GNF4B_FMT_NF4, GNF4B_S_F32>(da, au_k, rm, rw, (flags & GNF4B_FLAG_DECODE_BF16_ROWS) != 0, dgrid, dsmem, st);
                 else if (fmt == GNF4B_FMT_NF4)
-                    e = launch_decode_au<GNF4B_FMT_NF4, GNF4B_S_BF16>(da, au_k, rm, rw, dgrid, dsmem, st);
+                    e = launch_decode_au<GNF4B_FMT_NF4, GNF4B_S_BF16>(da, au_k, rm, rw, (flags & GNF4B_FLAG_DECODE_BF16_ROWS) != 0, dgrid, dsmem, st);
                 else
-                    e = launch_decode_au<GNF4B_FMT_MXFP4, GNF4B_S_E8M0>(da, au_k, rm, rw, dgrid, dsmem, st);
+                    e = launch_decode_au<GNF4B_FMT_MXFP4, GNF4B_S_E8M0>(da, au_k, rm, rw, (flags & GNF4B_FLAG_DECODE_BF16_ROWS) != 0, dgrid, dsmem, st);
                 if (e == cudaErrorNotSupported && x_act) return GNF4B_EUNSUPPORTED;
                 if (e != cudaSuccess) return cuda_fail(e, "decode kernel launch");
                 return GNF4B_OK;

@@ -56,6 +56,8 @@ extern "C" {
 #define GNF4B_FLAG_DECODE_ONE_ROW 0x80000u /* ablation: decode kernel with one weight row per warp in flight where it
                                             would keep two */
 
+#define GNF4B_FLAG_DECODE_BF16_ROWS 0x2000000u /* ablation: decode kernel, two activation rows per pass kept as bf16 pairs
+                                               and widened on use where it would keep them as fp32 (NF4, K <= 1024) */
 #define GNF4B_FLAG_FFN_UNFUSED    0x100000u /* ablation: gnf4b_ffn_grouped as three launches even where one fused
                                              launch would be taken */
 /* x is the gate_up output of the expert FFN, bf16 [T, 2K], and the activation between the two GEMMs is applied while

@@ -487,6 +487,38 @@ def test_padding_groups_are_skipped_silently(path, carrier):
     assert nf4_grouped.last_status(DEV) == 0
 
 
+@pytest.mark.parametrize("fmt,N,K,sizes,bf16_absmax", [
+    ("nf4", 2048, 768, [4, 4, 3, 12, 1, 2], False),        # up to 1024 columns: both rows as fp32
+    ("nf4", 72, 1024, [3, 1, 4, 4, 0, 16], True),
+    ("nf4", 264, 320, [2, 1, 2, 0, 5, 2], True),
+    ("nf4", 1536, 2048, [4, 3, 0, 9, 16, 1], False),       # longer rows: bf16 pairs either way
+    ("mxfp4", 136, 1024, [3, 1, 4, 4, 0, 16], False),      # MXFP4: bf16 pairs either way
+])
+def test_two_rows_as_fp32_decode_equals_bf16_pair_form_bitwise(fmt, N, K, sizes, bf16_absmax):
+    """Groups of 2..16 rows take the decode kernel two rows at a time.  NF4 rows of up to 1024 columns keep both
+    activation rows as fp32 in registers.  Same summation order per output element as the form that keeps bf16
+    pairs and widens them on use (FLAG_DECODE_BF16_ROWS) and as the general streaming kernel (device-side sizes):
+    same bits."""
+    gen = torch.Generator().manual_seed(K + N + sum(sizes))
+    E = 7
+    if fmt == "nf4":
+        W, S = synth.nf4_stack(E, N, K, gen, device=DEV, fast=True, bf16_absmax=bf16_absmax)
+        fn = gemm_4bit_grouped
+    else:
+        W, S = synth.mxfp4_stack(E, N, K, gen, device=DEV, fast=True)
+        fn = mxfp4_grouped.gemm_mxfp4_grouped
+    ids = [4, 0, 2, 4, 6, 5]
+    a = torch.randn(sum(sizes), K, generator=gen).to(torch.bfloat16).to(DEV)
+    wide = fn(a, W, S, sizes, ids, path=_gnf4b.PATH_STREAM)
+    pairs = fn(a, W, S, sizes, ids, path=_gnf4b.PATH_STREAM | _gnf4b.FLAG_DECODE_BF16_ROWS)
+    off = torch.tensor([0] + list(np.cumsum(sizes)), dtype=torch.int32, device=DEV)
+    general = fn(a, W, S, None, torch.tensor(ids, dtype=torch.int32, device=DEV), group_offsets=off, path=_gnf4b.PATH_STREAM)
+    assert torch.equal(wide, pairs)
+    assert torch.equal(wide, general)
+    assert rel_fro(wide, oracle_fwd64(fmt, a, W, S, sizes, ids)) <= REL_FRO_TOL
+    assert nf4_grouped.last_status(DEV) == 0
+
+
 @pytest.mark.parametrize("K", [1984, 2880])
 def test_two_row_decode_keeps_stage_scale_spans_16_byte_aligned(K):
     """MXFP4 rows whose scale row is not a multiple of 4 bytes (K = 1984: 62, K = 2880: 90): four scale rows are
